@@ -1,0 +1,654 @@
+// C-ABI entry points of libglmasr_fp4 (declared in include/glmasr_fp4.h): argument checks,
+// TMA descriptor construction, the one-time weight-scale pre-pack cache, private workspaces,
+// tile-shape selection and launches.  No torch types, no cuBLAS.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/glmasr_fp4.h"
+#include "elementwise.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_umma.cuh"
+#include "runtime.cuh"
+
+namespace glmasr {
+
+// ------------------------------------------------------------------------------------------
+// private state
+// ------------------------------------------------------------------------------------------
+static cudaStream_t g_stream = nullptr;
+static int *g_status = nullptr;
+static long long g_launches = 0;
+static int g_num_sms = 0;
+static bool g_umma_ready = false;
+
+static constexpr int kSlots = 12;
+static void *g_ws[kSlots] = {nullptr};
+static size_t g_ws_bytes[kSlots] = {0};
+
+struct PrepackedScales {
+    uint8_t *tiled;   // [ceil(N/128)][ceil(K/64)][512]
+    int N, K;
+};
+static std::unordered_map<const void *, PrepackedScales> g_prepack;
+
+cudaStream_t current_stream() { return g_stream; }
+
+int *device_status_word() {
+    if (g_status == nullptr) {
+        GLMASR_CUDA_CHECK(cudaMalloc(&g_status, 4 * sizeof(int)));
+        GLMASR_CUDA_CHECK(cudaMemset(g_status, 0, 4 * sizeof(int)));
+    }
+    return g_status;
+}
+
+void *workspace_slot(int slot, size_t bytes) {
+    if (bytes > g_ws_bytes[slot]) {
+        if (g_ws[slot]) {
+            GLMASR_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+            GLMASR_CUDA_CHECK(cudaFree(g_ws[slot]));
+        }
+        const size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+        GLMASR_CUDA_CHECK(cudaMalloc(&g_ws[slot], want));
+        g_ws_bytes[slot] = want;
+    }
+    return g_ws[slot];
+}
+void *workspace(size_t bytes) { return workspace_slot(0, bytes); }
+
+void free_all_private_state() {
+    cudaDeviceSynchronize();
+    for (int i = 0; i < kSlots; ++i) {
+        if (g_ws[i]) cudaFree(g_ws[i]);
+        g_ws[i] = nullptr;
+        g_ws_bytes[i] = 0;
+    }
+    for (auto &kv : g_prepack) cudaFree(kv.second.tiled);
+    g_prepack.clear();
+    if (g_status) cudaFree(g_status);
+    g_status = nullptr;
+}
+
+enum Slot : int {
+    WS_XQ = 0,        // quantised activations (packed e2m1)
+    WS_XSF = 1,       // their scales, 128x4-tiled
+    WS_XSF_ROW = 2,   // row-major scales (SIMT path)
+    WS_LOGITS = 3,    // lm_head logits
+    WS_TOKENS = 4,    // lm_head arg-max result
+    WS_TMP = 5,       // SIMT-path epilogue staging
+    WS_L_QKV = 6, WS_L_H1 = 7, WS_L_ACT = 8, WS_L_IN = 9, WS_L_OUT = 10,
+};
+
+static int num_sms() {
+    if (g_num_sms == 0) {
+        int dev = 0;
+        GLMASR_CUDA_CHECK(cudaGetDevice(&dev));
+        GLMASR_CUDA_CHECK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    return g_num_sms;
+}
+
+static bool force_simt() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_FP4_FORCE_SIMT");
+        v = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
+    }
+    return v == 1;
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA descriptors
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        GLMASR_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        GLMASR_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled not available");
+        fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D row-major tensor [rows, inner] of `elem_bytes`-byte elements, row pitch `pitch_bytes`;
+// boxes of box_rows x box_inner elements.
+static bool make_tmap(CUtensorMap *tm, const void *base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner,
+                      uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+    if (((uintptr_t)base & 15) != 0 || (pitch_bytes & 15) != 0) return false;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    const CUresult r = encode_fn()(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------
+// weight-scale pre-pack cache
+// ------------------------------------------------------------------------------------------
+static size_t tiled_sf_bytes(int rows, int K) {
+    return (size_t)((rows + 127) / 128) * (size_t)((K + 63) / 64) * 512;
+}
+
+static const uint8_t *prepacked_scales(const uint8_t *w_scales, int N, int K) {
+    auto it = g_prepack.find(w_scales);
+    if (it != g_prepack.end() && it->second.N == N && it->second.K == K) return it->second.tiled;
+    if (it != g_prepack.end()) {
+        GLMASR_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+        cudaFree(it->second.tiled);
+        g_prepack.erase(it);
+    }
+    PrepackedScales ps;
+    ps.N = N;
+    ps.K = K;
+    const size_t bytes = tiled_sf_bytes(N, K);
+    GLMASR_CUDA_CHECK(cudaMalloc(&ps.tiled, bytes));
+    GLMASR_CUDA_CHECK(cudaMemsetAsync(ps.tiled, 0, bytes, g_stream));
+    launch_swizzle_scales(ps.tiled, w_scales, N, K / 16, g_stream);
+    ++g_launches;
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+    g_prepack[w_scales] = ps;
+    return ps.tiled;
+}
+
+// ------------------------------------------------------------------------------------------
+// the fused linear
+// ------------------------------------------------------------------------------------------
+struct FusedArgs {
+    int mode;                       // GEMM_W4A4 / GEMM_W4A16 / GEMM_BF16
+    __nv_bfloat16 *out;
+    int ldo;
+    const __nv_bfloat16 *x;
+    int ldx;
+    const glmasr_fp4_weight *w;     // FP4 modes
+    const __nv_bfloat16 *w_bf16;    // BF16 mode (single weight)
+    int n_bf16;
+    int num_w;
+    float input_scale;
+    const __nv_bfloat16 *pre;
+    __nv_bfloat16 *prequant_scratch;
+    int epi;
+    const __nv_bfloat16 *residual;
+    const __nv_bfloat16 *bias;
+    int M, K;
+};
+
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+static bool tensor_core_eligible(const FusedArgs &a) {
+    if (force_simt()) return false;
+    if (a.K % 256 != 0) return false;
+    if (!aligned16(a.x) || !aligned16(a.out) || (a.ldx % 8) != 0) return false;
+    if (a.mode == GEMM_BF16) return aligned16(a.w_bf16);
+    for (int i = 0; i < a.num_w; ++i) {
+        if (a.w[i].w_scales == nullptr) return false;
+        if (!aligned16(a.w[i].w_packed) || !aligned16(a.w[i].w_scales)) return false;
+    }
+    return true;
+}
+
+static int total_out_cols(const FusedArgs &a) {
+    if (a.mode == GEMM_BF16) return a.n_bf16;
+    if (a.epi == EPI_SILU_GATE) return a.w[0].N;
+    int n = 0;
+    for (int i = 0; i < a.num_w; ++i) n += a.w[i].N;
+    return n;
+}
+
+// SIMT route: same results, any shape.
+static int run_simt(const FusedArgs &a) {
+    const uint8_t *xq = nullptr, *xs = nullptr;
+    const __nv_bfloat16 *x = a.x;
+    int ldx = a.ldx;
+    if (a.mode == GEMM_W4A4) {
+        uint8_t *q = (uint8_t *)workspace_slot(WS_XQ, (size_t)a.M * a.K / 2);
+        uint8_t *s = (uint8_t *)workspace_slot(WS_XSF_ROW, (size_t)a.M * a.K / 16);
+        launch_quantize_act(q, s, nullptr, a.x, a.pre, a.input_scale, a.M, a.K, a.ldx, g_stream);
+        ++g_launches;
+        xq = q;
+        xs = s;
+    } else if (a.pre != nullptr) {
+        GLMASR_CHECK(a.prequant_scratch != nullptr && a.ldx == a.K, "pre_quant_scale needs prequant_scratch and a dense x");
+        launch_prequant(a.prequant_scratch, a.x, a.pre, a.M, a.K, g_stream);
+        ++g_launches;
+        x = a.prequant_scratch;
+        ldx = a.K;
+    }
+    __nv_bfloat16 *dst = a.out;
+    int ldo = a.ldo;
+    if (a.epi == EPI_SILU_GATE) {
+        dst = (__nv_bfloat16 *)workspace_slot(WS_TMP, (size_t)a.M * 2 * a.w[0].N * 2);
+        ldo = 2 * a.w[0].N;
+    } else if (a.epi == EPI_RESIDUAL) {
+        dst = (__nv_bfloat16 *)workspace_slot(WS_TMP, (size_t)a.M * a.ldo * 2);
+    }
+    int col = 0;
+    const int nw = a.mode == GEMM_BF16 ? 1 : a.num_w;
+    for (int i = 0; i < nw; ++i) {
+        SimtGemmArgs g;
+        memset(&g, 0, sizeof(g));
+        g.mode = a.mode == GEMM_W4A4 ? 0 : (a.mode == GEMM_W4A16 ? 1 : 2);
+        g.x_packed = xq;
+        g.x_scales = xs;
+        g.x = x;
+        g.ldx = ldx;
+        g.M = a.M;
+        g.K = a.K;
+        g.out = dst;
+        g.ldo = ldo;
+        g.col0 = col;
+        g.bias = a.bias;
+        if (a.mode == GEMM_BF16) {
+            g.w_bf16 = a.w_bf16;
+            g.N = a.n_bf16;
+            g.alpha = 1.0f;
+        } else {
+            g.w_packed = a.w[i].w_packed;
+            g.w_scales = a.w[i].w_scales;
+            g.N = a.w[i].N;
+            g.alpha = a.mode == GEMM_W4A4 ? a.input_scale * a.w[i].w_global_scale : a.w[i].w_global_scale;
+        }
+        if (launch_simt_gemm(g, g_stream) != cudaSuccess) return -1;
+        ++g_launches;
+        col += g.N;
+    }
+    if (a.epi == EPI_SILU_GATE) {
+        GLMASR_CHECK(a.ldo == a.w[0].N, "SIMT SiLU path needs a dense output");
+        launch_silu_split(a.out, dst, a.M, a.w[0].N, g_stream);
+        ++g_launches;
+    } else if (a.epi == EPI_RESIDUAL) {
+        GLMASR_CHECK(a.ldo == total_out_cols(a), "SIMT residual path needs a dense output");
+        launch_residual_add(a.out, dst, a.residual, (long long)a.M * a.ldo, g_stream);
+        ++g_launches;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+static int run_fused(const FusedArgs &a) {
+    if (a.M <= 0 || a.K <= 0) return -1;
+    if (a.mode != GEMM_BF16) {
+        if (a.num_w < 1 || a.num_w > kMaxSegments) return -1;
+        for (int i = 0; i < a.num_w; ++i)
+            if (a.w[i].N <= 0 || a.w[i].w_packed == nullptr) return -1;
+        if (a.K % 16 != 0) return -1;
+        if (a.epi == EPI_SILU_GATE && (a.num_w != 2 || a.w[0].N != a.w[1].N)) return -1;
+        if (a.epi == EPI_RESIDUAL && (a.num_w != 1 || a.residual == nullptr)) return -1;
+    }
+    if (!tensor_core_eligible(a)) return run_simt(a);
+
+    if (!g_umma_ready) {
+        GLMASR_CUDA_CHECK(umma_gemm_init());
+        g_umma_ready = true;
+    }
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = a.M;
+    p.K = a.K;
+    p.out = a.out;
+    p.ldo = a.ldo;
+    p.residual = a.residual;
+    p.bias = a.bias;
+    p.epi = a.epi;
+    p.status = device_status_word();
+    p.num_m_tiles = (a.M + 127) / 128;
+    p.n_out = total_out_cols(a);
+
+    // operand A
+    const __nv_bfloat16 *x = a.x;
+    int ldx = a.ldx;
+    if (a.mode == GEMM_W4A4) {
+        uint8_t *xq = (uint8_t *)workspace_slot(WS_XQ, (size_t)a.M * a.K / 2);
+        uint8_t *xsf = (uint8_t *)workspace_slot(WS_XSF, tiled_sf_bytes(a.M, a.K));
+        launch_quantize_act(xq, nullptr, xsf, a.x, a.pre, a.input_scale, a.M, a.K, a.ldx, g_stream);
+        ++g_launches;
+        if (!make_tmap(&p.tm_a, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 2, (uint64_t)a.M,
+                       (uint64_t)a.K / 2, 128, 128, true))
+            return -1;
+        p.sfa = xsf;
+        p.num_k_blocks = a.K / 256;
+        p.sf_k_chunks = a.K / 64;
+    } else {
+        if (a.pre != nullptr) {
+            if (a.prequant_scratch == nullptr || a.ldx != a.K) return -1;
+            launch_prequant(a.prequant_scratch, a.x, a.pre, a.M, a.K, g_stream);
+            ++g_launches;
+            x = a.prequant_scratch;
+            ldx = a.K;
+        }
+        if (!make_tmap(&p.tm_a, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.M,
+                       (uint64_t)ldx * 2, 64, 128, true))
+            return -1;
+        p.num_k_blocks = a.K / 64;
+    }
+
+    // operand B
+    int subtiles = 0;
+    if (a.mode == GEMM_BF16) {
+        p.num_segs = 1;
+        p.seg_rows[0] = a.n_bf16;
+        p.seg_subtiles[0] = (a.n_bf16 + 127) / 128;
+        p.alpha[0] = 1.0f;
+        if (!make_tmap(&p.tm_b[0], a.w_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.n_bf16,
+                       (uint64_t)a.K * 2, 64, 128, true))
+            return -1;
+        subtiles = p.seg_subtiles[0];
+    } else {
+        p.num_segs = a.num_w;
+        for (int i = 0; i < a.num_w; ++i) {
+            const glmasr_fp4_weight &w = a.w[i];
+            p.seg_rows[i] = w.N;
+            p.seg_subtiles[i] = (w.N + 127) / 128;
+            subtiles += p.seg_subtiles[i];
+            p.alpha[i] = a.mode == GEMM_W4A4 ? a.input_scale * w.w_global_scale : w.w_global_scale;
+            if (!make_tmap(&p.tm_b[i], w.w_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 2, (uint64_t)w.N,
+                           (uint64_t)a.K / 2, 128, 128, true))
+                return -1;
+            if (a.mode == GEMM_W4A4) {
+                p.sfb[i] = prepacked_scales(w.w_scales, w.N, a.K);
+            } else {
+                if (!make_tmap(&p.tm_bs[i], w.w_scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 16,
+                               (uint64_t)w.N, (uint64_t)a.K / 16, 16, 128, false))
+                    return -1;
+            }
+        }
+    }
+
+    // tile shape: two weight sub-tiles per CTA tile when that still fills the machine
+    int nb;
+    if (a.epi == EPI_SILU_GATE) {
+        nb = 2;
+        p.num_n_tiles = p.seg_subtiles[0];
+    } else {
+        const int tiles2 = p.num_m_tiles * ((subtiles + 1) / 2);
+        nb = (subtiles >= 2 && tiles2 >= num_sms()) ? 2 : 1;
+        p.num_n_tiles = (subtiles + nb - 1) / nb;
+    }
+    const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int ctas = total_tiles < num_sms() ? total_tiles : num_sms();
+    if (launch_umma_gemm(a.mode, nb, p, ctas, g_stream) != cudaSuccess) return -1;
+    ++g_launches;
+    return 0;
+}
+
+}  // namespace glmasr
+
+using namespace glmasr;
+
+// ============================================================================================
+// 1. reference symbols
+// ============================================================================================
+extern "C" void fp4_dequant_to_bf16(uint16_t *out, const uint8_t *packed_w, const uint8_t *block_scales,
+                                    float global_scale, int rows, int cols) {
+    launch_dequant((__nv_bfloat16 *)out, packed_w, block_scales, global_scale, rows, cols, g_stream);
+    ++g_launches;
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void fp4_linear(void *handle, uint16_t *out, uint16_t *weight_scratch, uint16_t *prequant_scratch,
+                           const uint16_t *x, const uint8_t *w_packed, const uint8_t *w_scales, float w_global_scale,
+                           const uint16_t *pre_quant_scale, const uint16_t *bias, int M, int N, int K) {
+    (void)handle;
+    (void)weight_scratch;
+    if (M <= 0 || N <= 0 || K <= 0) return;   // the reference launches empty grids here
+    glmasr_fp4_weight w = {w_packed, w_scales, w_global_scale, N};
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = GEMM_W4A16;
+    a.out = (__nv_bfloat16 *)out;
+    a.ldo = N;
+    a.x = (const __nv_bfloat16 *)x;
+    a.ldx = K;
+    a.w = &w;
+    a.num_w = 1;
+    a.pre = (const __nv_bfloat16 *)pre_quant_scale;
+    a.prequant_scratch = (__nv_bfloat16 *)prequant_scratch;
+    a.epi = EPI_STORE;
+    a.bias = (const __nv_bfloat16 *)bias;
+    a.M = M;
+    a.K = K;
+    GLMASR_CHECK(run_fused(a) == 0, "fp4_linear failed (M=%d N=%d K=%d)", M, N, K);
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" int nvfp4_cutlass_available(void) { return 1; }
+
+extern "C" int nvfp4_linear(void *handle, uint16_t *out, uint16_t *dequant_buf, const uint16_t *x,
+                            const uint8_t *w_packed, const uint8_t *w_scales, float input_scale, float w_global_scale,
+                            const uint16_t *pre_quant_scale, const uint16_t *bias, int M, int N, int K) {
+    (void)handle;
+    (void)dequant_buf;
+    (void)bias;
+    if (M <= 0 || N <= 0 || K <= 0) return -1;
+    if (w_scales == nullptr) return -1;
+    if ((K % 16) != 0) return -1;
+    if (!(input_scale > 0.0f)) return -1;
+    glmasr_fp4_weight w = {w_packed, w_scales, w_global_scale, N};
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = GEMM_W4A4;
+    a.out = (__nv_bfloat16 *)out;
+    a.ldo = N;
+    a.x = (const __nv_bfloat16 *)x;
+    a.ldx = K;
+    a.w = &w;
+    a.num_w = 1;
+    a.input_scale = input_scale;
+    a.pre = (const __nv_bfloat16 *)pre_quant_scale;
+    a.epi = EPI_STORE;
+    a.M = M;
+    a.K = K;
+    return run_fused(a);
+}
+
+extern "C" void bf16_linear(void *handle, uint16_t *out, const uint16_t *x, const uint16_t *w, const uint16_t *bias,
+                            int M, int N, int K) {
+    (void)handle;
+    if (M <= 0 || N <= 0 || K <= 0) return;
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = GEMM_BF16;
+    a.out = (__nv_bfloat16 *)out;
+    a.ldo = N;
+    a.x = (const __nv_bfloat16 *)x;
+    a.ldx = K;
+    a.w_bf16 = (const __nv_bfloat16 *)w;
+    a.n_bf16 = N;
+    a.num_w = 1;
+    a.epi = EPI_STORE;
+    a.bias = (const __nv_bfloat16 *)bias;
+    a.M = M;
+    a.K = K;
+    GLMASR_CHECK(run_fused(a) == 0, "bf16_linear failed (M=%d N=%d K=%d)", M, N, K);
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void silu_mul_split_packed(uint16_t *out, const uint16_t *packed_gate_up, int M, int N) {
+    launch_silu_split((__nv_bfloat16 *)out, (const __nv_bfloat16 *)packed_gate_up, M, N, g_stream);
+    ++g_launches;
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void silu_elementwise_mul(uint16_t *gate, const uint16_t *up, int n) {
+    launch_silu_mul((__nv_bfloat16 *)gate, (const __nv_bfloat16 *)up, n, g_stream);
+    ++g_launches;
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void residual_add(uint16_t *out, const uint16_t *a, const uint16_t *b, int n) {
+    launch_residual_add((__nv_bfloat16 *)out, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, n, g_stream);
+    ++g_launches;
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void lm_head_argmax_batched(void *handle, const uint16_t *hidden, const uint16_t *lm_weight, int rows,
+                                       int dim, int vocab_size, int *out_tokens_host) {
+    if (rows <= 0) return;
+    uint16_t *logits = (uint16_t *)workspace_slot(WS_LOGITS, (size_t)rows * vocab_size * 2);
+    int *tokens = (int *)workspace_slot(WS_TOKENS, (size_t)rows * sizeof(int));
+    bf16_linear(handle, logits, hidden, lm_weight, nullptr, rows, vocab_size, dim);
+    launch_argmax_rows((const __nv_bfloat16 *)logits, tokens, rows, vocab_size, g_stream);
+    ++g_launches;
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(out_tokens_host, tokens, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, g_stream));
+    GLMASR_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+}
+
+extern "C" void lm_head_cleanup(void) {
+    GLMASR_CUDA_CHECK(cudaStreamSynchronize(g_stream));
+    for (int s : {(int)WS_LOGITS, (int)WS_TOKENS}) {
+        if (g_ws[s]) GLMASR_CUDA_CHECK(cudaFree(g_ws[s]));
+        g_ws[s] = nullptr;
+        g_ws_bytes[s] = 0;
+    }
+}
+
+// ============================================================================================
+// 2. additive entry points
+// ============================================================================================
+extern "C" int glmasr_fp4_linear_fused(int mode, uint16_t *out, int ldo, const uint16_t *x, int ldx,
+                                       const glmasr_fp4_weight *weights, int num_weights, float input_scale,
+                                       const uint16_t *pre_quant_scale, uint16_t *prequant_scratch, int epilogue,
+                                       const uint16_t *residual, int M, int K) {
+    if (mode != GLMASR_MODE_W4A4 && mode != GLMASR_MODE_W4A16) return -1;
+    if (out == nullptr || x == nullptr || weights == nullptr) return -1;
+    if (epilogue < 0 || epilogue > 2) return -1;
+    if (mode == GLMASR_MODE_W4A4) {
+        if (!(input_scale > 0.0f)) return -1;
+        for (int i = 0; i < num_weights && i < kMaxSegments; ++i)
+            if (weights[i].w_scales == nullptr) return -1;
+    }
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = mode == GLMASR_MODE_W4A4 ? GEMM_W4A4 : GEMM_W4A16;
+    a.out = (__nv_bfloat16 *)out;
+    a.ldo = ldo;
+    a.x = (const __nv_bfloat16 *)x;
+    a.ldx = ldx;
+    a.w = weights;
+    a.num_w = num_weights;
+    a.input_scale = input_scale;
+    a.pre = (const __nv_bfloat16 *)pre_quant_scale;
+    a.prequant_scratch = (__nv_bfloat16 *)prequant_scratch;
+    a.epi = epilogue;
+    a.residual = (const __nv_bfloat16 *)residual;
+    a.M = M;
+    a.K = K;
+    if (ldo < total_out_cols(a) || ldx < K) return -1;
+    return run_fused(a);
+}
+
+extern "C" int glmasr_fp4_prepack(const uint8_t *w_scales, int N, int K) {
+    if (w_scales == nullptr || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
+    return prepacked_scales(w_scales, N, K) != nullptr ? 0 : -1;
+}
+
+extern "C" void glmasr_fp4_forget(const void *w_scales) {
+    auto it = g_prepack.find(w_scales);
+    if (it == g_prepack.end()) return;
+    cudaStreamSynchronize(g_stream);
+    cudaFree(it->second.tiled);
+    g_prepack.erase(it);
+}
+
+extern "C" int glmasr_quantize_bf16_to_fp4(uint8_t *packed_out, uint8_t *scale_out, const uint16_t *x,
+                                           const uint16_t *pre_quant_scale, float input_scale, int M, int K) {
+    if (M <= 0 || K <= 0 || (K % 16) != 0 || !(input_scale > 0.0f)) return -1;
+    if (packed_out == nullptr || scale_out == nullptr || x == nullptr) return -1;
+    if (!aligned16(x) || ((uintptr_t)packed_out & 7) != 0) return -1;
+    launch_quantize_act(packed_out, scale_out, nullptr, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)pre_quant_scale,
+                        input_scale, M, K, K, g_stream);
+    ++g_launches;
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int glmasr_swizzle_rowwise_scales(uint8_t *dst, const uint8_t *src, int rows, int cols) {
+    if (dst == nullptr || src == nullptr || rows <= 0 || cols <= 0) return -1;
+    const size_t bytes = (size_t)((rows + 127) / 128 * 128) * (size_t)((cols + 3) / 4 * 4);
+    if (cudaMemsetAsync(dst, 0, bytes, g_stream) != cudaSuccess) return -1;
+    launch_swizzle_scales(dst, src, rows, cols, g_stream);
+    ++g_launches;
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int glmasr_argmax_rows(const uint16_t *logits, int *out_tokens, int rows, int vocab) {
+    if (logits == nullptr || out_tokens == nullptr || rows <= 0 || vocab <= 0) return -1;
+    launch_argmax_rows((const __nv_bfloat16 *)logits, out_tokens, rows, vocab, g_stream);
+    ++g_launches;
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+static int layer_proj_device(int mode, uint16_t *hidden_out, const uint16_t *hidden_in, const glmasr_layer_weights *lw,
+                             int M) {
+    const int H = lw->hidden, F = lw->ffn;
+    const int nqkv = lw->q.N + lw->k.N + lw->v.N;
+    if (lw->q.N != H || lw->o.N != H || lw->down.N != H || lw->gate.N != F || lw->up.N != F) return -1;
+    uint16_t *qkv = (uint16_t *)workspace_slot(WS_L_QKV, (size_t)M * nqkv * 2);
+    uint16_t *h1 = (uint16_t *)workspace_slot(WS_L_H1, (size_t)M * H * 2);
+    uint16_t *act = (uint16_t *)workspace_slot(WS_L_ACT, (size_t)M * F * 2);
+    const glmasr_fp4_weight qkvw[3] = {lw->q, lw->k, lw->v};
+    const glmasr_fp4_weight gu[2] = {lw->gate, lw->up};
+    int rc = glmasr_fp4_linear_fused(mode, qkv, nqkv, hidden_in, H, qkvw, 3, lw->in_qkv, nullptr, nullptr,
+                                     GLMASR_EPI_STORE, nullptr, M, H);
+    if (rc != 0) return rc;
+    // attention stand-in: the q slice of the fused output (row pitch nqkv) feeds o_proj
+    rc = glmasr_fp4_linear_fused(mode, h1, H, qkv, nqkv, &lw->o, 1, lw->in_o, nullptr, nullptr, GLMASR_EPI_RESIDUAL,
+                                 hidden_in, M, H);
+    if (rc != 0) return rc;
+    rc = glmasr_fp4_linear_fused(mode, act, F, h1, H, gu, 2, lw->in_gate_up, nullptr, nullptr, GLMASR_EPI_SILU_GATE,
+                                 nullptr, M, H);
+    if (rc != 0) return rc;
+    return glmasr_fp4_linear_fused(mode, hidden_out, H, act, F, &lw->down, 1, lw->in_down, nullptr, nullptr,
+                                   GLMASR_EPI_RESIDUAL, h1, M, F);
+}
+
+extern "C" int glmasr_fp4_layer_proj(int mode, uint16_t *hidden_out, const uint16_t *hidden_in,
+                                     const glmasr_layer_weights *lw, int M) {
+    if (hidden_out == nullptr || hidden_in == nullptr || lw == nullptr || M <= 0) return -1;
+    return layer_proj_device(mode, hidden_out, hidden_in, lw, M);
+}
+
+extern "C" int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16_t *hidden_in_host,
+                                          const glmasr_layer_weights *lw, int M) {
+    if (hidden_out_host == nullptr || hidden_in_host == nullptr || lw == nullptr || M <= 0) return -1;
+    const size_t bytes = (size_t)M * lw->hidden * 2;
+    uint16_t *din = (uint16_t *)workspace_slot(WS_L_IN, bytes);
+    uint16_t *dout = (uint16_t *)workspace_slot(WS_L_OUT, bytes);
+    if (cudaMemcpyAsync(din, hidden_in_host, bytes, cudaMemcpyHostToDevice, g_stream) != cudaSuccess) return -1;
+    const int rc = layer_proj_device(mode, dout, din, lw, M);
+    if (rc != 0) return rc;
+    if (cudaMemcpyAsync(hidden_out_host, dout, bytes, cudaMemcpyDeviceToHost, g_stream) != cudaSuccess) return -1;
+    return cudaStreamSynchronize(g_stream) == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int glmasr_fp4_status(void) {
+    int host[4] = {0, 0, 0, 0};
+    if (cudaStreamSynchronize(g_stream) != cudaSuccess) return -1;
+    if (g_status == nullptr) return 0;
+    if (cudaMemcpy(host, g_status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (host[0] != 0) cudaMemset(g_status, 0, sizeof(host));
+    return host[0];
+}
+
+extern "C" long long glmasr_launch_count(void) { return g_launches; }
+
+extern "C" void glmasr_set_stream(void *cuda_stream) { g_stream = (cudaStream_t)cuda_stream; }
+
+extern "C" void glmasr_fp4_cleanup(void) { free_all_private_state(); }

@@ -1,0 +1,31 @@
+// Device helpers for the stored FP4 format of the GLM-ASR Infer-engine checkpoints:
+// e2m1 nibbles (two per byte, even k in the low nibble), one e4m3 scale byte per 16 K-elements,
+// one fp32 per-tensor scale.  Restates Infer-engine/cuda/kernels.cu:96-120 of the reference.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace glmasr {
+
+// e2m1 nibble -> float (reference fp4_lut, kernels.cu:96-99), computed without a table:
+// magnitude code c = e1 e0 m;  c<2 -> c*0.5, else 2^(e-1) * (1 + m/2).
+__device__ __forceinline__ float e2m1_to_float(uint32_t nib) {
+    const uint32_t c = nib & 7u;
+    // fp32 bits of {0, .5, 1, 1.5, 2, 3, 4, 6}: for c >= 2 this is (c << 22) + 0x3F000000
+    uint32_t bits = (c << 22) + 0x3F000000u;
+    bits = (c == 0u) ? 0u : ((c == 1u) ? 0x3F000000u : bits);
+    bits |= (nib & 8u) << 28;
+    return __uint_as_float(bits);
+}
+
+// e4m3 byte -> float exactly as the reference decodes it (kernels.cu:103-120): no NaN pattern,
+// 0x7F -> 480, subnormals m/8 * 2^-6, sign bit honoured.
+__device__ __forceinline__ float e4m3_to_float_ref(uint32_t b) {
+    // (b & 0x7F) << 20 read as fp32 is value * 2^-120, subnormals included (fp32 keeps them).
+    const float mag = __uint_as_float((b & 0x7Fu) << 20) * 1.329227995784916e36f;  // * 2^120
+    return (b & 0x80u) ? -mag : mag;
+}
+
+}  // namespace glmasr

@@ -1,0 +1,56 @@
+// Parameters and launcher of the tcgen05 GEMM behind every FP4 linear (see gemm_umma.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace glmasr {
+
+enum GemmMode : int {
+    GEMM_W4A4 = 0,   // e2m1 weights x e2m1 activations, block-scaled MMA (reference nvfp4_linear semantics)
+    GEMM_W4A16 = 1,  // e2m1 weights dequantised in-kernel x bf16 activations (reference fp4_linear semantics)
+    GEMM_BF16 = 2,   // bf16 weights x bf16 activations (reference bf16_linear semantics, e.g. lm_head)
+};
+
+enum EpilogueMode : int {
+    EPI_STORE = 0,      // out[m, n] = bf16(acc * alpha_seg (+ bias[n]))
+    EPI_SILU_GATE = 1,  // segments 0/1 = gate/up: out[m, n] = bf16(silu(bf16(g)) * bf16(u))
+    EPI_RESIDUAL = 2,   // out[m, n] = bf16(float(bf16(acc * alpha)) + float(residual[m, n]))
+};
+
+static constexpr int kMaxSegments = 3;
+
+// One launch computes out[M, sum N_s] = x[M, K] * concat_s(W_s[N_s, K])^T for up to three
+// weight tensors that share the input (q|k|v, gate|up), each with its own per-tensor scale.
+struct alignas(64) GemmParams {
+    CUtensorMap tm_a;                   // activations, 128-row x 128-byte boxes, 128B swizzle
+    CUtensorMap tm_b[kMaxSegments];     // weights (packed e2m1 bytes, or bf16), same box
+    CUtensorMap tm_bs[kMaxSegments];    // W4A16: row-major e4m3 scales [N_s, K/16], 128-row x 16-byte boxes
+    const uint8_t *sfa;                 // W4A4: activation scales, 128x4-tiled
+    const uint8_t *sfb[kMaxSegments];   // W4A4: weight scales, 128x4-tiled
+    float alpha[kMaxSegments];          // applied to the fp32 accumulator of that segment
+    int seg_rows[kMaxSegments];         // N_s
+    int seg_subtiles[kMaxSegments];     // ceil(N_s / 128)
+    int num_segs;
+    int M, K;
+    int n_out;                          // output columns
+    int ldo;                            // output (and residual) row pitch in elements
+    __nv_bfloat16 *out;
+    const __nv_bfloat16 *residual;
+    const __nv_bfloat16 *bias;
+    int epi;
+    int num_m_tiles, num_n_tiles;
+    int num_k_blocks;                   // K steps of 128 operand bytes per row (W4A4: 256 elements, else 64)
+    int sf_k_chunks;                    // W4A4: 512-byte scale chunks per 128-row tile along K (= ceil(K/64))
+    int *status;
+};
+
+// nb = 128-row weight sub-tiles per CTA tile (1 or 2).  Returns cudaSuccess or the launch error.
+cudaError_t launch_umma_gemm(int mode, int nb, const GemmParams &p, int num_ctas, cudaStream_t st);
+// Opt in to the large dynamic shared memory carve-out once per process.
+cudaError_t umma_gemm_init();
+int umma_gemm_threads(int mode, int nb);
+int umma_gemm_smem_bytes(int mode, int nb);
+
+}  // namespace glmasr

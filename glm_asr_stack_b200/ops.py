@@ -1,0 +1,280 @@
+"""Host-side mirror of the Infer-engine operator interface for the FP4 linear path.
+
+Same names, argument meaning and error behaviour as the reference's C entry points
+(Infer-engine/include/cuda_kernels.h), taking torch CUDA tensors instead of raw pointers.
+torch is used only for device memory; every computation happens inside libglmasr_fp4.so.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import Fp4Weight, LayerWeights
+
+MODE_W4A4 = 0
+MODE_W4A16 = 1
+EPI_STORE = 0
+EPI_SILU_GATE = 1
+EPI_RESIDUAL = 2
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("expected a CUDA tensor")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _check(t: torch.Tensor, dtype, name: str):
+    if t.dtype != dtype:
+        raise TypeError(f"{name}: expected {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: must be contiguous")
+
+
+@dataclass
+class Fp4Tensor:
+    """One FP4 weight as the safetensors loader leaves it on the device
+    (Infer-engine/src/safetensors.c:48-55): ``weight`` U8 [N, K/2], ``weight_scale`` F8_E4M3
+    bytes [N, K/16], scalar ``weight_scale_2``; optional ``input_scale`` / ``pre_quant_scale``."""
+
+    w_packed: torch.Tensor
+    w_scales: torch.Tensor
+    w_global_scale: float
+    input_scale: float = 1.0
+    pre_quant_scale: Optional[torch.Tensor] = None
+
+    @property
+    def N(self) -> int:
+        return self.w_packed.shape[0]
+
+    @property
+    def K(self) -> int:
+        return self.w_packed.shape[1] * 2
+
+    def c_struct(self) -> Fp4Weight:
+        return Fp4Weight(self.w_packed.data_ptr(), self.w_scales.data_ptr(), float(self.w_global_scale), self.N)
+
+
+def fp4_dequant_to_bf16(packed_w: torch.Tensor, block_scales: Optional[torch.Tensor], global_scale: float,
+                        rows: Optional[int] = None, cols: Optional[int] = None) -> torch.Tensor:
+    """reference: fp4_dequant_to_bf16, Infer-engine/cuda/kernels.cu:234-246."""
+    lib = _lib.load()
+    _check(packed_w, torch.uint8, "packed_w")
+    rows = packed_w.shape[0] if rows is None else rows
+    cols = packed_w.shape[1] * 2 if cols is None else cols
+    out = torch.empty((rows, cols), dtype=torch.bfloat16, device=packed_w.device)
+    lib.fp4_dequant_to_bf16(_ptr(out), _ptr(packed_w), _ptr(block_scales), float(global_scale), rows, cols)
+    return out
+
+
+def fp4_linear(x: torch.Tensor, w_packed: torch.Tensor, w_scales: Optional[torch.Tensor], w_global_scale: float,
+               pre_quant_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference: fp4_linear (W4A16), Infer-engine/cuda/kernels.cu:1297-1318."""
+    lib = _lib.load()
+    _check(x, torch.bfloat16, "x")
+    _check(w_packed, torch.uint8, "w_packed")
+    M, K = x.shape
+    N = w_packed.shape[0]
+    if w_packed.shape[1] * 2 != K:
+        raise ValueError("w_packed must be [N, K/2]")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    scratch = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if pre_quant_scale is not None else None
+    lib.fp4_linear(None, _ptr(out), None, _ptr(scratch), _ptr(x), _ptr(w_packed), _ptr(w_scales),
+                   float(w_global_scale), _ptr(pre_quant_scale), _ptr(bias), M, N, K)
+    return out
+
+
+def nvfp4_cutlass_available() -> int:
+    return _lib.load().nvfp4_cutlass_available()
+
+
+def nvfp4_linear(out: torch.Tensor, x: torch.Tensor, w_packed: torch.Tensor, w_scales: Optional[torch.Tensor],
+                 input_scale: float, w_global_scale: float, pre_quant_scale: Optional[torch.Tensor] = None,
+                 bias: Optional[torch.Tensor] = None, M: Optional[int] = None, N: Optional[int] = None,
+                 K: Optional[int] = None) -> int:
+    """reference: nvfp4_linear (W4A4), Infer-engine/cuda/nvfp4_cutlass.cu:118-270.
+    Returns 0 on success, -1 when the reference would (bad sizes, missing scales, K % 16,
+    input_scale <= 0); ``out`` is untouched in that case."""
+    lib = _lib.load()
+    M = x.shape[0] if M is None else M
+    K = x.shape[1] if K is None else K
+    N = w_packed.shape[0] if N is None else N
+    return lib.nvfp4_linear(None, _ptr(out), None, _ptr(x), _ptr(w_packed), _ptr(w_scales), float(input_scale),
+                            float(w_global_scale), _ptr(pre_quant_scale), _ptr(bias), M, N, K)
+
+
+def bf16_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference: bf16_linear, Infer-engine/cuda/kernels.cu:1147-1193."""
+    lib = _lib.load()
+    _check(x, torch.bfloat16, "x")
+    _check(w, torch.bfloat16, "w")
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    lib.bf16_linear(None, _ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K)
+    return out
+
+
+def silu_mul_split_packed(packed_gate_up: torch.Tensor) -> torch.Tensor:
+    """reference: silu_mul_split_packed, Infer-engine/cuda/kernels.cu:1252-1273."""
+    lib = _lib.load()
+    _check(packed_gate_up, torch.bfloat16, "packed_gate_up")
+    M, N2 = packed_gate_up.shape
+    out = torch.empty((M, N2 // 2), dtype=torch.bfloat16, device=packed_gate_up.device)
+    lib.silu_mul_split_packed(_ptr(out), _ptr(packed_gate_up), M, N2 // 2)
+    return out
+
+
+def silu_elementwise_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """reference: silu_elementwise_mul (in place on gate), Infer-engine/cuda/kernels.cu:405-421."""
+    lib = _lib.load()
+    _check(gate, torch.bfloat16, "gate")
+    _check(up, torch.bfloat16, "up")
+    lib.silu_elementwise_mul(_ptr(gate), _ptr(up), gate.numel())
+    return gate
+
+
+def residual_add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference: residual_add, Infer-engine/cuda/kernels.cu:741-761."""
+    lib = _lib.load()
+    _check(a, torch.bfloat16, "a")
+    _check(b, torch.bfloat16, "b")
+    out = torch.empty_like(a) if out is None else out
+    lib.residual_add(_ptr(out), _ptr(a), _ptr(b), a.numel())
+    return out
+
+
+def lm_head_argmax_batched(hidden: torch.Tensor, lm_weight: torch.Tensor) -> torch.Tensor:
+    """reference: lm_head_argmax_batched, Infer-engine/cuda/kernels.cu:1443-1459.  Returns the
+    token ids as a HOST int32 tensor (the reference copies them to the host synchronously)."""
+    lib = _lib.load()
+    _check(hidden, torch.bfloat16, "hidden")
+    _check(lm_weight, torch.bfloat16, "lm_weight")
+    rows, dim = hidden.shape
+    vocab = lm_weight.shape[0]
+    tokens = torch.empty(rows, dtype=torch.int32)
+    lib.lm_head_argmax_batched(None, _ptr(hidden), _ptr(lm_weight), rows, dim, vocab,
+                               ctypes.c_void_p(tokens.data_ptr()))
+    return tokens
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    lib = _lib.load()
+    _check(logits, torch.bfloat16, "logits")
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    rc = lib.glmasr_argmax_rows(_ptr(logits), _ptr(out), rows, vocab)
+    if rc != 0:
+        raise RuntimeError("glmasr_argmax_rows failed")
+    return out
+
+
+def quantize_bf16_to_fp4(x: torch.Tensor, input_scale: float, pre_quant_scale: Optional[torch.Tensor] = None):
+    """reference: quantize_bf16_to_fp4_kernel, Infer-engine/cuda/nvfp4_cutlass.cu:35-87.
+    Returns (packed [M, K/2] u8, scales [M, K/16] u8)."""
+    lib = _lib.load()
+    _check(x, torch.bfloat16, "x")
+    M, K = x.shape
+    packed = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((M, K // 16), dtype=torch.uint8, device=x.device)
+    rc = lib.glmasr_quantize_bf16_to_fp4(_ptr(packed), _ptr(scales), _ptr(x), _ptr(pre_quant_scale),
+                                         float(input_scale), M, K)
+    if rc != 0:
+        raise ValueError("glmasr_quantize_bf16_to_fp4 rejected the arguments")
+    return packed, scales
+
+
+def swizzle_rowwise_scales(scales: torch.Tensor) -> torch.Tensor:
+    """reference: swizzle_rowwise_scales_kernel, Infer-engine/cuda/nvfp4_cutlass.cu:89-111."""
+    lib = _lib.load()
+    _check(scales, torch.uint8, "scales")
+    rows, cols = scales.shape
+    n = ((rows + 127) // 128 * 128) * ((cols + 3) // 4 * 4)
+    dst = torch.empty(n, dtype=torch.uint8, device=scales.device)
+    rc = lib.glmasr_swizzle_rowwise_scales(_ptr(dst), _ptr(scales), rows, cols)
+    if rc != 0:
+        raise ValueError("glmasr_swizzle_rowwise_scales rejected the arguments")
+    return dst
+
+
+def fp4_linear_fused(mode: int, x: torch.Tensor, weights: Sequence[Fp4Tensor], epilogue: int = EPI_STORE,
+                     residual: Optional[torch.Tensor] = None, input_scale: float = 1.0,
+                     pre_quant_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                     ldx: Optional[int] = None, M: Optional[int] = None) -> torch.Tensor:
+    """Up to three same-input FP4 projections in one GEMM with a fused epilogue
+    (glmasr_fp4_linear_fused; replaces linear_proj_pair_same_input + silu_mul_split_packed /
+    residual_add, Infer-engine/cuda/decoder.cu:923-978)."""
+    lib = _lib.load()
+    if x.dtype != torch.bfloat16:
+        raise TypeError("x must be bf16")
+    K = weights[0].K
+    M = x.shape[0] if M is None else M
+    ldx = x.stride(0) if ldx is None else ldx
+    n_out = weights[0].N if epilogue == EPI_SILU_GATE else sum(w.N for w in weights)
+    if out is None:
+        out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    arr = (Fp4Weight * len(weights))(*[w.c_struct() for w in weights])
+    scratch = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if (
+        pre_quant_scale is not None and mode == MODE_W4A16) else None
+    rc = lib.glmasr_fp4_linear_fused(mode, _ptr(out), out.stride(0), _ptr(x), ldx, arr, len(weights),
+                                     float(input_scale), _ptr(pre_quant_scale), _ptr(scratch), epilogue,
+                                     _ptr(residual), M, K)
+    if rc != 0:
+        raise ValueError("glmasr_fp4_linear_fused rejected the arguments")
+    return out
+
+
+def make_layer_weights(q, k, v, o, gate, up, down, hidden: int, ffn: int) -> LayerWeights:
+    return LayerWeights(q.c_struct(), k.c_struct(), v.c_struct(), o.c_struct(), gate.c_struct(), up.c_struct(),
+                        down.c_struct(), float(q.input_scale), float(o.input_scale), float(gate.input_scale),
+                        float(down.input_scale), hidden, ffn)
+
+
+def layer_proj(mode: int, hidden_in: torch.Tensor, lw: LayerWeights, out: Optional[torch.Tensor] = None):
+    """The four fused FP4 projections of one decoder layer on device tensors (glmasr_fp4_layer_proj)."""
+    lib = _lib.load()
+    out = torch.empty_like(hidden_in) if out is None else out
+    rc = lib.glmasr_fp4_layer_proj(mode, _ptr(out), _ptr(hidden_in), ctypes.byref(lw), hidden_in.shape[0])
+    if rc != 0:
+        raise RuntimeError("glmasr_fp4_layer_proj failed")
+    return out
+
+
+def layer_proj_host(mode: int, hidden_in_host: torch.Tensor, hidden_out_host: torch.Tensor, lw: LayerWeights):
+    """Same through HOST (pinned) buffers: copy in, run, copy out, synchronise."""
+    lib = _lib.load()
+    rc = lib.glmasr_fp4_layer_proj_host(mode, ctypes.c_void_p(hidden_out_host.data_ptr()),
+                                        ctypes.c_void_p(hidden_in_host.data_ptr()), ctypes.byref(lw),
+                                        hidden_in_host.shape[0])
+    if rc != 0:
+        raise RuntimeError("glmasr_fp4_layer_proj_host failed")
+    return hidden_out_host
+
+
+def status() -> int:
+    """Synchronise; return and clear the first device-side status code (0 = ok)."""
+    return _lib.load().glmasr_fp4_status()
+
+
+def launch_count() -> int:
+    return int(_lib.load().glmasr_launch_count())
+
+
+def set_stream(stream: Optional[torch.cuda.Stream]):
+    _lib.load().glmasr_set_stream(ctypes.c_void_p(stream.cuda_stream) if stream is not None else None)
+
+
+def prepack(w: Fp4Tensor) -> int:
+    return _lib.load().glmasr_fp4_prepack(_ptr(w.w_scales), w.N, w.K)
+
+
+def cleanup():
+    _lib.load().glmasr_fp4_cleanup()

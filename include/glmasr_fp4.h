@@ -1,0 +1,166 @@
+/*
+ * libglmasr_fp4 -- B200 (sm_100a) drop-in for the FP4-weight linear path of the GLM-ASR
+ * Infer-engine.  Plain C ABI: bf16 tensors are uint16_t*, handles are void*, every pointer
+ * is a DEVICE pointer unless the parameter name ends in _host.
+ *
+ * Section 1 re-exports, with unchanged names, argument order and error behaviour, the
+ * symbols the engine's decoder links for this path; each declaration cites the reference
+ * interface it replaces (paths inside the reference project).  Section 2 is additive.
+ *
+ * Threading/stream contract (same as the reference): one host thread, launches go to the
+ * legacy default stream unless glmasr_set_stream() was called, not re-entrant.
+ * Error contract: the void entry points print to stderr and exit(1) on a CUDA error
+ * (reference: Infer-engine/include/types.h:182-199); the int entry points return 0 on
+ * success and -1 on bad arguments or a launch failure.
+ *
+ * FP4 storage format (reference: Infer-engine/cuda/kernels.cu:96-120, 200-231):
+ *   w_packed  uint8 [N, K/2]   two e2m1 nibbles per byte, even k in bits 0-3
+ *   w_scales  uint8 [N, K/16]  one e4m3 scale per 16 consecutive k, row-major
+ *   w_global_scale  fp32 per tensor;   weight = lut[nibble] * e4m3(scale) * global
+ */
+#ifndef GLMASR_FP4_H
+#define GLMASR_FP4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================= 1. reference symbols (drop-in) ======================= */
+
+/* Infer-engine/include/cuda_kernels.h:17-21, Infer-engine/cuda/kernels.cu:234-246.
+ * out[r,c] = bf16(lut[nibble] * e4m3(block_scales[r, c/16]) * global_scale);
+ * block_scales == NULL means scale 1.  Bit-exact with the reference. */
+void fp4_dequant_to_bf16(uint16_t *out, const uint8_t *packed_w, const uint8_t *block_scales,
+                         float global_scale, int rows, int cols);
+
+/* Infer-engine/include/cuda_kernels.h:80-89, Infer-engine/cuda/kernels.cu:1297-1318.
+ * W4A16: out[M,N] = bf16(x[M,K] * dequant(W)[N,K]^T (+ bias)), fp32 accumulation.
+ * The reference materialises the bf16 weight in weight_scratch on every call; this
+ * implementation dequantises inside the GEMM and leaves weight_scratch untouched.
+ * prequant_scratch ([M,K] bf16) is written only when pre_quant_scale != NULL, as in the
+ * reference.  handle is ignored (no cuBLAS). */
+void fp4_linear(void *handle, uint16_t *out, uint16_t *weight_scratch, uint16_t *prequant_scratch,
+                const uint16_t *x, const uint8_t *w_packed, const uint8_t *w_scales,
+                float w_global_scale, const uint16_t *pre_quant_scale, const uint16_t *bias,
+                int M, int N, int K);
+
+/* Infer-engine/include/cuda_kernels.h:91, Infer-engine/cuda/nvfp4_cutlass.cu:113-116. Returns 1. */
+int nvfp4_cutlass_available(void);
+
+/* Infer-engine/include/cuda_kernels.h:93-101, Infer-engine/cuda/nvfp4_cutlass.cu:118-270.
+ * W4A4: activations are quantised to e2m1 with one e4m3 scale per 16 k exactly as the
+ * reference quantiser does, then a block-scaled FP4 x FP4 product with fp32 accumulation,
+ * alpha = input_scale * w_global_scale, bf16 out.  Returns -1 (nothing launched) when
+ * M, N or K <= 0, w_scales == NULL, K % 16 != 0 or input_scale <= 0.  bias is ignored, as
+ * in the reference.  dequant_buf is NOT used: temporaries live in a private workspace
+ * (the reference carves them from dequant_buf + N*K and can overrun it). */
+int nvfp4_linear(void *handle, uint16_t *out, uint16_t *dequant_buf, const uint16_t *x,
+                 const uint8_t *w_packed, const uint8_t *w_scales, float input_scale,
+                 float w_global_scale, const uint16_t *pre_quant_scale, const uint16_t *bias,
+                 int M, int N, int K);
+
+/* Infer-engine/include/cuda_kernels.h:63-68, Infer-engine/cuda/kernels.cu:1147-1193.
+ * out[M,N] = bf16(x[M,K] * w[N,K]^T (+ bias)), bf16 weights (the reference lm_head). */
+void bf16_linear(void *handle, uint16_t *out, const uint16_t *x, const uint16_t *w,
+                 const uint16_t *bias, int M, int N, int K);
+
+/* Infer-engine/include/cuda_kernels.h:76-78, Infer-engine/cuda/kernels.cu:1252-1273.
+ * out[m,n] = bf16((g*sigmoid(g))*u), g = packed[m,n], u = packed[m,N+n]. */
+void silu_mul_split_packed(uint16_t *out, const uint16_t *packed_gate_up, int M, int N);
+
+/* Infer-engine/include/cuda_kernels.h:32, Infer-engine/cuda/kernels.cu:405-421. In place on gate. */
+void silu_elementwise_mul(uint16_t *gate, const uint16_t *up, int n);
+
+/* Infer-engine/include/cuda_kernels.h:45-46, Infer-engine/cuda/kernels.cu:741-761. */
+void residual_add(uint16_t *out, const uint16_t *a, const uint16_t *b, int n);
+
+/* Infer-engine/include/cuda_kernels.h:176-180, Infer-engine/cuda/kernels.cu:1443-1459.
+ * bf16 lm_head projection + row arg-max (reference tie-break), tokens copied to the HOST
+ * array out_tokens_host before returning. */
+void lm_head_argmax_batched(void *handle, const uint16_t *hidden, const uint16_t *lm_weight,
+                            int rows, int dim, int vocab_size, int *out_tokens_host);
+
+/* Infer-engine/include/cuda_kernels.h:182, Infer-engine/cuda/kernels.cu:1461-1475. */
+void lm_head_cleanup(void);
+
+/* ======================= 2. additive entry points ======================= */
+
+#define GLMASR_MODE_W4A4  0   /* nvfp4_linear arithmetic */
+#define GLMASR_MODE_W4A16 1   /* fp4_linear arithmetic   */
+
+#define GLMASR_EPI_STORE     0  /* out = bf16(acc*alpha)                                         */
+#define GLMASR_EPI_SILU_GATE 1  /* weights = {gate, up}: out[M,N] = silu_mul_split_packed fused   */
+#define GLMASR_EPI_RESIDUAL  2  /* one weight: out = residual_add(bf16(acc*alpha), residual) fused */
+
+typedef struct {
+    const uint8_t *w_packed;   /* [N, K/2] */
+    const uint8_t *w_scales;   /* [N, K/16] */
+    float w_global_scale;      /* the tensor's weight_scale_2 */
+    int N;
+} glmasr_fp4_weight;
+
+/* Up to three FP4 weights that share one input (q|k|v, gate|up) in ONE GEMM, each with its
+ * own per-tensor scale, replacing linear_proj + linear_proj_pair_same_input
+ * (Infer-engine/cuda/decoder.cu:861-978) and, through the epilogue modes, the separate
+ * silu_mul_split_packed / residual_add passes.  Output columns are the weights'
+ * concatenated rows (EPI_STORE, EPI_RESIDUAL) or N of the gate (EPI_SILU_GATE).
+ * x has row pitch ldx elements, out and residual row pitch ldo.  input_scale is used by
+ * W4A4 only.  prequant_scratch ([M,K] bf16) is needed for W4A16 with pre_quant_scale.
+ * Returns 0, or -1 on invalid arguments. */
+int glmasr_fp4_linear_fused(int mode, uint16_t *out, int ldo, const uint16_t *x, int ldx,
+                            const glmasr_fp4_weight *weights, int num_weights, float input_scale,
+                            const uint16_t *pre_quant_scale, uint16_t *prequant_scratch,
+                            int epilogue, const uint16_t *residual, int M, int K);
+
+/* One-time re-tiling of a weight's e4m3 scales into the 128x4 tile order the tensor core
+ * reads (what Infer-engine/cuda/nvfp4_cutlass.cu:184-188 redoes on every call; the slot of
+ * the declared-but-undefined swizzle_weight_scale, Infer-engine/cuda/kernels.cuh:24).
+ * Cached by device pointer; nvfp4_linear / glmasr_fp4_linear_fused call it on first use. */
+int glmasr_fp4_prepack(const uint8_t *w_scales, int N, int K);
+/* Drop cached state for a weight whose memory is about to be freed (safetensors_free). */
+void glmasr_fp4_forget(const void *w_scales);
+
+/* The reference activation quantiser as a stand-alone call
+ * (Infer-engine/cuda/nvfp4_cutlass.cu:35-87): packed_out [M,K/2], scale_out [M,K/16] row-major. */
+int glmasr_quantize_bf16_to_fp4(uint8_t *packed_out, uint8_t *scale_out, const uint16_t *x,
+                                const uint16_t *pre_quant_scale, float input_scale, int M, int K);
+/* Infer-engine/cuda/nvfp4_cutlass.cu:89-111 into dst of ceil128(rows)*ceil4(cols) bytes (zero-filled here). */
+int glmasr_swizzle_rowwise_scales(uint8_t *dst, const uint8_t *src, int rows, int cols);
+
+/* Row arg-max over bf16 logits [rows, vocab] with the reference tie-break
+ * (Infer-engine/cuda/kernels.cu:1387-1426); out_tokens is a device array. */
+int glmasr_argmax_rows(const uint16_t *logits, int *out_tokens, int rows, int vocab);
+
+/* The FP4 projections of one decoder layer in the order the reference drivers call them
+ * (Infer-engine/cuda/decoder.cu:1375-1391, 1443-1533): q|k|v, o + residual, gate|up with
+ * SiLU-gate, down + residual.  Attention itself is not part of this path: the q slice of the
+ * fused q|k|v output stands in for the attention output.  hidden_in/out are [M, hidden]. */
+typedef struct {
+    glmasr_fp4_weight q, k, v, o, gate, up, down;
+    float in_qkv, in_o, in_gate_up, in_down;   /* per-projection input_scale (W4A4) */
+    int hidden, ffn;
+} glmasr_layer_weights;
+int glmasr_fp4_layer_proj(int mode, uint16_t *hidden_out, const uint16_t *hidden_in,
+                          const glmasr_layer_weights *lw, int M);
+/* Same, with HOST (preferably pinned) hidden_in_host / hidden_out_host: copies in, runs,
+ * copies out and synchronises -- the end-to-end call the benchmark times. */
+int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16_t *hidden_in_host,
+                               const glmasr_layer_weights *lw, int M);
+
+/* Synchronise and return the first device-side status code recorded since the last call
+ * (0 = none; 1..5 = a bounded wait inside a kernel ran out), then clear it. */
+int glmasr_fp4_status(void);
+/* Number of kernels this library has launched since load (for launch accounting). */
+long long glmasr_launch_count(void);
+/* Route all launches to the given cudaStream_t (NULL = legacy default stream). */
+void glmasr_set_stream(void *cuda_stream);
+/* Free every private workspace / cache (decoder_cleanup_all / lm_head_cleanup analogue). */
+void glmasr_fp4_cleanup(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLMASR_FP4_H */
