@@ -52,6 +52,8 @@ SIGNATURES = {
     "glmasr_fp4_layer_proj_host": (c_int, [c_int, P, P, POINTER(LayerWeights), c_int]),
     "glmasr_fp4_status": (c_int, []),
     "glmasr_launch_count": (c_longlong, []),
+    "glmasr_profile_enable": (None, [c_int]),
+    "glmasr_profile_read": (c_int, [c_int, P, P, P]),
     "glmasr_set_stream": (None, [P]),
     "glmasr_fp4_cleanup": (None, []),
 }

@@ -29,6 +29,15 @@ static long long g_launches = 0;
 static int g_num_sms = 0;
 static bool g_umma_ready = false;
 
+// optional per-launch timing of the GEMM kernel (CUDA events on the launching stream)
+static bool g_profile = false;
+struct TimedLaunch {
+    cudaEvent_t start, stop;
+    double flops;
+    double bytes;
+};
+static std::vector<TimedLaunch> g_timed;
+
 static constexpr int kSlots = 12;
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
@@ -383,8 +392,25 @@ static int run_fused(const FusedArgs &a) {
     }
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
     const int ctas = total_tiles < num_sms() ? total_tiles : num_sms();
+    TimedLaunch tl;
+    if (g_profile) {
+        cudaEventCreate(&tl.start);
+        cudaEventCreate(&tl.stop);
+        int n_rows = 0;
+        for (int i = 0; i < p.num_segs; ++i) n_rows += p.seg_rows[i];
+        tl.flops = 2.0 * a.M * (double)n_rows * a.K;
+        // algorithmic bytes of this launch: operands as stored + output (+ residual read)
+        const double wbytes = a.mode == GEMM_BF16 ? 2.0 * n_rows * a.K : (double)n_rows * a.K / 2 + (double)n_rows * a.K / 16;
+        const double xbytes = a.mode == GEMM_W4A4 ? (double)a.M * a.K / 2 + (double)a.M * a.K / 16 : 2.0 * a.M * a.K;
+        tl.bytes = wbytes + xbytes + 2.0 * a.M * p.n_out + (a.epi == EPI_RESIDUAL ? 2.0 * a.M * p.n_out : 0.0);
+        cudaEventRecord(tl.start, g_stream);
+    }
     if (launch_umma_gemm(a.mode, nb, p, ctas, g_stream) != cudaSuccess) return -1;
     ++g_launches;
+    if (g_profile) {
+        cudaEventRecord(tl.stop, g_stream);
+        g_timed.push_back(tl);
+    }
     return 0;
 }
 
@@ -648,6 +674,36 @@ extern "C" int glmasr_fp4_status(void) {
 }
 
 extern "C" long long glmasr_launch_count(void) { return g_launches; }
+
+extern "C" void glmasr_profile_enable(int on) {
+    g_profile = on != 0;
+    if (!g_profile) {
+        for (auto &t : g_timed) {
+            cudaEventDestroy(t.start);
+            cudaEventDestroy(t.stop);
+        }
+        g_timed.clear();
+    }
+}
+
+extern "C" int glmasr_profile_read(int max_entries, double *ms, double *flops, double *bytes) {
+    if (cudaStreamSynchronize(g_stream) != cudaSuccess) return -1;
+    int n = 0;
+    for (auto &t : g_timed) {
+        if (n < max_entries) {
+            float f = 0.0f;
+            cudaEventElapsedTime(&f, t.start, t.stop);
+            ms[n] = f;
+            flops[n] = t.flops;
+            bytes[n] = t.bytes;
+            ++n;
+        }
+        cudaEventDestroy(t.start);
+        cudaEventDestroy(t.stop);
+    }
+    g_timed.clear();
+    return n;
+}
 
 extern "C" void glmasr_set_stream(void *cuda_stream) { g_stream = (cudaStream_t)cuda_stream; }
 

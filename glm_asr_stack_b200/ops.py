@@ -268,6 +268,20 @@ def launch_count() -> int:
     return int(_lib.load().glmasr_launch_count())
 
 
+def profile_enable(on: bool):
+    _lib.load().glmasr_profile_enable(1 if on else 0)
+
+
+def profile_read(max_entries: int = 4096):
+    """[(ms, flops, bytes)] of the GEMM launches recorded since the last read."""
+    arr = (ctypes.c_double * max_entries)
+    ms, fl, by = arr(), arr(), arr()
+    n = _lib.load().glmasr_profile_read(max_entries, ms, fl, by)
+    if n < 0:
+        raise RuntimeError("glmasr_profile_read failed")
+    return [(ms[i], fl[i], by[i]) for i in range(n)]
+
+
 def set_stream(stream: Optional[torch.cuda.Stream]):
     _lib.load().glmasr_set_stream(ctypes.c_void_p(stream.cuda_stream) if stream is not None else None)
 

@@ -155,6 +155,12 @@ int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16
 int glmasr_fp4_status(void);
 /* Number of kernels this library has launched since load (for launch accounting). */
 long long glmasr_launch_count(void);
+/* Per-launch timing of the tensor-core GEMM kernel with CUDA events recorded on the launching
+ * stream.  While enabled, every GEMM launch is bracketed; glmasr_profile_read synchronises,
+ * returns up to max_entries (duration ms, algorithmic flops, algorithmic bytes) triples in
+ * launch order and clears the list.  Off by default. */
+void glmasr_profile_enable(int on);
+int glmasr_profile_read(int max_entries, double *ms, double *flops, double *bytes);
 /* Route all launches to the given cudaStream_t (NULL = legacy default stream). */
 void glmasr_set_stream(void *cuda_stream);
 /* Free every private workspace / cache (decoder_cleanup_all / lm_head_cleanup analogue). */

@@ -1,0 +1,94 @@
+"""ctypes access to the reference's OWN FP4 kernels, compiled unmodified from the reference
+sources into oracle/_ref/libglmasr_ref.so by oracle/Makefile (test infrastructure; needs a GPU).
+"""
+import ctypes
+import os
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from conftest import ROOT
+
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "libglmasr_ref.so")
+P = c_void_p
+
+
+def available() -> bool:
+    return os.path.exists(REF_SO)
+
+
+class RefLib:
+    def __init__(self):
+        self.lib = ctypes.CDLL(REF_SO, mode=ctypes.RTLD_LOCAL)
+        L = self.lib
+        L.fp4_dequant_to_bf16.argtypes = [P, P, P, c_float, c_int, c_int]
+        L.fp4_linear.argtypes = [P, P, P, P, P, P, P, c_float, P, P, c_int, c_int, c_int]
+        L.nvfp4_linear.argtypes = [P, P, P, P, P, P, c_float, c_float, P, P, c_int, c_int, c_int]
+        L.nvfp4_linear.restype = c_int
+        L.bf16_linear.argtypes = [P, P, P, P, P, c_int, c_int, c_int]
+        L.silu_mul_split_packed.argtypes = [P, P, c_int, c_int]
+        L.residual_add.argtypes = [P, P, P, c_int]
+        L.lm_head_argmax_batched.argtypes = [P, P, P, c_int, c_int, c_int, P]
+        for f in (L.fp4_dequant_to_bf16, L.fp4_linear, L.bf16_linear, L.silu_mul_split_packed, L.residual_add,
+                  L.lm_head_argmax_batched):
+            f.restype = None
+        # the reference's fp4_linear / bf16_linear take a cublasHandle_t
+        self.cublas = ctypes.CDLL("libcublas.so.12")
+        self.handle = c_void_p()
+        rc = self.cublas.cublasCreate_v2(ctypes.byref(self.handle))
+        assert rc == 0, f"cublasCreate failed: {rc}"
+
+    @staticmethod
+    def _p(t):
+        return None if t is None else c_void_p(t.data_ptr())
+
+    def fp4_dequant_to_bf16(self, packed, scales, g):
+        rows, cols = packed.shape[0], packed.shape[1] * 2
+        out = torch.empty((rows, cols), dtype=torch.bfloat16, device="cuda")
+        self.lib.fp4_dequant_to_bf16(self._p(out), self._p(packed), self._p(scales), g, rows, cols)
+        torch.cuda.synchronize()
+        return out
+
+    def fp4_linear(self, x, packed, scales, g, pre=None):
+        M, K = x.shape
+        N = packed.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        wscratch = torch.empty((N, K), dtype=torch.bfloat16, device="cuda")
+        pscratch = torch.empty((M, K), dtype=torch.bfloat16, device="cuda")
+        self.lib.fp4_linear(self.handle, self._p(out), self._p(wscratch), self._p(pscratch), self._p(x),
+                            self._p(packed), self._p(scales), g, self._p(pre), None, M, N, K)
+        torch.cuda.synchronize()
+        return out
+
+    def nvfp4_linear(self, x, packed, scales, input_scale, g, pre=None):
+        M, K = x.shape
+        N = packed.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        # the reference carves its temporaries from dequant_buf + N*K; give it ample room
+        mp = (M + 127) // 128 * 128
+        extra = mp * K + 4 * mp * (K // 16 + 4) + ((N + 127) // 128 * 128) * (K // 16 + 4) + 2 * mp * N + 4096
+        buf = torch.empty(N * K + (extra + 1) // 2 + 1024, dtype=torch.bfloat16, device="cuda")
+        rc = self.lib.nvfp4_linear(self.handle, self._p(out), self._p(buf), self._p(x), self._p(packed),
+                                   self._p(scales), input_scale, g, self._p(pre), None, M, N, K)
+        torch.cuda.synchronize()
+        return rc, out
+
+    def silu_mul_split_packed(self, packed):
+        M, N2 = packed.shape
+        out = torch.empty((M, N2 // 2), dtype=torch.bfloat16, device="cuda")
+        self.lib.silu_mul_split_packed(self._p(out), self._p(packed), M, N2 // 2)
+        torch.cuda.synchronize()
+        return out
+
+    def residual_add(self, a, b):
+        out = torch.empty_like(a)
+        self.lib.residual_add(self._p(out), self._p(a), self._p(b), a.numel())
+        torch.cuda.synchronize()
+        return out
+
+    def lm_head_argmax_batched(self, hidden, w):
+        rows, dim = hidden.shape
+        tokens = torch.empty(rows, dtype=torch.int32)
+        self.lib.lm_head_argmax_batched(self.handle, self._p(hidden), self._p(w), rows, dim, w.shape[0],
+                                        c_void_p(tokens.data_ptr()))
+        return tokens
