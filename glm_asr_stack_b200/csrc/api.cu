@@ -38,7 +38,7 @@ struct TimedLaunch {
 };
 static std::vector<TimedLaunch> g_timed;
 
-static constexpr int kSlots = 12;
+static constexpr int kSlots = 13;
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
 
@@ -93,6 +93,8 @@ enum Slot : int {
     WS_TOKENS = 4,    // lm_head arg-max result
     WS_TMP = 5,       // SIMT-path epilogue staging
     WS_L_QKV = 6, WS_L_H1 = 7, WS_L_ACT = 8, WS_L_IN = 9, WS_L_OUT = 10,
+    WS_WDEQ = 11,
+    WS_DBG = 12,      // cycle counters of timing experiments     // W4A16 large-M: dequantised bf16 weights
 };
 
 static int num_sms() {
@@ -102,6 +104,26 @@ static int num_sms() {
         GLMASR_CUDA_CHECK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
     }
     return g_num_sms;
+}
+
+// rows from which W4A16 dequantises each weight once instead of inside the GEMM
+static int w4a16_dequant_once_rows() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_W4A16_DEQUANT_ONCE_ROWS");
+        v = (e && e[0]) ? atoi(e) : 1024;
+        if (v < 1) v = 1;
+    }
+    return v;
+}
+
+static int debug_flags() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_DEBUG_FLAGS");
+        v = (e && e[0]) ? atoi(e) : 0;
+    }
+    return v;
 }
 
 static bool force_simt() {
@@ -187,9 +209,10 @@ struct FusedArgs {
     const __nv_bfloat16 *x;
     int ldx;
     const glmasr_fp4_weight *w;     // FP4 modes
-    const __nv_bfloat16 *w_bf16;    // BF16 mode (single weight)
-    int n_bf16;
+    const __nv_bfloat16 *w_bf16[kMaxSegments];   // BF16 mode: one bf16 [N_s, K] tensor per segment
+    int n_bf16[kMaxSegments];
     int num_w;
+    __nv_bfloat16 *weight_scratch;  // W4A16, large M: caller scratch for the dequantised weight (may be NULL)
     float input_scale;
     const __nv_bfloat16 *pre;
     __nv_bfloat16 *prequant_scratch;
@@ -205,7 +228,11 @@ static bool tensor_core_eligible(const FusedArgs &a) {
     if (force_simt()) return false;
     if (a.K % 256 != 0) return false;
     if (!aligned16(a.x) || !aligned16(a.out) || (a.ldx % 8) != 0) return false;
-    if (a.mode == GEMM_BF16) return aligned16(a.w_bf16);
+    if (a.mode == GEMM_BF16) {
+        for (int i = 0; i < a.num_w; ++i)
+            if (!aligned16(a.w_bf16[i])) return false;
+        return true;
+    }
     for (int i = 0; i < a.num_w; ++i) {
         if (a.w[i].w_scales == nullptr) return false;
         if (!aligned16(a.w[i].w_packed) || !aligned16(a.w[i].w_scales)) return false;
@@ -214,10 +241,9 @@ static bool tensor_core_eligible(const FusedArgs &a) {
 }
 
 static int total_out_cols(const FusedArgs &a) {
-    if (a.mode == GEMM_BF16) return a.n_bf16;
-    if (a.epi == EPI_SILU_GATE) return a.w[0].N;
+    if (a.epi == EPI_SILU_GATE) return a.mode == GEMM_BF16 ? a.n_bf16[0] : a.w[0].N;
     int n = 0;
-    for (int i = 0; i < a.num_w; ++i) n += a.w[i].N;
+    for (int i = 0; i < a.num_w; ++i) n += a.mode == GEMM_BF16 ? a.n_bf16[i] : a.w[i].N;
     return n;
 }
 
@@ -242,15 +268,15 @@ static int run_simt(const FusedArgs &a) {
     }
     __nv_bfloat16 *dst = a.out;
     int ldo = a.ldo;
+    const int n0 = a.mode == GEMM_BF16 ? a.n_bf16[0] : a.w[0].N;
     if (a.epi == EPI_SILU_GATE) {
-        dst = (__nv_bfloat16 *)workspace_slot(WS_TMP, (size_t)a.M * 2 * a.w[0].N * 2);
-        ldo = 2 * a.w[0].N;
+        dst = (__nv_bfloat16 *)workspace_slot(WS_TMP, (size_t)a.M * 2 * n0 * 2);
+        ldo = 2 * n0;
     } else if (a.epi == EPI_RESIDUAL) {
         dst = (__nv_bfloat16 *)workspace_slot(WS_TMP, (size_t)a.M * a.ldo * 2);
     }
     int col = 0;
-    const int nw = a.mode == GEMM_BF16 ? 1 : a.num_w;
-    for (int i = 0; i < nw; ++i) {
+    for (int i = 0; i < a.num_w; ++i) {
         SimtGemmArgs g;
         memset(&g, 0, sizeof(g));
         g.mode = a.mode == GEMM_W4A4 ? 0 : (a.mode == GEMM_W4A16 ? 1 : 2);
@@ -265,8 +291,8 @@ static int run_simt(const FusedArgs &a) {
         g.col0 = col;
         g.bias = a.bias;
         if (a.mode == GEMM_BF16) {
-            g.w_bf16 = a.w_bf16;
-            g.N = a.n_bf16;
+            g.w_bf16 = a.w_bf16[i];
+            g.N = a.n_bf16[i];
             g.alpha = 1.0f;
         } else {
             g.w_packed = a.w[i].w_packed;
@@ -279,8 +305,8 @@ static int run_simt(const FusedArgs &a) {
         col += g.N;
     }
     if (a.epi == EPI_SILU_GATE) {
-        GLMASR_CHECK(a.ldo == a.w[0].N, "SIMT SiLU path needs a dense output");
-        launch_silu_split(a.out, dst, a.M, a.w[0].N, g_stream);
+        GLMASR_CHECK(a.ldo == n0, "SIMT SiLU path needs a dense output");
+        launch_silu_split(a.out, dst, a.M, n0, g_stream);
         ++g_launches;
     } else if (a.epi == EPI_RESIDUAL) {
         GLMASR_CHECK(a.ldo == total_out_cols(a), "SIMT residual path needs a dense output");
@@ -302,6 +328,29 @@ static int run_fused(const FusedArgs &a) {
     }
     if (!tensor_core_eligible(a)) return run_simt(a);
 
+    // W4A16 with many rows: the in-kernel dequant (repeated for every 128-row tile) becomes the
+    // bottleneck, so do what the reference does -- dequantise each weight once to bf16
+    // (Infer-engine/cuda/kernels.cu:1316) -- and run the bf16 GEMM on the result.
+    if (a.mode == GEMM_W4A16 && a.M >= w4a16_dequant_once_rows()) {
+        size_t elems = 0;
+        for (int i = 0; i < a.num_w; ++i) elems += (size_t)a.w[i].N * a.K;
+        __nv_bfloat16 *wd = (a.weight_scratch != nullptr && a.num_w == 1)
+                                ? a.weight_scratch
+                                : (__nv_bfloat16 *)workspace_slot(WS_WDEQ, elems * 2);
+        FusedArgs b = a;
+        b.mode = GEMM_BF16;
+        size_t off = 0;
+        for (int i = 0; i < a.num_w; ++i) {
+            launch_dequant(wd + off, a.w[i].w_packed, a.w[i].w_scales, a.w[i].w_global_scale, a.w[i].N, a.K, g_stream);
+            ++g_launches;
+            b.w_bf16[i] = wd + off;
+            b.n_bf16[i] = a.w[i].N;
+            off += (size_t)a.w[i].N * a.K;
+        }
+        b.w = nullptr;
+        return run_fused(b);
+    }
+
     if (!g_umma_ready) {
         GLMASR_CUDA_CHECK(umma_gemm_init());
         g_umma_ready = true;
@@ -317,6 +366,8 @@ static int run_fused(const FusedArgs &a) {
     p.bias = a.bias;
     p.epi = a.epi;
     p.status = device_status_word();
+    p.debug = debug_flags();
+    p.dbg_cycles = (p.debug & 64) ? (unsigned long long *)workspace_slot(WS_DBG, 148 * 16 * 8 * 4) : nullptr;
     p.num_m_tiles = (a.M + 127) / 128;
     p.n_out = total_out_cols(a);
 
@@ -351,14 +402,16 @@ static int run_fused(const FusedArgs &a) {
     // operand B
     int subtiles = 0;
     if (a.mode == GEMM_BF16) {
-        p.num_segs = 1;
-        p.seg_rows[0] = a.n_bf16;
-        p.seg_subtiles[0] = (a.n_bf16 + 127) / 128;
-        p.alpha[0] = 1.0f;
-        if (!make_tmap(&p.tm_b[0], a.w_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K, (uint64_t)a.n_bf16,
-                       (uint64_t)a.K * 2, 64, 128, true))
-            return -1;
-        subtiles = p.seg_subtiles[0];
+        p.num_segs = a.num_w;
+        for (int i = 0; i < a.num_w; ++i) {
+            p.seg_rows[i] = a.n_bf16[i];
+            p.seg_subtiles[i] = (a.n_bf16[i] + 127) / 128;
+            subtiles += p.seg_subtiles[i];
+            p.alpha[i] = 1.0f;
+            if (!make_tmap(&p.tm_b[i], a.w_bf16[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.K,
+                           (uint64_t)a.n_bf16[i], (uint64_t)a.K * 2, 64, 128, true))
+                return -1;
+        }
     } else {
         p.num_segs = a.num_w;
         for (int i = 0; i < a.num_w; ++i) {
@@ -388,6 +441,7 @@ static int run_fused(const FusedArgs &a) {
     } else {
         const int tiles2 = p.num_m_tiles * ((subtiles + 1) / 2);
         nb = (subtiles >= 2 && tiles2 >= num_sms()) ? 2 : 1;
+        if (getenv("GLMASR_FORCE_NB") != nullptr) nb = atoi(getenv("GLMASR_FORCE_NB")) == 1 ? 1 : 2;   // experiments
         p.num_n_tiles = (subtiles + nb - 1) / nb;
     }
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
@@ -432,7 +486,6 @@ extern "C" void fp4_linear(void *handle, uint16_t *out, uint16_t *weight_scratch
                            const uint16_t *x, const uint8_t *w_packed, const uint8_t *w_scales, float w_global_scale,
                            const uint16_t *pre_quant_scale, const uint16_t *bias, int M, int N, int K) {
     (void)handle;
-    (void)weight_scratch;
     if (M <= 0 || N <= 0 || K <= 0) return;   // the reference launches empty grids here
     glmasr_fp4_weight w = {w_packed, w_scales, w_global_scale, N};
     FusedArgs a;
@@ -446,6 +499,7 @@ extern "C" void fp4_linear(void *handle, uint16_t *out, uint16_t *weight_scratch
     a.num_w = 1;
     a.pre = (const __nv_bfloat16 *)pre_quant_scale;
     a.prequant_scratch = (__nv_bfloat16 *)prequant_scratch;
+    a.weight_scratch = (__nv_bfloat16 *)weight_scratch;
     a.epi = EPI_STORE;
     a.bias = (const __nv_bfloat16 *)bias;
     a.M = M;
@@ -495,8 +549,8 @@ extern "C" void bf16_linear(void *handle, uint16_t *out, const uint16_t *x, cons
     a.ldo = N;
     a.x = (const __nv_bfloat16 *)x;
     a.ldx = K;
-    a.w_bf16 = (const __nv_bfloat16 *)w;
-    a.n_bf16 = N;
+    a.w_bf16[0] = (const __nv_bfloat16 *)w;
+    a.n_bf16[0] = N;
     a.num_w = 1;
     a.epi = EPI_STORE;
     a.bias = (const __nv_bfloat16 *)bias;
@@ -674,6 +728,15 @@ extern "C" int glmasr_fp4_status(void) {
 }
 
 extern "C" long long glmasr_launch_count(void) { return g_launches; }
+
+// timing experiments: copy the per-CTA cycle counters of the last instrumented GEMM launch
+extern "C" int glmasr_debug_cycles(unsigned long long *host_out, int max_ctas) {
+    if (g_ws[WS_DBG] == nullptr) return 0;
+    cudaStreamSynchronize(g_stream);
+    const int n = max_ctas < 148 ? max_ctas : 148;
+    if (cudaMemcpy(host_out, g_ws[WS_DBG], (size_t)n * 16 * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return n;
+}
 
 extern "C" void glmasr_profile_enable(int on) {
     g_profile = on != 0;

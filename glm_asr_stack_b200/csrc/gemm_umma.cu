@@ -6,9 +6,10 @@
 //   warp 0      TMA producer: activation tile, weight tile(s), and (W4A4) the 128x4-tiled scale
 //               chunks, into a ring of shared-memory stages guarded by full/empty mbarriers
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits stages
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator, apply the per-tensor scale and the
-//               fused SiLU-gate / residual, 16-byte bf16 stores
-//   warps 6+    (W4A16 only) dequantise packed e2m1 weights + e4m3 scales from a raw ring into
+//   warps 2-9   epilogue: tcgen05.ld the fp32 accumulator (two warps per TMEM lane quadrant, half
+//               the columns each), apply the per-tensor scale and the fused SiLU-gate / residual,
+//               16-byte bf16 stores
+//   warps 10+   (W4A16 only) dequantise packed e2m1 weights + e4m3 scales from a raw ring into
 //               the 128B-swizzled bf16 operand tile the MMA reads
 //
 // Tokens sit on the 128 TMEM lanes (operand A), weight rows on the accumulator columns
@@ -53,11 +54,23 @@ struct Cfg {
     static constexpr int RAW_STAGE_BYTES = MODE == GEMM_W4A16 ? NB * RAW_SUB : 0;
     static constexpr int STAGES = MODE == GEMM_W4A16 ? (NB == 2 ? 3 : 4) : (NB == 2 ? 4 : 6);
     static constexpr int NUM_ACC = (MODE == GEMM_W4A4 && NB == 2) ? 1 : 2;
+    // epilogue warps: one or two per TMEM lane quadrant (each then takes half the columns); the
+    // W4A16 variant keeps four because its dequant warps need the register budget
+    static constexpr int EPI_WARPS = MODE == GEMM_W4A16 ? 4 : 8;
+    static constexpr int FIRST_DQ_WARP = 2 + EPI_WARPS;
     static constexpr int DQ_WARPS = MODE == GEMM_W4A16 ? 4 * NB : 0;
-    static constexpr int THREADS = (6 + DQ_WARPS) * 32;
-    static constexpr int SFA_COL = NUM_ACC * BN;          // tensor-memory column of the A scales
+    static constexpr int THREADS = (2 + EPI_WARPS + DQ_WARPS) * 32;
+    // With a single accumulator the epilogue first drains its columns into registers and hands the
+    // accumulator back to the MMA warp, then converts and stores while the next tile is computed.
+    static constexpr bool EARLY_RELEASE = NUM_ACC == 1;
+    // scale factors of one stage: 16 columns for A, 16 per weight sub-tile for B; two such sets are
+    // alternated stage by stage so that the copy for the next stage does not wait for the MMAs
+    // still reading the current one
+    static constexpr int SF_SET_COLS = 16 + 16 * NB;
+    static constexpr int SF_SETS = 2;
+    static constexpr int SFA_COL = NUM_ACC * BN;          // tensor-memory column of the A scales (set 0)
     static constexpr int SFB_COL = SFA_COL + 16;
-    static constexpr int TMEM_NEEDED = NUM_ACC * BN + (MODE == GEMM_W4A4 ? 16 + 16 * NB : 0);
+    static constexpr int TMEM_NEEDED = NUM_ACC * BN + (MODE == GEMM_W4A4 ? SF_SETS * SF_SET_COLS : 0);
     static constexpr int TMEM_COLS = next_pow2_cols(TMEM_NEEDED);
     static constexpr int BAR_BYTES = 1024;
     static constexpr int SMEM_BYTES = 1024 + BAR_BYTES + STAGES * STAGE_BYTES + RAW_STAGES * RAW_STAGE_BYTES;
@@ -148,9 +161,19 @@ __device__ __forceinline__ void store_row_chunk(__nv_bfloat16 *dst, const float 
             const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
             w[i] = *reinterpret_cast<const uint32_t *>(&b);
         }
-        uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+        if (((uintptr_t)dst & 31) == 0) {
+            // 32-byte stores: every store fills a whole 32-byte L2 sector
 #pragma unroll
-        for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            for (int i = 0; i < 2; ++i)
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * i),
+                             "r"(w[8 * i]), "r"(w[8 * i + 1]), "r"(w[8 * i + 2]), "r"(w[8 * i + 3]), "r"(w[8 * i + 4]),
+                             "r"(w[8 * i + 5]), "r"(w[8 * i + 6]), "r"(w[8 * i + 7])
+                             : "memory");
+        } else {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
@@ -182,6 +205,10 @@ __device__ __forceinline__ float silu_gate(float g, float u) {
     const float sig = __fdiv_rn(1.0f, 1.0f + expf(-g));
     return (g * sig) * u;
 }
+
+// cycle accounting for timing experiments (debug & 64): T0 opens an interval, ACC closes it into a counter
+#define DBG_T0() long long _t0 = dbg ? clock64() : 0
+#define DBG_ACC(slot) do { if (dbg) { long long _t1 = clock64(); dbg_acc[slot] += (unsigned long long)(_t1 - _t0); _t0 = _t1; } } while (0)
 
 // ---------------------------------------------------------------------------------------------
 template <int MODE, int NB>
@@ -216,7 +243,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
         }
         for (int a = 0; a < C::NUM_ACC; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), C::EPI_WARPS);
         }
         for (int r = 0; r < C::RAW_STAGES; ++r) {
             mbar_init(rfull_bar(r), 1);
@@ -238,143 +265,185 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
 
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
     const int nkb = p.num_k_blocks;
+    const bool dbg = (p.debug & 64) != 0 && p.dbg_cycles != nullptr;
+    unsigned long long dbg_acc[4] = {0, 0, 0, 0};
 
     if (warp == 0) {
         // ================================ TMA producer ================================
-        if (lane == 0) {
-            uint32_t it = 0, raw_it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int m_tile = tile % p.num_m_tiles;
-                const int n_tile = tile / p.num_m_tiles;
-                SubTile st[NB];
+        // The whole warp walks the loop (uniform control flow and addresses); one elected lane issues.
+        const bool leader = elect_one();
+        uint32_t it = 0, raw_it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            const int m_tile = tile % p.num_m_tiles;
+            const int n_tile = tile / p.num_m_tiles;
+            SubTile st[NB];
 #pragma unroll
-                for (int h = 0; h < NB; ++h) st[h] = resolve_subtile(p, n_tile, h, NB);
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if constexpr (MODE == GEMM_W4A16) {
-                        if ((kb & 3) == 0) {
-                            const int r = raw_it & 1;
-                            const uint32_t rph = (raw_it >> 1) & 1u;
-                            if (!mbar_wait(rempty_bar(r), rph ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+            for (int h = 0; h < NB; ++h) st[h] = resolve_subtile(p, n_tile, h, NB);
+            const uint8_t *sfa_src = nullptr;
+            const uint8_t *sfb_src[NB];
+            if constexpr (MODE == GEMM_W4A4) {
+                sfa_src = p.sfa + (size_t)m_tile * p.sf_k_chunks * C::SF_CHUNK;
+#pragma unroll
+                for (int h = 0; h < NB; ++h) {
+                    // a sub-tile past the end of its tensor reads tile 0 (any valid memory: its columns are never stored)
+                    const int rt = st[h].ncols > 0 ? (st[h].row0 >> 7) : 0;
+                    sfb_src[h] = p.sfb[st[h].seg] + (size_t)rt * p.sf_k_chunks * C::SF_CHUNK;
+                }
+            }
+            for (int kb = 0; kb < nkb; ++kb) {
+                if constexpr (MODE == GEMM_W4A16) {
+                    if ((kb & 3) == 0) {
+                        const int r = raw_it & 1;
+                        const uint32_t rph = (raw_it >> 1) & 1u;
+                        if (!mbar_wait_warp(rempty_bar(r), rph ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                        const uint32_t rb = raw_tiles + (uint32_t)r * C::RAW_STAGE_BYTES;
+                        if (leader) {
                             mbar_expect_tx(rfull_bar(r), C::RAW_STAGE_BYTES);
-                            const uint32_t rb = raw_tiles + (uint32_t)r * C::RAW_STAGE_BYTES;
 #pragma unroll
                             for (int h = 0; h < NB; ++h) {
                                 tma_load_2d(rb + h * C::RAW_SUB, &p.tm_b[st[h].seg], rfull_bar(r), (kb >> 2) * 128, st[h].row0);
                                 tma_load_2d(rb + h * C::RAW_SUB + C::SUB_BYTES, &p.tm_bs[st[h].seg], rfull_bar(r),
                                             (kb >> 2) * 16, st[h].row0);
                             }
-                            ++raw_it;
                         }
+                        ++raw_it;
                     }
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), C::TX_BYTES);
-                    const uint32_t sb = stage_base(s);
-                    // innermost coordinate in elements of the tensor map: bytes for packed e2m1, bf16 otherwise
-                    const int kx = MODE == GEMM_W4A4 ? kb * 128 : kb * 64;
+                }
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1u;
+                DBG_T0();
+                if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                DBG_ACC(0);
+                if ((p.debug & 8) && it >= (uint32_t)C::STAGES) {   // experiment: no memory traffic
+                    if (leader) mbar_arrive(full_bar(s));
+                    ++it;
+                    continue;
+                }
+                const uint32_t sb = stage_base(s);
+                // innermost coordinate in elements of the tensor map: bytes for packed e2m1, bf16 otherwise
+                const int kx = MODE == GEMM_W4A4 ? kb * 128 : kb * 64;
+                if (leader) {
+                    mbar_expect_tx(full_bar(s), (p.debug & 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
                     tma_load_2d(sb, &p.tm_a, full_bar(s), kx, m_tile * 128);
                     if constexpr (MODE != GEMM_W4A16) {
 #pragma unroll
                         for (int h = 0; h < NB; ++h)
                             tma_load_2d(sb + C::A_BYTES + h * C::SUB_BYTES, &p.tm_b[st[h].seg], full_bar(s), kx, st[h].row0);
                     }
-                    if constexpr (MODE == GEMM_W4A4) {
+                    if (MODE == GEMM_W4A4 && !(p.debug & 2)) {
                         const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
-                        bulk_load_1d(sf, p.sfa + ((size_t)m_tile * p.sf_k_chunks + (size_t)kb * 4) * C::SF_CHUNK, C::SF_TILE,
-                                     full_bar(s));
+                        bulk_load_1d(sf, sfa_src + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
 #pragma unroll
-                        for (int h = 0; h < NB; ++h) {
-                            // a sub-tile past the end of its tensor reads tile 0 (any valid memory: its columns are never stored)
-                            const int rt = st[h].ncols > 0 ? (st[h].row0 >> 7) : 0;
-                            bulk_load_1d(sf + (1 + h) * C::SF_TILE,
-                                         p.sfb[st[h].seg] + ((size_t)rt * p.sf_k_chunks + (size_t)kb * 4) * C::SF_CHUNK,
-                                         C::SF_TILE, full_bar(s));
-                        }
+                        for (int h = 0; h < NB; ++h)
+                            bulk_load_1d(sf + (1 + h) * C::SF_TILE, sfb_src[h] + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
                     }
-                    ++it;
                 }
+                ++it;
+                DBG_ACC(1);
             }
         }
+        if (dbg && leader) { p.dbg_cycles[blockIdx.x * 16 + 0] = dbg_acc[0]; p.dbg_cycles[blockIdx.x * 16 + 1] = dbg_acc[1]; }
     } else if (warp == 1) {
         // ================================ MMA issuer ==================================
-        if (lane == 0) {
-            constexpr uint32_t idesc = MODE == GEMM_W4A4 ? idesc_nvfp4(128, C::BN) : idesc_bf16(128, C::BN);
-            uint32_t it = 0, acc_it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int acc = acc_it % C::NUM_ACC;
-                const uint32_t aph = (acc_it / C::NUM_ACC) & 1u;
-                if (!mbar_wait(tempty_bar(acc), aph ^ 1u, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
+        // Warp-uniform loop; the elected lane issues tcgen05.cp / tcgen05.mma / tcgen05.commit.
+        const bool leader = elect_one();
+        constexpr uint32_t idesc = MODE == GEMM_W4A4 ? idesc_nvfp4(128, C::BN) : idesc_bf16(128, C::BN);
+        uint32_t it = 0, acc_it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            const int acc = acc_it % C::NUM_ACC;
+            const uint32_t aph = (acc_it / C::NUM_ACC) & 1u;
+            DBG_T0();
+            if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1u, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
+            DBG_ACC(0);
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C::BN);
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1u;
+                if (!mbar_wait_warp(full_bar(s), ph, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
+                DBG_ACC(1);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C::BN);
-                for (int kb = 0; kb < nkb; ++kb) {
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1u;
-                    if (!mbar_wait(full_bar(s), ph, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_addr = stage_base(s);
-                    const uint32_t b_addr = a_addr + C::A_BYTES;
-                    if constexpr (MODE == GEMM_W4A4) {
-                        const uint32_t sf = a_addr + C::A_BYTES + C::B_BYTES;
+                const uint32_t a_addr = stage_base(s);
+                const uint32_t b_addr = a_addr + C::A_BYTES;
+                const uint32_t sf_set = ((p.debug & 32) ? 0u : (it & 1u)) * C::SF_SET_COLS;
+                const uint32_t sfa_t = tmem_base + C::SFA_COL + sf_set;
+                const uint32_t sfb_t = tmem_base + C::SFB_COL + sf_set;
+                // descriptors differ from stage to stage only in their 14-bit start-address field
+                const uint64_t adesc0 = smem_desc_sw128(a_addr);
+                const uint64_t bdesc0 = smem_desc_sw128(b_addr);
+                if (leader) {
+                    if (MODE == GEMM_W4A4 && !((p.debug & 1) && it > 1)) {
+                        const uint64_t sfdesc0 = smem_desc_sf_chunk(a_addr + C::A_BYTES + C::B_BYTES);
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
-                            tmem_cp_32x128b_warpx4(tmem_base + C::SFA_COL + 4 * c, smem_desc_sf_chunk(sf + c * C::SF_CHUNK));
+                            tmem_cp_32x128b_warpx4(sfa_t + 4 * c, sfdesc0 + (uint64_t)((c * C::SF_CHUNK) >> 4));
 #pragma unroll
                         for (int h = 0; h < NB; ++h)
 #pragma unroll
                             for (int c = 0; c < 4; ++c)
-                                tmem_cp_32x128b_warpx4(tmem_base + C::SFB_COL + c * 4 * NB + 4 * h,
-                                                       smem_desc_sf_chunk(sf + (1 + h) * C::SF_TILE + c * C::SF_CHUNK));
+                                tmem_cp_32x128b_warpx4(sfb_t + c * 4 * NB + 4 * h,
+                                                       sfdesc0 + (uint64_t)(((1 + h) * C::SF_TILE + c * C::SF_CHUNK) >> 4));
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const uint64_t adesc = smem_desc_sw128(a_addr + k * 32);
-                        const uint64_t bdesc = smem_desc_sw128(b_addr + k * 32);
+                        if ((p.debug & 16) && k > 0) break;   // experiment: a quarter of the MMAs
+                        const uint64_t adesc = adesc0 + (uint64_t)((k * 32) >> 4);
+                        const uint64_t bdesc = bdesc0 + (uint64_t)((k * 32) >> 4);
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
                         if constexpr (MODE == GEMM_W4A4)
-                            umma_nvfp4(d_tmem, adesc, bdesc, idesc, accumulate, tmem_base + C::SFA_COL + 4 * k,
-                                       tmem_base + C::SFB_COL + 4 * NB * k);
+                            umma_nvfp4(d_tmem, adesc, bdesc, idesc, accumulate, sfa_t + 4 * k, sfb_t + 4 * NB * k);
                         else
                             umma_bf16(d_tmem, adesc, bdesc, idesc, accumulate);
                     }
                     umma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
-                    ++it;
                 }
-                if (!ok) break;
-                umma_commit(tfull_bar(acc));     // accumulator complete
-                ++acc_it;
+                ++it;
+                DBG_ACC(2);
             }
+            if (!ok) break;
+            if (leader) umma_commit(tfull_bar(acc));     // accumulator complete
+            ++acc_it;
         }
-    } else if (warp < 6) {
+        if (dbg && leader) for (int i = 0; i < 3; ++i) p.dbg_cycles[blockIdx.x * 16 + 4 + i] = dbg_acc[i];
+    } else if (warp < C::FIRST_DQ_WARP) {
         // ================================ epilogue =====================================
         const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;        // which half of the accumulator columns
+        constexpr int HC = C::BN / (C::EPI_WARPS / 4);   // columns per warp
+        constexpr int NCH = HC / 32;             // 32-column groups per warp
         uint32_t acc_it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int m_tile = tile % p.num_m_tiles;
             const int n_tile = tile / p.num_m_tiles;
             const int acc = acc_it % C::NUM_ACC;
             const uint32_t aph = (acc_it / C::NUM_ACC) & 1u;
+            DBG_T0();
             bool ok = mbar_wait(tfull_bar(acc), aph, abort_word, ST_TIMEOUT_EPILOGUE);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
+            DBG_ACC(0);
             tc_fence_after();
             const int row = m_tile * 128 + quad * 32 + lane;
             const bool row_ok = row < p.M;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::BN);
             __nv_bfloat16 *out_row = p.out + (size_t)row * p.ldo;
+            auto release_acc = [&]() {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                DBG_ACC(1);
+            };
 
             if (p.epi == EPI_SILU_GATE) {
                 if constexpr (NB == 2) {
+                    // gate columns [GC*half, +GC) pair with up columns [128 + GC*half, +GC)
+                    constexpr int GC = 128 / (C::EPI_WARPS / 4);
+                    constexpr int GCH = GC / 32;
                     const SubTile sg = resolve_subtile(p, n_tile, 0, NB);
                     const float ag = p.alpha[0], au = p.alpha[1];
-#pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint32_t rg[32], ru[32];
-                        tmem_ld_x32(t_row + ch * 32, rg);
-                        tmem_ld_x32(t_row + 128 + ch * 32, ru);
-                        tmem_ld_wait();
+                    auto finish_gate = [&](const uint32_t (&rg)[32], const uint32_t (&ru)[32], int ch) {
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -382,51 +451,89 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                             const float u = bf16_round(__uint_as_float(ru[i]) * au);
                             v[i] = silu_gate(g, u);
                         }
-                        const int nvalid = sg.ncols - ch * 32;
-                        if (row_ok && nvalid > 0) store_row_chunk(out_row + sg.col0 + ch * 32, v, nvalid);
+                        const int c0 = half * GC + ch * 32;
+                        const int nvalid = sg.ncols - c0;
+                        if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
+                    };
+                    if constexpr (C::EARLY_RELEASE) {
+                        uint32_t rg[GCH][32], ru[GCH][32];
+#pragma unroll
+                        for (int ch = 0; ch < GCH; ++ch) {
+                            tmem_ld_x32(t_row + half * GC + ch * 32, rg[ch]);
+                            tmem_ld_x32(t_row + 128 + half * GC + ch * 32, ru[ch]);
+                        }
+                        tmem_ld_wait();
+                        release_acc();
+#pragma unroll
+                        for (int ch = 0; ch < GCH; ++ch) finish_gate(rg[ch], ru[ch], ch);
+                    } else {
+#pragma unroll 1
+                        for (int ch = 0; ch < GCH; ++ch) {
+                            uint32_t rg[32], ru[32];
+                            tmem_ld_x32(t_row + half * GC + ch * 32, rg);
+                            tmem_ld_x32(t_row + 128 + half * GC + ch * 32, ru);
+                            tmem_ld_wait();
+                            finish_gate(rg, ru, ch);
+                        }
+                        release_acc();
                     }
                 }
             } else {
+                // plain / bias / residual: this warp's columns [half*HC, +HC) of the tile
+                const int sub = (half * HC) / 128;            // weight sub-tile the columns belong to
+                const int sub_c0 = (half * HC) % 128;         // first column inside that sub-tile
+                const SubTile st = resolve_subtile(p, n_tile, sub, NB);
+                const float alpha = p.alpha[st.seg];
+                auto finish_chunk = [&](const uint32_t (&r)[32], int ch) {
+                    const int c0 = sub_c0 + ch * 32;
+                    const int nvalid = st.ncols - c0;
+                    if (!(row_ok && nvalid > 0)) return;
+                    const int col = st.col0 + c0;
+                    float v[32];
 #pragma unroll
-                for (int h = 0; h < NB; ++h) {
-                    const SubTile st = resolve_subtile(p, n_tile, h, NB);
-                    const float alpha = p.alpha[st.seg];
-#pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint32_t r[32];
-                        tmem_ld_x32(t_row + h * 128 + ch * 32, r);
-                        tmem_ld_wait();
-                        const int nvalid = st.ncols - ch * 32;
-                        if (!(row_ok && nvalid > 0)) continue;
-                        const int col = st.col0 + ch * 32;
-                        float v[32];
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+                    if (p.bias != nullptr) {
+                        float b[32];
+                        load_row_chunk(p.bias + col, b, nvalid);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-                        if (p.bias != nullptr) {
-                            float b[32];
-                            load_row_chunk(p.bias + col, b, nvalid);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] += b[i];
-                        }
-                        if (p.epi == EPI_RESIDUAL) {
-                            float res[32];
-                            load_row_chunk(p.residual + (size_t)row * p.ldo + col, res, nvalid);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
-                        }
-                        store_row_chunk(out_row + col, v, nvalid);
+                        for (int i = 0; i < 32; ++i) v[i] += b[i];
                     }
+                    if (p.epi == EPI_RESIDUAL) {
+                        float res[32];
+                        load_row_chunk(p.residual + (size_t)row * p.ldo + col, res, nvalid);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
+                    }
+                    if (!(p.debug & 4)) store_row_chunk(out_row + col, v, nvalid);
+                };
+                if constexpr (C::EARLY_RELEASE) {
+                    uint32_t r[NCH][32];
+#pragma unroll
+                    for (int ch = 0; ch < NCH; ++ch) tmem_ld_x32(t_row + half * HC + ch * 32, r[ch]);
+                    tmem_ld_wait();
+                    release_acc();
+#pragma unroll
+                    for (int ch = 0; ch < NCH; ++ch) finish_chunk(r[ch], ch);
+                } else {
+#pragma unroll 1
+                    for (int ch = 0; ch < NCH; ++ch) {
+                        uint32_t r[32];
+                        tmem_ld_x32(t_row + half * HC + ch * 32, r);
+                        tmem_ld_wait();
+                        finish_chunk(r, ch);
+                    }
+                    release_acc();
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            DBG_ACC(2);
             ++acc_it;
         }
+        if (dbg && warp == 2 && lane == 0)
+            for (int i = 0; i < 3; ++i) p.dbg_cycles[blockIdx.x * 16 + 8 + i] = dbg_acc[i];
     } else {
         // ================================ W4A16 dequant warps ============================
         if constexpr (MODE == GEMM_W4A16) {
-            const int dq = warp - 6;
+            const int dq = warp - C::FIRST_DQ_WARP;
             const int h = dq >> 2;                       // weight sub-tile
             const int r = (dq & 3) * 32 + lane;          // row within the sub-tile
             const uint32_t sw = (uint32_t)(r & 7);
@@ -519,7 +626,7 @@ cudaError_t launch_umma_gemm(int mode, int nb, const GemmParams &p, int num_ctas
 
 int umma_gemm_threads(int mode, int nb) {
     if (mode == GEMM_W4A16) return nb == 2 ? Cfg<GEMM_W4A16, 2>::THREADS : Cfg<GEMM_W4A16, 1>::THREADS;
-    return 192;
+    return Cfg<GEMM_W4A4, 2>::THREADS;
 }
 
 int umma_gemm_smem_bytes(int mode, int nb) {

@@ -44,6 +44,8 @@ struct alignas(64) GemmParams {
     int num_k_blocks;                   // K steps of 128 operand bytes per row (W4A4: 256 elements, else 64)
     int sf_k_chunks;                    // W4A4: 512-byte scale chunks per 128-row tile along K (= ceil(K/64))
     int *status;
+    int debug;                          // timing experiments only (GLMASR_DEBUG_FLAGS); 0 in normal use
+    unsigned long long *dbg_cycles;     // debug & 64: per-CTA cycle counters [gridDim.x][16]
 };
 
 // nb = 128-row weight sub-tiles per CTA tile (1 or 2).  Returns cudaSuccess or the launch error.

@@ -66,6 +66,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Same, for a whole converged warp: every lane polls, the verdict is made warp-uniform so that
+// the code after it (and the values it computes) stays uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_word, int code) {
+    const bool ok = mbar_wait(bar, parity, abort_word, code);
+    return __all_sync(0xFFFFFFFFu, ok);
+}
+
+// One lane of a converged warp (always the same one).  Single-instruction work such as a TMA
+// issue or a tcgen05.mma is guarded by this while the surrounding address arithmetic runs
+// warp-uniformly, which lets it live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- proxy fences -----------------------------------------------------------------------
 // Make generic-proxy writes to shared memory visible to the async proxy (UMMA / TMA reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -38,8 +38,10 @@ void fp4_dequant_to_bf16(uint16_t *out, const uint8_t *packed_w, const uint8_t *
 
 /* Infer-engine/include/cuda_kernels.h:80-89, Infer-engine/cuda/kernels.cu:1297-1318.
  * W4A16: out[M,N] = bf16(x[M,K] * dequant(W)[N,K]^T (+ bias)), fp32 accumulation.
- * The reference materialises the bf16 weight in weight_scratch on every call; this
- * implementation dequantises inside the GEMM and leaves weight_scratch untouched.
+ * The reference materialises the bf16 weight in weight_scratch on every call.  Here, below
+ * 1024 rows (decode), the weight is dequantised inside the GEMM and weight_scratch is left
+ * untouched; from 1024 rows (prefill) it is dequantised once per call into weight_scratch
+ * (a private workspace if NULL), exactly like the reference, and a bf16 GEMM follows.
  * prequant_scratch ([M,K] bf16) is written only when pre_quant_scale != NULL, as in the
  * reference.  handle is ignored (no cuBLAS). */
 void fp4_linear(void *handle, uint16_t *out, uint16_t *weight_scratch, uint16_t *prequant_scratch,

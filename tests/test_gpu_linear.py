@@ -207,10 +207,21 @@ def test_full_size_prefill_properties(ops):
     isc = synth.default_input_scale(x)
     for mode in (ops.MODE_W4A16, ops.MODE_W4A4):
         big = ops.fp4_linear_fused(mode, x, [q, k, v], input_scale=isc)
-        small = ops.fp4_linear_fused(mode, x[:130].contiguous(), [q, k, v], input_scale=isc)
-        assert torch.equal(big[:130], small)
+        # 1100 rows: same code route as the big launch (W4A16 dequantises once from 1024 rows up)
+        small = ops.fp4_linear_fused(mode, x[:1100].contiguous(), [q, k, v], input_scale=isc)
+        assert torch.equal(big[:1100], small)
+        # 130 rows: W4A16 dequantises inside the GEMM there (weights not rounded to bf16 with the
+        # per-tensor scale folded in), so only bf16-rounding-level agreement is expected
+        tiny = ops.fp4_linear_fused(mode, x[:130].contiguous(), [q, k, v], input_scale=isc)
+        if mode == ops.MODE_W4A4:
+            assert torch.equal(big[:130], tiny)
+        else:
+            assert o.rel_err(bits_of(big[:130]), bits_of(tiny)) <= REL_TOL_TIGHT
         tail = ops.fp4_linear_fused(mode, x[9984:].contiguous(), [q, k, v], input_scale=isc)
-        assert torch.equal(big[9984:], tail)
+        if mode == ops.MODE_W4A4:
+            assert torch.equal(big[9984:], tail)
+        else:
+            assert o.rel_err(bits_of(big[9984:]), bits_of(tail)) <= REL_TOL_TIGHT
         single = ops.fp4_linear_fused(mode, x, [k], input_scale=isc)
         assert torch.equal(big[:, 2048:2560], single)
         # oracle on a row sample
