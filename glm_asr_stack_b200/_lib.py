@@ -50,6 +50,7 @@ SIGNATURES = {
     "glmasr_argmax_rows": (c_int, [P, P, c_int, c_int]),
     "glmasr_fp4_layer_proj": (c_int, [c_int, P, P, POINTER(LayerWeights), c_int]),
     "glmasr_fp4_layer_proj_host": (c_int, [c_int, P, P, POINTER(LayerWeights), c_int]),
+    "glmasr_nvfp4_linear_noalloc": (c_int, [P, P, P, P, c_float, c_float, c_int, c_int, c_int]),
     "glmasr_fp4_status": (c_int, []),
     "glmasr_launch_count": (c_longlong, []),
     "glmasr_profile_enable": (None, [c_int]),

@@ -718,6 +718,111 @@ extern "C" int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, c
     return cudaStreamSynchronize(g_stream) == cudaSuccess ? 0 : -1;
 }
 
+// ============================================================================================
+// W4A4 linear that allocates nothing
+// ============================================================================================
+// Scratch of the no-allocation entry point: quantised activations, their tiled scales and the
+// re-tiled weight scales.  Lives in the library image, so every GPU that loads the library
+// holds these bytes until the process exits.
+static constexpr int kNoAllocMaxM = 512;                        // rows of x
+static constexpr int kNoAllocMaxK = 8192;                       // reduction length
+static constexpr long long kNoAllocMaxWeight = 32ll << 20;      // ceil128(N) * K elements
+static constexpr size_t kNoAllocXq = (size_t)kNoAllocMaxM * kNoAllocMaxK / 2;                    // 2 MiB
+static constexpr size_t kNoAllocXsf = (size_t)(kNoAllocMaxM / 128) * (kNoAllocMaxK / 64) * 512;  // 256 KiB
+static constexpr size_t kNoAllocWsf = (size_t)(kNoAllocMaxWeight / 16);                          // 2 MiB
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocXq + kNoAllocXsf + kNoAllocWsf];
+
+static constexpr int kMaxDevices = 64;
+static uint8_t *g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device.  The array's name is only a
+// host-side handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+static uint8_t *noalloc_scratch_for_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) {
+            fprintf(stderr, "glmasr_nvfp4_linear_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            return nullptr;
+        }
+        g_noalloc_ptr[dev] = (uint8_t *)ptr;
+        if (!g_umma_ready) {
+            if (umma_gemm_init() != cudaSuccess) return nullptr;
+            g_umma_ready = true;
+        }
+        (void)num_sms();
+        (void)encode_fn();
+    }
+    return g_noalloc_ptr[dev];
+}
+
+extern "C" int glmasr_nvfp4_linear_noalloc(uint16_t *out, const uint16_t *x, const uint8_t *w_packed,
+                                           const uint8_t *w_scales, float input_scale, float w_global_scale,
+                                           int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0 || out == nullptr || x == nullptr || w_packed == nullptr || w_scales == nullptr)
+        return -1;
+    if (!(input_scale > 0.0f)) return -1;
+    const long long n_pad = ((long long)N + 127) / 128 * 128;
+    if (M > kNoAllocMaxM || K > kNoAllocMaxK || n_pad * K > kNoAllocMaxWeight) {
+        fprintf(stderr,
+                "glmasr_nvfp4_linear_noalloc: M=%d N=%d K=%d exceeds the built-in scratch "
+                "(M <= %d, K <= %d, ceil128(N)*K <= %lld); use nvfp4_linear instead\n",
+                M, N, K, kNoAllocMaxM, kNoAllocMaxK, kNoAllocMaxWeight);
+        return -1;
+    }
+    if (K % 256 != 0 || !aligned16(x) || !aligned16(out) || !aligned16(w_packed) || !aligned16(w_scales) || (N % 8) != 0) {
+        fprintf(stderr, "glmasr_nvfp4_linear_noalloc: needs K %% 256 == 0, N %% 8 == 0 and 16-byte aligned pointers\n");
+        return -1;
+    }
+    uint8_t *scratch = noalloc_scratch_for_current_device();
+    if (scratch == nullptr) return -1;
+    uint8_t *xq = scratch;
+    uint8_t *xsf = scratch + kNoAllocXq;
+    uint8_t *wsf = scratch + kNoAllocXq + kNoAllocXsf;
+
+    // the re-tiled weight scales must be zero where no real scale lands (rows past N)
+    if (cudaMemsetAsync(wsf, 0, tiled_sf_bytes(N, K), g_stream) != cudaSuccess) return -1;
+    launch_swizzle_scales(wsf, w_scales, N, K / 16, g_stream);
+    ++g_launches;
+    launch_quantize_act(xq, nullptr, xsf, (const __nv_bfloat16 *)x, nullptr, input_scale, M, K, K, g_stream);
+    ++g_launches;
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = M;
+    p.K = K;
+    p.out = (__nv_bfloat16 *)out;
+    p.ldo = N;
+    p.epi = EPI_STORE;
+    p.status = nullptr;
+    p.num_m_tiles = (M + 127) / 128;
+    p.n_out = N;
+    p.num_segs = 1;
+    p.seg_rows[0] = N;
+    p.seg_subtiles[0] = (N + 127) / 128;
+    p.alpha[0] = input_scale * w_global_scale;
+    p.sfa = xsf;
+    p.sfb[0] = wsf;
+    p.num_k_blocks = K / 256;
+    p.sf_k_chunks = K / 64;
+    if (!make_tmap(&p.tm_a, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, 128, 128, true))
+        return -1;
+    if (!make_tmap(&p.tm_b[0], w_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, 128,
+                   128, true))
+        return -1;
+    const int subtiles = p.seg_subtiles[0];
+    const int tiles2 = p.num_m_tiles * ((subtiles + 1) / 2);
+    const int nb = (subtiles >= 2 && tiles2 >= num_sms()) ? 2 : 1;
+    p.num_n_tiles = (subtiles + nb - 1) / nb;
+    const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int ctas = total_tiles < num_sms() ? total_tiles : num_sms();
+    if (launch_umma_gemm(GEMM_W4A4, nb, p, ctas, g_stream) != cudaSuccess) return -1;
+    ++g_launches;
+    return 0;
+}
+
 extern "C" int glmasr_fp4_status(void) {
     int host[4] = {0, 0, 0, 0};
     if (cudaStreamSynchronize(g_stream) != cudaSuccess) return -1;

@@ -111,6 +111,20 @@ def nvfp4_linear(out: torch.Tensor, x: torch.Tensor, w_packed: torch.Tensor, w_s
                             float(w_global_scale), _ptr(pre_quant_scale), _ptr(bias), M, N, K)
 
 
+def nvfp4_linear_noalloc(out: torch.Tensor, x: torch.Tensor, w_packed: torch.Tensor, w_scales: torch.Tensor,
+                         input_scale: float, w_global_scale: float) -> int:
+    """glmasr_nvfp4_linear_noalloc: the W4A4 linear for callers that must not allocate device
+    memory (for instance a decode loop running after the engine has handed all free memory to the
+    KV pool).  Temporaries live in a fixed array inside the library; returns -1 for sizes beyond it
+    (M > 512, K > 8192, ceil128(N)*K > 32 Mi) or unsupported alignment.  Calls must not overlap
+    on the GPU: they share that array."""
+    lib = _lib.load()
+    M, K = x.shape
+    N = w_packed.shape[0]
+    return lib.glmasr_nvfp4_linear_noalloc(_ptr(out), _ptr(x), _ptr(w_packed), _ptr(w_scales), float(input_scale),
+                                           float(w_global_scale), M, N, K)
+
+
 def bf16_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """reference: bf16_linear, Infer-engine/cuda/kernels.cu:1147-1193."""
     lib = _lib.load()

@@ -64,7 +64,7 @@ int nvfp4_linear(void *handle, uint16_t *out, uint16_t *dequant_buf, const uint1
                  float w_global_scale, const uint16_t *pre_quant_scale, const uint16_t *bias,
                  int M, int N, int K);
 
-/* Infer-engine/include/cuda_kernels.h:63-68, Infer-engine/cuda/kernels.cu:1147-1193.
+/* Infer-engine/include/cuda_kernels.h:66-70, Infer-engine/cuda/kernels.cu:1147-1193.
  * out[M,N] = bf16(x[M,K] * w[N,K]^T (+ bias)), bf16 weights (the reference lm_head). */
 void bf16_linear(void *handle, uint16_t *out, const uint16_t *x, const uint16_t *w,
                  const uint16_t *bias, int M, int N, int K);
@@ -151,6 +151,24 @@ int glmasr_fp4_layer_proj(int mode, uint16_t *hidden_out, const uint16_t *hidden
  * copies out and synchronises -- the end-to-end call the benchmark times. */
 int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16_t *hidden_in_host,
                                const glmasr_layer_weights *lw, int M);
+
+/* W4A4 linear (nvfp4_linear arithmetic, no pre_quant_scale, no bias) for callers that must not
+ * allocate device memory.  No counterpart in the reference.  The engine sizes its paged-KV pool
+ * from whatever device memory is still free after warm-up, so a decode-loop call that grows a
+ * workspace later can fail or stall the loop on cudaMalloc's implicit synchronisation; this
+ * entry point instead keeps its temporaries (quantised activations, their scales, the re-tiled
+ * weight scales) in a fixed 4.25 MiB array inside the library image, resident on every GPU that
+ * loads the library until the process exits.
+ * Limits: M <= 512, K <= 8192, K % 256 == 0, N % 8 == 0, ceil128(N) * K <= 32 Mi, 16-byte aligned
+ * pointers; anything else returns -1 with a message on stderr (use nvfp4_linear then).
+ * The first call on each device looks up the array's device address and opts the kernels in to
+ * large shared memory; make that first call before any stream capture begins.
+ * All calls share the one array and it keeps the previous call's contents (the part that must
+ * start at zero is cleared on every call), so two calls whose GPU work overlaps -- different
+ * streams, different host threads -- race; issue them in stream order. */
+int glmasr_nvfp4_linear_noalloc(uint16_t *out, const uint16_t *x, const uint8_t *w_packed,
+                                const uint8_t *w_scales, float input_scale, float w_global_scale,
+                                int M, int N, int K);
 
 /* Synchronise and return the first device-side status code recorded since the last call
  * (0 = none; 1..5 = a bounded wait inside a kernel ran out), then clear it. */
