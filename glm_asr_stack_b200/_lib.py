@@ -41,6 +41,13 @@ SIGNATURES = {
     "residual_add": (None, [P, P, P, c_int]),
     "lm_head_argmax_batched": (None, [P, P, P, c_int, c_int, c_int, P]),
     "lm_head_cleanup": (None, []),
+    "rmsnorm": (None, [P, P, P, c_float, c_int, c_int]),
+    "embedding_lookup": (None, [P, P, P, c_int, c_int]),
+    "reshape_and_cache": (None, [P, P, P, P, P, c_int, c_int, c_int, c_int]),
+    "paged_decode_attention": (None, [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "decoder_decode_step_batched": (None, [P, P, P, P, P, P, P, c_int, P, P, P]),
+    "glmasr_rope_single_token": (None, [P, P, c_int, c_int, c_int]),
+    "glmasr_decoder_forget_weights": (None, []),
     "glmasr_fp4_linear_fused": (c_int, [c_int, P, c_int, P, c_int, POINTER(Fp4Weight), c_int, c_float, P, P,
                                         c_int, P, c_int, c_int]),
     "glmasr_fp4_prepack": (c_int, [P, c_int, c_int]),

@@ -28,6 +28,7 @@ static int *g_status = nullptr;
 static long long g_launches = 0;
 static int g_num_sms = 0;
 static bool g_umma_ready = false;
+static bool g_pair_ready = false;
 
 // optional per-launch timing of the GEMM kernel (CUDA events on the launching stream)
 static bool g_profile = false;
@@ -38,7 +39,7 @@ struct TimedLaunch {
 };
 static std::vector<TimedLaunch> g_timed;
 
-static constexpr int kSlots = 13;
+static constexpr int kSlots = 24;   // 0..12 used here, 13..23 by the decode step (decoder_step.cu)
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
 
@@ -124,6 +125,16 @@ static int debug_flags() {
         v = (e && e[0]) ? atoi(e) : 0;
     }
     return v;
+}
+
+// GLMASR_PAIR_KERNEL=0 keeps W4A4 on the single-CTA kernel (comparison runs)
+static bool use_pair_kernel() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_PAIR_KERNEL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 static bool force_simt() {
@@ -385,6 +396,9 @@ static int run_fused(const FusedArgs &a) {
         p.sfa = xsf;
         p.num_k_blocks = a.K / 256;
         p.sf_k_chunks = a.K / 64;
+        if (!make_tmap(&p.tm_sfa, xsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, 128,
+                       (uint64_t)((a.M + 127) / 128) * (uint64_t)(a.K / 64), 512, 128, 4, false))
+            return -1;
     } else {
         if (a.pre != nullptr) {
             if (a.prequant_scratch == nullptr || a.ldx != a.K) return -1;
@@ -425,11 +439,46 @@ static int run_fused(const FusedArgs &a) {
                 return -1;
             if (a.mode == GEMM_W4A4) {
                 p.sfb[i] = prepacked_scales(w.w_scales, w.N, a.K);
+                if (!make_tmap(&p.tm_sfb[i], p.sfb[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, 128,
+                               (uint64_t)((w.N + 127) / 128) * (uint64_t)(a.K / 64), 512, 128, 4, false))
+                    return -1;
             } else {
                 if (!make_tmap(&p.tm_bs[i], w.w_scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 16,
                                (uint64_t)w.N, (uint64_t)a.K / 16, 16, 128, false))
                     return -1;
             }
+        }
+    }
+
+    // W4A4 with enough 256 x 256 tiles for every CTA pair: the cta_group::2 kernel
+    if (a.mode == GEMM_W4A4 && use_pair_kernel()) {
+        const int n_tiles = a.epi == EPI_SILU_GATE ? p.seg_subtiles[0] : (subtiles + 1) / 2;
+        const int m_pairs = (p.num_m_tiles + 1) / 2;
+        const int pairs = num_sms() / 2;
+        if (m_pairs * n_tiles >= pairs && a.M >= 512) {
+            if (!g_pair_ready) {
+                GLMASR_CUDA_CHECK(umma_gemm_pair_init());
+                g_pair_ready = true;
+            }
+            p.num_n_tiles = n_tiles;
+            TimedLaunch tl;
+            if (g_profile) {
+                cudaEventCreate(&tl.start);
+                cudaEventCreate(&tl.stop);
+                int n_rows = 0;
+                for (int i = 0; i < p.num_segs; ++i) n_rows += p.seg_rows[i];
+                tl.flops = 2.0 * a.M * (double)n_rows * a.K;
+                tl.bytes = (double)n_rows * a.K * 0.5625 + (double)a.M * a.K * 0.5625 + 2.0 * a.M * p.n_out +
+                           (a.epi == EPI_RESIDUAL ? 2.0 * a.M * p.n_out : 0.0);
+                cudaEventRecord(tl.start, g_stream);
+            }
+            if (launch_umma_gemm_pair(p, pairs, g_stream) != cudaSuccess) return -1;
+            ++g_launches;
+            if (g_profile) {
+                cudaEventRecord(tl.stop, g_stream);
+                g_timed.push_back(tl);
+            }
+            return 0;
         }
     }
 

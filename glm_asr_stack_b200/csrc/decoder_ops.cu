@@ -1,0 +1,332 @@
+// Step-resident glue kernels of the batched decode step (bf16, HBM-bound).  They are not FP4
+// work, but the decode step cannot run without them and the paged attention decides its time:
+// 256 sequences x ~325 tokens x 28 layers of K and V are 4.8 GB per step against 0.83 GB of
+// FP4 weights.
+#include <cuda_bf16.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "decoder_ops.cuh"
+
+namespace glmasr {
+
+// --------------------------------------------------------------------------------------------
+// RMSNorm (reference: Infer-engine/cuda/kernels.cu:252-295): out = (x / sqrt(mean(x^2)+eps)) * w.
+// The reference uses one warp per row: lane l adds x[l]^2, x[l+32]^2, ... in order, then a
+// shfl_down tree.  Here a 256-thread block stages the row in shared memory with 16-byte loads,
+// warp 0 repeats exactly that summation order from shared memory (so the result is bit-equal),
+// and all threads normalise.
+// --------------------------------------------------------------------------------------------
+__global__ void rmsnorm_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ x,
+                               const __nv_bfloat16 *__restrict__ weight, float eps, int rows, int dim) {
+    extern __shared__ __nv_bfloat16 row_s[];
+    __shared__ float rms_s;
+    const int row = blockIdx.x;
+    if (row >= rows) return;
+    const __nv_bfloat16 *xr = x + (size_t)row * dim;
+    __nv_bfloat16 *orow = out + (size_t)row * dim;
+    const bool vec = (dim % 8 == 0) && (((uintptr_t)xr & 15) == 0) && (((uintptr_t)orow & 15) == 0) &&
+                     (((uintptr_t)weight & 15) == 0);
+    if (vec) {
+        for (int i = threadIdx.x; i < dim / 8; i += blockDim.x)
+            reinterpret_cast<uint4 *>(row_s)[i] = reinterpret_cast<const uint4 *>(xr)[i];
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) row_s[i] = xr[i];
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float sum_sq = 0.0f;
+        for (int i = threadIdx.x; i < dim; i += 32) {
+            const float v = __bfloat162float(row_s[i]);
+            sum_sq += v * v;
+        }
+        for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
+        if (threadIdx.x == 0) rms_s = sqrtf(sum_sq / dim + eps);
+    }
+    __syncthreads();
+    const float rms = rms_s;
+    if (vec) {
+        for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) {
+            const uint4 xv = reinterpret_cast<const uint4 *>(row_s)[i];
+            const uint4 wv = reinterpret_cast<const uint4 *>(weight)[i];
+            const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float a0 = __fdiv_rn(__uint_as_float(xs[j] << 16), rms) * __uint_as_float(ws[j] << 16);
+                const float a1 = __fdiv_rn(__uint_as_float(xs[j] & 0xFFFF0000u), rms) * __uint_as_float(ws[j] & 0xFFFF0000u);
+                const __nv_bfloat162 b = __floats2bfloat162_rn(a0, a1);
+                o[j] = *reinterpret_cast<const uint32_t *>(&b);
+            }
+            reinterpret_cast<uint4 *>(orow)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x)
+            orow[i] = __float2bfloat16(__fdiv_rn(__bfloat162float(row_s[i]), rms) * __bfloat162float(weight[i]));
+    }
+}
+
+void launch_rmsnorm(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps, int rows,
+                    int dim, cudaStream_t st) {
+    if (rows <= 0 || dim <= 0) return;
+    rmsnorm_kernel<<<rows, 256, (size_t)dim * sizeof(__nv_bfloat16), st>>>(out, x, weight, eps, rows, dim);
+}
+
+// --------------------------------------------------------------------------------------------
+// RoPE for one new token per sequence (reference: rope_batched_single_token_kernel,
+// Infer-engine/cuda/decoder.cu:605-632): rotate-half, theta 10000, full head_dim, position =
+// positions[seq]; same float expressions, so bit-equal.
+// --------------------------------------------------------------------------------------------
+__global__ void rope_single_token_kernel(__nv_bfloat16 *tensor, int ld, int col0, const int *__restrict__ positions,
+                                         int num_seqs, int n_heads, int head_dim) {
+    const int half_dim = head_dim / 2;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= num_seqs * n_heads * half_dim) return;
+    const int seq = idx / (n_heads * half_dim);
+    const int head = (idx / half_dim) % n_heads;
+    const int d = idx % half_dim;
+    const int pos = positions[seq];
+    const float inv_freq = 1.0f / powf(10000.0f, (2.0f * d) / head_dim);
+    const float theta = pos * inv_freq;
+    const float cos_t = cosf(theta);
+    const float sin_t = sinf(theta);
+    __nv_bfloat16 *base = tensor + (size_t)seq * ld + col0 + head * head_dim;
+    const float v0 = __bfloat162float(base[d]);
+    const float v1 = __bfloat162float(base[d + half_dim]);
+    base[d] = __float2bfloat16(v0 * cos_t - v1 * sin_t);
+    base[d + half_dim] = __float2bfloat16(v0 * sin_t + v1 * cos_t);
+}
+
+void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int *positions, int num_seqs, int n_heads,
+                              int head_dim, cudaStream_t st) {
+    const int total = num_seqs * n_heads * (head_dim / 2);
+    if (total <= 0) return;
+    rope_single_token_kernel<<<(total + 255) / 256, 256, 0, st>>>(tensor, ld, col0, positions, num_seqs, n_heads, head_dim);
+}
+
+// --------------------------------------------------------------------------------------------
+// reshape_and_cache (reference: Infer-engine/cuda/paged_kv.cu:70-97): scatter each token's K and
+// V rows to slot = block * block_size + offset of the paged cache
+// [block][token][kv_head][dim].  16 bytes per thread.
+// --------------------------------------------------------------------------------------------
+__global__ void reshape_and_cache_kernel(__nv_bfloat16 *__restrict__ key_cache, __nv_bfloat16 *__restrict__ value_cache,
+                                         const __nv_bfloat16 *__restrict__ key, int ldk,
+                                         const __nv_bfloat16 *__restrict__ value, int ldv,
+                                         const int64_t *__restrict__ slot_mapping, int num_tokens, int row_elems) {
+    const int chunks = row_elems / 8;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= num_tokens * chunks) return;
+    const int tok = idx / chunks, c = idx % chunks;
+    const int64_t slot = slot_mapping[tok];
+    const size_t dst = (size_t)slot * row_elems + (size_t)c * 8;
+    *reinterpret_cast<uint4 *>(key_cache + dst) = *reinterpret_cast<const uint4 *>(key + (size_t)tok * ldk + c * 8);
+    *reinterpret_cast<uint4 *>(value_cache + dst) = *reinterpret_cast<const uint4 *>(value + (size_t)tok * ldv + c * 8);
+}
+
+__global__ void reshape_and_cache_scalar_kernel(__nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache,
+                                                const __nv_bfloat16 *key, int ldk, const __nv_bfloat16 *value, int ldv,
+                                                const int64_t *slot_mapping, int num_tokens, int row_elems) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= num_tokens * row_elems) return;
+    const int tok = idx / row_elems, c = idx % row_elems;
+    const size_t dst = (size_t)slot_mapping[tok] * row_elems + c;
+    key_cache[dst] = key[(size_t)tok * ldk + c];
+    value_cache[dst] = value[(size_t)tok * ldv + c];
+}
+
+void launch_reshape_and_cache(__nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, const __nv_bfloat16 *key, int ldk,
+                              const __nv_bfloat16 *value, int ldv, const int64_t *slot_mapping, int num_tokens,
+                              int num_kv_heads, int head_dim, int block_size, cudaStream_t st) {
+    (void)block_size;   // slot * row_elems already is ((block*block_size + offset) * kv_heads + head) * dim
+    const int row_elems = num_kv_heads * head_dim;
+    if (num_tokens <= 0 || row_elems <= 0) return;
+    const bool vec = (row_elems % 8 == 0) && (ldk % 8 == 0) && (ldv % 8 == 0) && (((uintptr_t)key & 15) == 0) &&
+                     (((uintptr_t)value & 15) == 0) && (((uintptr_t)key_cache & 15) == 0) &&
+                     (((uintptr_t)value_cache & 15) == 0);
+    if (vec) {
+        const int total = num_tokens * (row_elems / 8);
+        reshape_and_cache_kernel<<<(total + 255) / 256, 256, 0, st>>>(key_cache, value_cache, key, ldk, value, ldv,
+                                                                      slot_mapping, num_tokens, row_elems);
+    } else {
+        const int total = num_tokens * row_elems;
+        reshape_and_cache_scalar_kernel<<<(total + 255) / 256, 256, 0, st>>>(key_cache, value_cache, key, ldk, value,
+                                                                             ldv, slot_mapping, num_tokens, row_elems);
+    }
+}
+
+}  // namespace glmasr
+
+namespace glmasr {
+
+// --------------------------------------------------------------------------------------------
+// Paged GQA decode attention, head_dim 128 (reference: paged_decode_attention and its
+// gqa4_h128 warp kernel, Infer-engine/cuda/paged_kv.cu:321-422, 440-519):
+//   out[seq, h, :] = softmax_t( q[seq, h, :] . K[t, kv(h), :] / sqrt(128) ) V[t, kv(h), :]
+// over the seq_lens[seq] cached tokens found through the block table; a negative block id masks
+// its tokens; seq_len <= 0 gives zeros; the final division adds 1e-9 to the sum as the
+// reference does.
+//
+// One CTA per (kv head, sequence); warp g handles query head kv*G + g, so all G warps read the
+// same K/V rows (one HBM read, the rest L1 hits).  A lane owns 4 consecutive dims (8-byte loads,
+// 256 contiguous bytes per warp per row).  Tokens are taken 8 at a time: 8 independent dot
+// products and shuffle reductions in flight, one online-softmax update per 8 tokens (the
+// reference updates per token; the result differs only by fp32 rounding).
+// --------------------------------------------------------------------------------------------
+static constexpr int kAttnTokens = 8;
+
+__global__ void __launch_bounds__(256) paged_decode_attention_h128_kernel(
+    __nv_bfloat16 *__restrict__ out, int ldo, const __nv_bfloat16 *__restrict__ query, int ldq,
+    const __nv_bfloat16 *__restrict__ key_cache, const __nv_bfloat16 *__restrict__ value_cache,
+    const int *__restrict__ block_tables, const int *__restrict__ seq_lens, int num_q_heads, int num_kv_heads,
+    int group, int block_size, int max_blocks_per_seq, float scale) {
+    const int kv_head = blockIdx.x;
+    const int seq = blockIdx.y;
+    const int g = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (g >= group) return;
+    const int q_head = kv_head * group + g;
+    const int seq_len = seq_lens[seq];
+    __nv_bfloat16 *out_ptr = out + (size_t)seq * ldo + (size_t)q_head * 128 + lane * 4;
+    if (seq_len <= 0) {
+        *reinterpret_cast<uint2 *>(out_ptr) = make_uint2(0u, 0u);
+        return;
+    }
+    const uint2 qraw = *reinterpret_cast<const uint2 *>(query + (size_t)seq * ldq + (size_t)q_head * 128 + lane * 4);
+    const float q0 = __uint_as_float(qraw.x << 16), q1 = __uint_as_float(qraw.x & 0xFFFF0000u);
+    const float q2 = __uint_as_float(qraw.y << 16), q3 = __uint_as_float(qraw.y & 0xFFFF0000u);
+    const int *bt = block_tables + (size_t)seq * max_blocks_per_seq;
+    const size_t row_elems = (size_t)num_kv_heads * 128;
+    const size_t head_off = (size_t)kv_head * 128 + lane * 4;
+
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    float run_max = -INFINITY, run_sum = 0.f;
+
+    for (int t0 = 0; t0 < seq_len; t0 += kAttnTokens) {
+        uint2 kr[kAttnTokens], vr[kAttnTokens];
+        bool valid[kAttnTokens];
+#pragma unroll
+        for (int j = 0; j < kAttnTokens; ++j) {
+            const int t = t0 + j;
+            int blk = -1;
+            if (t < seq_len) blk = bt[t / block_size];
+            valid[j] = blk >= 0;
+            kr[j] = make_uint2(0u, 0u);
+            vr[j] = make_uint2(0u, 0u);
+            if (valid[j]) {
+                const size_t base = ((size_t)blk * block_size + (size_t)(t % block_size)) * row_elems + head_off;
+                kr[j] = *reinterpret_cast<const uint2 *>(key_cache + base);
+                vr[j] = *reinterpret_cast<const uint2 *>(value_cache + base);
+            }
+        }
+        float s[kAttnTokens];
+#pragma unroll
+        for (int j = 0; j < kAttnTokens; ++j) {
+            s[j] = q0 * __uint_as_float(kr[j].x << 16) + q1 * __uint_as_float(kr[j].x & 0xFFFF0000u) +
+                   q2 * __uint_as_float(kr[j].y << 16) + q3 * __uint_as_float(kr[j].y & 0xFFFF0000u);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+            for (int j = 0; j < kAttnTokens; ++j) s[j] += __shfl_xor_sync(0xFFFFFFFFu, s[j], off);
+        }
+        float cmax = run_max;
+#pragma unroll
+        for (int j = 0; j < kAttnTokens; ++j) {
+            s[j] = valid[j] ? s[j] * scale : -INFINITY;
+            cmax = fmaxf(cmax, s[j]);
+        }
+        if (cmax == -INFINITY) continue;          // nothing valid yet
+        const float corr = (run_max == -INFINITY) ? 0.f : expf(run_max - cmax);
+        acc0 *= corr; acc1 *= corr; acc2 *= corr; acc3 *= corr;
+        run_sum *= corr;
+#pragma unroll
+        for (int j = 0; j < kAttnTokens; ++j) {
+            const float pj = valid[j] ? expf(s[j] - cmax) : 0.f;
+            run_sum += pj;
+            acc0 += pj * __uint_as_float(vr[j].x << 16);
+            acc1 += pj * __uint_as_float(vr[j].x & 0xFFFF0000u);
+            acc2 += pj * __uint_as_float(vr[j].y << 16);
+            acc3 += pj * __uint_as_float(vr[j].y & 0xFFFF0000u);
+        }
+        run_max = cmax;
+    }
+    const float inv = 1.0f / (run_sum + 1e-9f);
+    const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
+    const __nv_bfloat162 o23 = __floats2bfloat162_rn(acc2 * inv, acc3 * inv);
+    *reinterpret_cast<uint2 *>(out_ptr) =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&o01), *reinterpret_cast<const uint32_t *>(&o23));
+}
+
+bool launch_paged_decode_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *query, int ldq,
+                                   const __nv_bfloat16 *key_cache, const __nv_bfloat16 *value_cache,
+                                   const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
+                                   int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                                   cudaStream_t st) {
+    if (head_dim != 128 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return false;
+    const int group = num_q_heads / num_kv_heads;
+    if (group > 8 || (ldq % 4) != 0 || (ldo % 4) != 0) return false;
+    if (num_seqs <= 0) return true;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    dim3 grid(num_kv_heads, num_seqs);
+    paged_decode_attention_h128_kernel<<<grid, 32 * group, 0, st>>>(out, ldo, query, ldq, key_cache, value_cache,
+                                                                    block_tables, seq_lens, num_q_heads, num_kv_heads,
+                                                                    group, block_size, max_blocks_per_seq, scale);
+    return true;
+}
+
+// --------------------------------------------------------------------------------------------
+// embedding_lookup (reference: Infer-engine/cuda/kernels.cu:712-736) and row gather / scatter
+// --------------------------------------------------------------------------------------------
+__global__ void embedding_lookup_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ table,
+                                        const int *__restrict__ ids, int n, int dim) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    const __nv_bfloat16 *row = table + (size_t)ids[i] * dim;
+    __nv_bfloat16 *orow = out + (size_t)i * dim;
+    if (dim % 8 == 0 && (((uintptr_t)row & 15) == 0) && (((uintptr_t)orow & 15) == 0)) {
+        for (int d = threadIdx.x; d < dim / 8; d += blockDim.x)
+            reinterpret_cast<uint4 *>(orow)[d] = reinterpret_cast<const uint4 *>(row)[d];
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) orow[d] = row[d];
+    }
+}
+
+void launch_embedding_lookup(__nv_bfloat16 *out, const __nv_bfloat16 *table, const int *ids, int n, int dim,
+                             cudaStream_t st) {
+    if (n <= 0) return;
+    embedding_lookup_kernel<<<n, 256, 0, st>>>(out, table, ids, n, dim);
+}
+
+__global__ void gather_rows_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *const *__restrict__ src_rows,
+                                   int n, int dim) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    const __nv_bfloat16 *row = src_rows[i];
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) out[(size_t)i * dim + d] = row[d];
+}
+__global__ void scatter_rows_kernel(__nv_bfloat16 *const *__restrict__ dst_rows, const __nv_bfloat16 *__restrict__ in,
+                                    int n, int dim) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    __nv_bfloat16 *row = dst_rows[i];
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) row[d] = in[(size_t)i * dim + d];
+}
+void launch_gather_rows(__nv_bfloat16 *out, const __nv_bfloat16 *const *src_rows, int n, int dim, cudaStream_t st) {
+    if (n > 0) gather_rows_kernel<<<n, 256, 0, st>>>(out, src_rows, n, dim);
+}
+void launch_scatter_rows(__nv_bfloat16 *const *dst_rows, const __nv_bfloat16 *in, int n, int dim, cudaStream_t st) {
+    if (n > 0) scatter_rows_kernel<<<n, 256, 0, st>>>(dst_rows, in, n, dim);
+}
+
+__global__ void gather_block_tables_kernel(int *__restrict__ dst, const int *__restrict__ tables,
+                                           const int *__restrict__ rows, int n, int width) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    const int *src = tables + (size_t)rows[i] * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) dst[(size_t)i * width + d] = src[d];
+}
+void launch_gather_block_tables(int *dst, const int *tables, const int *rows, int n, int width, cudaStream_t st) {
+    if (n > 0) gather_block_tables_kernel<<<n, 128, 0, st>>>(dst, tables, rows, n, width);
+}
+
+}  // namespace glmasr

@@ -1,0 +1,34 @@
+// Launchers of the decoder's step-resident glue kernels (decoder_ops.cu): RMSNorm, rotate-half
+// RoPE for one new token per sequence, paged-KV write, paged GQA decode attention, embedding
+// gather, row gather/scatter.  All take explicit row pitches so that they can read q / k / v
+// straight out of the fused q|k|v projection output.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace glmasr {
+
+void launch_rmsnorm(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps, int rows,
+                    int dim, cudaStream_t st);
+// In place on `tensor` rows of pitch `ld`: heads [0, n_heads) of head_dim at column offset col0.
+void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int *positions, int num_seqs, int n_heads,
+                              int head_dim, cudaStream_t st);
+void launch_reshape_and_cache(__nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, const __nv_bfloat16 *key, int ldk,
+                              const __nv_bfloat16 *value, int ldv, const int64_t *slot_mapping, int num_tokens,
+                              int num_kv_heads, int head_dim, int block_size, cudaStream_t st);
+// Returns false when the shape is not supported (head_dim != 128 or q heads not a multiple of kv heads, group > 8).
+bool launch_paged_decode_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *query, int ldq,
+                                   const __nv_bfloat16 *key_cache, const __nv_bfloat16 *value_cache,
+                                   const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
+                                   int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                                   cudaStream_t st);
+void launch_embedding_lookup(__nv_bfloat16 *out, const __nv_bfloat16 *table, const int *ids, int n, int dim,
+                             cudaStream_t st);
+// out[i, :] = src_rows[i][:]  /  dst_rows[i][:] = in[i, :]   (device arrays of row pointers)
+void launch_gather_rows(__nv_bfloat16 *out, const __nv_bfloat16 *const *src_rows, int n, int dim, cudaStream_t st);
+void launch_scatter_rows(__nv_bfloat16 *const *dst_rows, const __nv_bfloat16 *in, int n, int dim, cudaStream_t st);
+// dst[i, :] = tables[rows[i], :]  (int32 block tables)
+void launch_gather_block_tables(int *dst, const int *tables, const int *rows, int n, int width, cudaStream_t st);
+
+}  // namespace glmasr

@@ -1,0 +1,374 @@
+// Batched single-token decode step of the 28-layer decoder behind the engine's own entry point
+// (reference: decoder_decode_step_batched, Infer-engine/cuda/decoder.cu:1849-2173), plus the
+// reference-named glue entry points it is built from.
+//
+// Same inputs, outputs and side effects as the reference driver: gathers query_ptrs[i] rows,
+// runs every layer (RMSNorm eps 1e-5, q|k|v, rotate-half RoPE at position = cached length, KV
+// write to the paged pool, paged GQA attention over cached+1 tokens, o + residual, RMSNorm,
+// gate|up + SiLU-gate, down + residual), final RMSNorm, writes the rows back to query_ptrs[i],
+// bumps h_seq_lens / d_seq_lens.  Differences in HOW:
+//   * tensor names are resolved once per WeightStore into a per-layer pointer table (the reference
+//     does ~37 linear string scans per layer per step);
+//   * q|k|v and gate|up are single fused GEMMs with SiLU-gate / residual in the epilogue, RoPE,
+//     cache write and attention read q/k/v in place from the fused output;
+//   * the per-sequence block-table rows are gathered by one kernel (the reference issues one
+//     cudaMemcpy per sequence);
+//   * no per-layer residual copies: the norm writes to a second buffer.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <vector>
+
+#include "../../include/glmasr_engine_types.h"
+#include "../../include/glmasr_fp4.h"
+#include "decoder_ops.cuh"
+#include "runtime.cuh"
+
+namespace glmasr {
+
+struct ProjRef {
+    int dtype = -1;                     // GLMASR_DTYPE_UINT8 (FP4) or GLMASR_DTYPE_BF16
+    const void *w = nullptr;
+    const uint8_t *scales = nullptr;
+    float global_scale = 1.0f;
+    float input_scale = 1.0f;
+    const uint16_t *pre = nullptr;
+    int N = 0, K = 0;
+};
+
+struct LayerRef {
+    const uint16_t *norm1 = nullptr, *norm2 = nullptr;
+    ProjRef q, k, v, o, gate, up, down;
+};
+
+struct ModelRefs {
+    const glmasr_WeightStore *ws = nullptr;
+    int count = -1;
+    std::vector<LayerRef> layers;
+    const uint16_t *final_norm = nullptr;
+};
+
+static ModelRefs g_refs;
+
+static const glmasr_Tensor *find_tensor(const glmasr_WeightStore *ws, const char *name) {
+    for (int i = 0; i < ws->count; ++i)
+        if (ws->names[i] != nullptr && strcmp(ws->names[i], name) == 0) return &ws->tensors[i];
+    return nullptr;
+}
+
+static const glmasr_Tensor *require_tensor(const glmasr_WeightStore *ws, const char *name) {
+    const glmasr_Tensor *t = find_tensor(ws, name);
+    if (t == nullptr) {   // reference: wget(), Infer-engine/cuda/decoder.cu:849-854
+        fprintf(stderr, "Weight not found: %s\n", name);
+        exit(1);
+    }
+    return t;
+}
+
+static float read_scalar(const glmasr_Tensor *t, float fallback) {
+    // reference: decoder_scalar_read_cached (Infer-engine/cuda/decoder.cu:165-187); read once here
+    if (t == nullptr || t->data == nullptr) return fallback;
+    float v = fallback;
+    GLMASR_CUDA_CHECK(cudaMemcpy(&v, t->data, sizeof(float), cudaMemcpyDeviceToHost));
+    return v;
+}
+
+static ProjRef resolve_proj(const glmasr_WeightStore *ws, int layer, const char *block, const char *proj) {
+    char name[256];
+    ProjRef r;
+    snprintf(name, sizeof(name), "language_model.model.layers.%d.%s.%s.weight", layer, block, proj);
+    const glmasr_Tensor *tw = require_tensor(ws, name);
+    r.dtype = tw->dtype;
+    r.w = tw->data;
+    r.N = (int)tw->shape[0];
+    r.K = tw->dtype == GLMASR_DTYPE_UINT8 ? (int)tw->shape[1] * 2 : (int)tw->shape[1];
+    GLMASR_CHECK(tw->dtype == GLMASR_DTYPE_UINT8 || tw->dtype == GLMASR_DTYPE_BF16,
+                 "Unsupported decoder weight dtype %d for %s", tw->dtype, name);
+    snprintf(name, sizeof(name), "language_model.model.layers.%d.%s.%s.weight_scale", layer, block, proj);
+    const glmasr_Tensor *ts = find_tensor(ws, name);
+    r.scales = ts ? (const uint8_t *)ts->data : nullptr;
+    snprintf(name, sizeof(name), "language_model.model.layers.%d.%s.%s.weight_scale_2", layer, block, proj);
+    r.global_scale = read_scalar(find_tensor(ws, name), 1.0f);
+    snprintf(name, sizeof(name), "language_model.model.layers.%d.%s.%s.input_scale", layer, block, proj);
+    r.input_scale = read_scalar(find_tensor(ws, name), 1.0f);
+    snprintf(name, sizeof(name), "language_model.model.layers.%d.%s.%s.pre_quant_scale", layer, block, proj);
+    const glmasr_Tensor *tp = find_tensor(ws, name);
+    r.pre = tp ? (const uint16_t *)tp->data : nullptr;
+    return r;
+}
+
+static const ModelRefs &model_refs(const glmasr_WeightStore *ws, int num_layers) {
+    if (g_refs.ws == ws && g_refs.count == ws->count && (int)g_refs.layers.size() == num_layers) return g_refs;
+    g_refs = ModelRefs();
+    g_refs.ws = ws;
+    g_refs.count = ws->count;
+    g_refs.layers.resize(num_layers);
+    char name[256];
+    for (int l = 0; l < num_layers; ++l) {
+        LayerRef &L = g_refs.layers[l];
+        snprintf(name, sizeof(name), "language_model.model.layers.%d.input_layernorm.weight", l);
+        L.norm1 = (const uint16_t *)require_tensor(ws, name)->data;
+        snprintf(name, sizeof(name), "language_model.model.layers.%d.post_attention_layernorm.weight", l);
+        L.norm2 = (const uint16_t *)require_tensor(ws, name)->data;
+        L.q = resolve_proj(ws, l, "self_attn", "q_proj");
+        L.k = resolve_proj(ws, l, "self_attn", "k_proj");
+        L.v = resolve_proj(ws, l, "self_attn", "v_proj");
+        L.o = resolve_proj(ws, l, "self_attn", "o_proj");
+        L.gate = resolve_proj(ws, l, "mlp", "gate_proj");
+        L.up = resolve_proj(ws, l, "mlp", "up_proj");
+        L.down = resolve_proj(ws, l, "mlp", "down_proj");
+    }
+    g_refs.final_norm = (const uint16_t *)require_tensor(ws, "language_model.model.norm.weight")->data;
+    return g_refs;
+}
+
+void forget_model_refs() { g_refs = ModelRefs(); }
+
+static bool prefer_w4a4() {
+    // reference: prefer_nvfp4_cutlass, Infer-engine/cuda/decoder.cu:142-151
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("GLMASR_USE_CUTLASS_NVFP4");
+        state = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
+    }
+    return state == 1;
+}
+
+static glmasr_fp4_weight as_weight(const ProjRef &p) {
+    glmasr_fp4_weight w;
+    w.w_packed = (const uint8_t *)p.w;
+    w.w_scales = p.scales;
+    w.w_global_scale = p.global_scale;
+    w.N = p.N;
+    return w;
+}
+
+// One projection on its own: the reference's linear_proj (Infer-engine/cuda/decoder.cu:861-921)
+// with an optional fused residual.
+static void single_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, const ProjRef &p, int M,
+                        const uint16_t *residual, uint16_t *scratch) {
+    if (p.dtype == GLMASR_DTYPE_BF16) {
+        // bf16_linear keeps the reference's dense signature: go through the scratch buffer when the
+        // destination is a column slice of a wider buffer
+        GLMASR_CHECK(ldx == p.K, "bf16 projection needs a dense input");
+        uint16_t *dst = ldo == p.N ? out : scratch;
+        bf16_linear(nullptr, dst, x, (const uint16_t *)p.w, nullptr, M, p.N, p.K);
+        if (residual) {
+            GLMASR_CHECK(ldo == p.N, "bf16 projection with residual needs a dense output");
+            residual_add(out, out, residual, M * p.N);
+        } else if (dst != out) {
+            GLMASR_CUDA_CHECK(cudaMemcpy2DAsync(out, (size_t)ldo * 2, dst, (size_t)p.N * 2, (size_t)p.N * 2, M,
+                                                cudaMemcpyDeviceToDevice, current_stream()));
+        }
+        return;
+    }
+    const glmasr_fp4_weight w = as_weight(p);
+    const int epi = residual ? GLMASR_EPI_RESIDUAL : GLMASR_EPI_STORE;
+    int rc = -1;
+    if (prefer_w4a4() && p.scales != nullptr && p.input_scale > 0.0f)
+        rc = glmasr_fp4_linear_fused(GLMASR_MODE_W4A4, out, ldo, x, ldx, &w, 1, p.input_scale, p.pre, nullptr, epi,
+                                     residual, M, p.K);
+    if (rc != 0)
+        rc = glmasr_fp4_linear_fused(GLMASR_MODE_W4A16, out, ldo, x, ldx, &w, 1, 1.0f, p.pre, scratch, epi, residual, M,
+                                     p.K);
+    GLMASR_CHECK(rc == 0, "decoder projection failed (N=%d K=%d M=%d)", p.N, p.K, M);
+}
+
+// Several same-input FP4 projections as one GEMM when the reference's own fusion rule allows it
+// (all FP4, none with a pre_quant_scale: Infer-engine/cuda/decoder.cu:957-963) and, for W4A4, they
+// share their input_scale.  Returns false when the caller has to run them one by one.
+static bool fused_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, const ProjRef *const *ps, int n, int epi,
+                       int M) {
+    glmasr_fp4_weight w[3];
+    for (int i = 0; i < n; ++i) {
+        if (ps[i]->dtype != GLMASR_DTYPE_UINT8 || ps[i]->pre != nullptr || ps[i]->K != ps[0]->K) return false;
+        w[i] = as_weight(*ps[i]);
+    }
+    bool w4a4 = prefer_w4a4();
+    for (int i = 0; i < n && w4a4; ++i)
+        if (ps[i]->scales == nullptr || !(ps[i]->input_scale > 0.0f) || ps[i]->input_scale != ps[0]->input_scale) w4a4 = false;
+    const int rc = glmasr_fp4_linear_fused(w4a4 ? GLMASR_MODE_W4A4 : GLMASR_MODE_W4A16, out, ldo, x, ldx, w, n,
+                                           w4a4 ? ps[0]->input_scale : 1.0f, nullptr, nullptr, epi, nullptr, M, ps[0]->K);
+    return rc == 0;
+}
+
+}  // namespace glmasr
+
+using namespace glmasr;
+
+enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
+    WS_D_HID = 13, WS_D_NORM = 14, WS_D_QKV = 15, WS_D_ATTN = 16, WS_D_ACT = 17, WS_D_SLOT = 18, WS_D_LENS = 19,
+    WS_D_BT = 20, WS_D_ROWS = 21, WS_D_PTRS = 22, WS_D_SCRATCH = 23,
+};
+
+// ============================================================================================
+// reference-named glue entry points
+// ============================================================================================
+extern "C" void rmsnorm(uint16_t *out, const uint16_t *x, const uint16_t *weight, float eps, int rows, int dim) {
+    launch_rmsnorm((__nv_bfloat16 *)out, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)weight, eps, rows, dim,
+                   current_stream());
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void embedding_lookup(uint16_t *out, const uint16_t *table, const int *ids, int n, int dim) {
+    launch_embedding_lookup((__nv_bfloat16 *)out, (const __nv_bfloat16 *)table, ids, n, dim, current_stream());
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void reshape_and_cache(uint16_t *key_cache, uint16_t *value_cache, const uint16_t *key, const uint16_t *value,
+                                  const int64_t *slot_mapping, int num_tokens, int num_kv_heads, int head_dim,
+                                  int block_size) {
+    const int row = num_kv_heads * head_dim;
+    launch_reshape_and_cache((__nv_bfloat16 *)key_cache, (__nv_bfloat16 *)value_cache, (const __nv_bfloat16 *)key, row,
+                             (const __nv_bfloat16 *)value, row, slot_mapping, num_tokens, num_kv_heads, head_dim,
+                             block_size, current_stream());
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void paged_decode_attention(uint16_t *out, const uint16_t *query, const uint16_t *key_cache,
+                                       const uint16_t *value_cache, const int *block_tables, const int *seq_lens,
+                                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                       int max_blocks_per_seq) {
+    const int ld = num_q_heads * head_dim;
+    const bool ok = launch_paged_decode_attention((__nv_bfloat16 *)out, ld, (const __nv_bfloat16 *)query, ld,
+                                                  (const __nv_bfloat16 *)key_cache, (const __nv_bfloat16 *)value_cache,
+                                                  block_tables, seq_lens, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                                  block_size, max_blocks_per_seq, current_stream());
+    GLMASR_CHECK(ok, "paged_decode_attention: unsupported shape (head_dim %d, %d q / %d kv heads)", head_dim,
+                 num_q_heads, num_kv_heads);
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void glmasr_rope_single_token(uint16_t *tensor, const int *positions, int num_seqs, int n_heads,
+                                         int head_dim) {
+    launch_rope_single_token((__nv_bfloat16 *)tensor, n_heads * head_dim, 0, positions, num_seqs, n_heads, head_dim,
+                             current_stream());
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+// ============================================================================================
+// decoder_decode_step_batched
+// ============================================================================================
+extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint16_t **query_ptrs, void *pool_v,
+                                            void *bts_v, int *d_seq_lens, int *h_seq_lens, int num_seqs,
+                                            int *seq_indices, uint16_t *dequant_buf, const void *cfg_v) {
+    (void)handle;
+    (void)dequant_buf;
+    const glmasr_WeightStore *ws = (const glmasr_WeightStore *)ws_v;
+    const glmasr_ModelConfig *cfg = (const glmasr_ModelConfig *)cfg_v;
+    glmasr_KVPool *pool = (glmasr_KVPool *)pool_v;
+    glmasr_BlockTable *bts = (glmasr_BlockTable *)bts_v;
+    if (num_seqs <= 0) return;
+    GLMASR_CHECK(query_ptrs != nullptr, "decoder_decode_step_batched: query_ptrs is NULL");
+    GLMASR_CHECK(pool != nullptr, "decoder_decode_step_batched: pool is NULL");
+    GLMASR_CHECK(bts != nullptr, "decoder_decode_step_batched: bts is NULL");
+    GLMASR_CHECK(d_seq_lens != nullptr, "decoder_decode_step_batched: d_seq_lens is NULL");
+    GLMASR_CHECK(h_seq_lens != nullptr, "decoder_decode_step_batched: h_seq_lens is NULL");
+
+    const int H = cfg->dec_hidden, L = cfg->dec_layers, QH = cfg->dec_heads, KVH = cfg->dec_kv_heads;
+    const int HD = cfg->dec_head_dim, F = cfg->dec_ffn;
+    const int KV = KVH * HD, NQKV = H + 2 * KV, M = num_seqs;
+    GLMASR_CHECK(QH * HD == H, "decoder_decode_step_batched: heads * head_dim != hidden");
+    const ModelRefs &refs = model_refs(ws, L);
+    cudaStream_t st = current_stream();
+
+    // ---- host-side step set-up (reference: decoder.cu:1911-1938) ----
+    std::vector<int64_t> h_slot(M);
+    std::vector<int> h_total(M), h_rows(M);
+    bool contiguous = true;
+    for (int s = 0; s < M; ++s) {
+        const int cached = h_seq_lens[s];
+        GLMASR_CHECK(query_ptrs[s] != nullptr, "decoder_decode_step_batched: query_ptrs[%d] is NULL", s);
+        GLMASR_CHECK(bts[s].h_table != nullptr, "decoder_decode_step_batched: bts[%d].h_table is NULL", s);
+        GLMASR_CHECK(cached >= 0, "decoder_decode_step_batched: negative seq len for seq %d", s);
+        const int logical = cached / pool->block_size;
+        GLMASR_CHECK(logical < bts[s].num_blocks, "decoder_decode_step_batched: seq %d length %d exceeds %d allocated blocks",
+                     s, cached, bts[s].num_blocks);
+        h_slot[s] = (int64_t)bts[s].h_table[logical] * (int64_t)pool->block_size + (int64_t)(cached % pool->block_size);
+        h_total[s] = cached + 1;
+        h_rows[s] = seq_indices ? seq_indices[s] : bts[s].seq_idx;
+        GLMASR_CHECK(h_rows[s] >= 0 && h_rows[s] < pool->max_seqs,
+                     "decoder_decode_step_batched: invalid seq index %d for batch row %d", h_rows[s], s);
+        if (query_ptrs[s] != query_ptrs[0] + (size_t)s * H) contiguous = false;
+    }
+
+    uint16_t *hid = (uint16_t *)workspace_slot(WS_D_HID, (size_t)M * H * 2);
+    uint16_t *nrm = (uint16_t *)workspace_slot(WS_D_NORM, (size_t)M * H * 2);
+    uint16_t *qkv = (uint16_t *)workspace_slot(WS_D_QKV, (size_t)M * NQKV * 2);
+    uint16_t *att = (uint16_t *)workspace_slot(WS_D_ATTN, (size_t)M * H * 2);
+    uint16_t *act = (uint16_t *)workspace_slot(WS_D_ACT, (size_t)M * 2 * F * 2);
+    int64_t *d_slot = (int64_t *)workspace_slot(WS_D_SLOT, (size_t)M * sizeof(int64_t));
+    int *d_total = (int *)workspace_slot(WS_D_LENS, (size_t)M * sizeof(int));
+    int *d_bt = (int *)workspace_slot(WS_D_BT, (size_t)M * pool->max_blocks_per_seq * sizeof(int));
+    int *d_rows = (int *)workspace_slot(WS_D_ROWS, (size_t)M * sizeof(int));
+    uint16_t **d_ptrs = (uint16_t **)workspace_slot(WS_D_PTRS, (size_t)M * sizeof(void *));
+    uint16_t *scratch = (uint16_t *)workspace_slot(WS_D_SCRATCH, (size_t)M * (F > H ? F : H) * 2);
+
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_total, h_total.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_rows, h_rows.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
+    if (contiguous) {
+        GLMASR_CUDA_CHECK(cudaMemcpyAsync(hid, query_ptrs[0], (size_t)M * H * 2, cudaMemcpyDeviceToDevice, st));
+    } else {
+        GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_ptrs, query_ptrs, (size_t)M * sizeof(void *), cudaMemcpyHostToDevice, st));
+        launch_gather_rows((__nv_bfloat16 *)hid, (const __nv_bfloat16 *const *)d_ptrs, M, H, st);
+    }
+    launch_gather_block_tables(d_bt, pool->d_block_tables, d_rows, M, pool->max_blocks_per_seq, st);
+    // the vectors above are pageable host memory: the async copies have completed staging on return
+
+    for (int l = 0; l < L; ++l) {
+        const LayerRef &R = refs.layers[l];
+        __nv_bfloat16 *k_base = (__nv_bfloat16 *)pool->k_cache + (size_t)l * pool->layer_stride;
+        __nv_bfloat16 *v_base = (__nv_bfloat16 *)pool->v_cache + (size_t)l * pool->layer_stride;
+
+        launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st);
+
+        // q | k | v into one [M, H + 2 KV] buffer
+        const ProjRef *qkv_p[3] = {&R.q, &R.k, &R.v};
+        if (!fused_proj(qkv, NQKV, nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) {
+            single_proj(qkv, NQKV, nrm, H, R.q, M, nullptr, scratch);
+            const ProjRef *kv_p[2] = {&R.k, &R.v};
+            if (!fused_proj(qkv + H, NQKV, nrm, H, kv_p, 2, GLMASR_EPI_STORE, M)) {
+                single_proj(qkv + H, NQKV, nrm, H, R.k, M, nullptr, scratch);
+                single_proj(qkv + H + KV, NQKV, nrm, H, R.v, M, nullptr, scratch);
+            }
+        }
+        // RoPE on q and k in place (position = cached length), KV write, attention over cached + 1 tokens
+        launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, 0, d_seq_lens, M, QH, HD, st);
+        launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, H, d_seq_lens, M, KVH, HD, st);
+        launch_reshape_and_cache(k_base, v_base, (const __nv_bfloat16 *)qkv + H, NQKV, (const __nv_bfloat16 *)qkv + H + KV,
+                                 NQKV, d_slot, M, KVH, HD, pool->block_size, st);
+        const bool ok = launch_paged_decode_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV, k_base,
+                                                      v_base, d_bt, d_total, M, QH, KVH, HD, pool->block_size,
+                                                      pool->max_blocks_per_seq, st);
+        GLMASR_CHECK(ok, "decoder_decode_step_batched: unsupported attention shape");
+
+        // o + residual -> hid (residual is the pre-norm hidden state)
+        single_proj(hid, H, att, H, R.o, M, hid, scratch);
+
+        launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st);
+        const ProjRef *gu_p[2] = {&R.gate, &R.up};
+        if (!fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
+            single_proj(act, F, nrm, H, R.gate, M, nullptr, scratch);
+            single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
+            silu_elementwise_mul(act, act + (size_t)M * F, M * F);
+        }
+        single_proj(hid, H, act, F, R.down, M, hid, scratch);
+    }
+
+    launch_rmsnorm((__nv_bfloat16 *)hid, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)refs.final_norm, 1e-5f, M, H, st);
+    if (contiguous) {
+        GLMASR_CUDA_CHECK(cudaMemcpyAsync(query_ptrs[0], hid, (size_t)M * H * 2, cudaMemcpyDeviceToDevice, st));
+    } else {
+        launch_scatter_rows((__nv_bfloat16 *const *)d_ptrs, (const __nv_bfloat16 *)hid, M, H, st);
+    }
+    for (int s = 0; s < M; ++s) h_seq_lens[s] = h_total[s];
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_seq_lens, d_total, (size_t)M * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" void glmasr_decoder_forget_weights(void) { forget_model_refs(); }

@@ -32,6 +32,7 @@
 #include <stdint.h>
 
 #include "fp4_format.cuh"
+#include "gemm_device.cuh"
 #include "gemm_umma.cuh"
 #include "ptx.cuh"
 
@@ -79,136 +80,6 @@ struct Cfg {
     static_assert(TMEM_NEEDED <= 512, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
-
-struct SubTile {
-    int seg;        // weight tensor
-    int row0;       // first weight row of the 128-row sub-tile (may lie past the tensor: zero-filled)
-    int col0;       // first output column
-    int ncols;      // valid output columns (0..128)
-};
-
-__device__ __forceinline__ SubTile resolve_subtile(const GemmParams &p, int n_tile, int h, int nb) {
-    SubTile t;
-    if (p.epi == EPI_SILU_GATE) {
-        t.seg = h;
-        t.row0 = n_tile * 128;
-        t.col0 = n_tile * 128;
-        t.ncols = min(128, p.seg_rows[0] - t.row0);
-        return t;
-    }
-    int g = n_tile * nb + h;
-    int seg = 0, col = 0;
-    while (seg < p.num_segs - 1 && g >= p.seg_subtiles[seg]) {
-        g -= p.seg_subtiles[seg];
-        col += p.seg_rows[seg];
-        ++seg;
-    }
-    t.seg = seg;
-    t.row0 = g * 128;
-    t.col0 = col + g * 128;
-    t.ncols = max(0, min(128, p.seg_rows[seg] - t.row0));
-    return t;
-}
-
-// ---- shared-memory access by 32-bit shared address ---------------------------------------
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
-// ---- W4A16 dequant: 8 e2m1 nibbles (one 32-bit word) times one block scale -> 8 bf16 ------
-// e2m1x2 -> f16x2 is a hardware conversion; an f16 pattern shifted right by 3 reads as a bf16
-// of value v * 2^-112 (zero stays zero), so one bf16x2 multiply by (scale * 2^112) yields the
-// exact product lut*scale (6 significant bits) as bf16.
-__device__ __forceinline__ uint32_t e2m1x2_to_scaled_bf16x2(uint32_t byte, __nv_bfloat162 s2) {
-    const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
-    const uint32_t hb = (uint32_t)h.x | ((uint32_t)h.y << 16);
-    const uint32_t t = ((hb >> 3) & 0x0FFF0FFFu) | (hb & 0x80008000u);
-    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&t), s2);
-    return *reinterpret_cast<const uint32_t *>(&r);
-}
-__device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 s2) {
-    uint4 o;
-    o.x = e2m1x2_to_scaled_bf16x2(w & 0xFFu, s2);
-    o.y = e2m1x2_to_scaled_bf16x2((w >> 8) & 0xFFu, s2);
-    o.z = e2m1x2_to_scaled_bf16x2((w >> 16) & 0xFFu, s2);
-    o.w = e2m1x2_to_scaled_bf16x2(w >> 24, s2);
-    return o;
-}
-__device__ __forceinline__ __nv_bfloat162 block_scale_bf16x2(uint32_t scale_byte) {
-    // e4m3 decoded as the reference does (no NaN pattern), times 2^112; exact in bf16.
-    const float s = e4m3_to_float_ref(scale_byte) * 5.192296858534828e33f;  // 2^112
-    return __floats2bfloat162_rn(s, s);
-}
-
-// ---- epilogue helpers ----------------------------------------------------------------------
-__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
-
-__device__ __forceinline__ void store_row_chunk(__nv_bfloat16 *dst, const float (&v)[32], int nvalid) {
-    if (nvalid >= 32 && (((uintptr_t)dst & 15) == 0)) {
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-            w[i] = *reinterpret_cast<const uint32_t *>(&b);
-        }
-        if (((uintptr_t)dst & 31) == 0) {
-            // 32-byte stores: every store fills a whole 32-byte L2 sector
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * i),
-                             "r"(w[8 * i]), "r"(w[8 * i + 1]), "r"(w[8 * i + 2]), "r"(w[8 * i + 3]), "r"(w[8 * i + 4]),
-                             "r"(w[8 * i + 5]), "r"(w[8 * i + 6]), "r"(w[8 * i + 7])
-                             : "memory");
-        } else {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (i < nvalid) dst[i] = __float2bfloat16(v[i]);
-    }
-}
-
-__device__ __forceinline__ void load_row_chunk(const __nv_bfloat16 *src, float (&v)[32], int nvalid) {
-    if (nvalid >= 32 && (((uintptr_t)src & 15) == 0)) {
-        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 q = s4[i];
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
-                v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
-            }
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = i < nvalid ? __bfloat162float(src[i]) : 0.0f;
-    }
-}
-
-__device__ __forceinline__ float silu_gate(float g, float u) {
-    // same operation order as the reference SiLU-gate (Infer-engine/cuda/kernels.cu:1259-1263)
-    const float sig = __fdiv_rn(1.0f, 1.0f + expf(-g));
-    return (g * sig) * u;
-}
-
-// cycle accounting for timing experiments (debug & 64): T0 opens an interval, ACC closes it into a counter
-#define DBG_T0() long long _t0 = dbg ? clock64() : 0
-#define DBG_ACC(slot) do { if (dbg) { long long _t1 = clock64(); dbg_acc[slot] += (unsigned long long)(_t1 - _t0); _t0 = _t1; } } while (0)
 
 // ---------------------------------------------------------------------------------------------
 template <int MODE, int NB>

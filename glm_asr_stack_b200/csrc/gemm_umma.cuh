@@ -27,6 +27,8 @@ struct alignas(64) GemmParams {
     CUtensorMap tm_a;                   // activations, 128-row x 128-byte boxes, 128B swizzle
     CUtensorMap tm_b[kMaxSegments];     // weights (packed e2m1 bytes, or bf16), same box
     CUtensorMap tm_bs[kMaxSegments];    // W4A16: row-major e4m3 scales [N_s, K/16], 128-row x 16-byte boxes
+    CUtensorMap tm_sfa;                 // W4A4 pair kernel: tiled activation scales as [chunks, 128 x u32], 4-chunk boxes
+    CUtensorMap tm_sfb[kMaxSegments];   // W4A4 pair kernel: tiled weight scales, same view
     const uint8_t *sfa;                 // W4A4: activation scales, 128x4-tiled
     const uint8_t *sfb[kMaxSegments];   // W4A4: weight scales, 128x4-tiled
     float alpha[kMaxSegments];          // applied to the fp32 accumulator of that segment
@@ -47,6 +49,10 @@ struct alignas(64) GemmParams {
     int debug;                          // timing experiments only (GLMASR_DEBUG_FLAGS); 0 in normal use
     unsigned long long *dbg_cycles;     // debug & 64: per-CTA cycle counters [gridDim.x][16]
 };
+
+// W4A4 on CTA pairs (cta_group::2): 256 x 256 tiles, one cluster of two CTAs per tile.
+cudaError_t launch_umma_gemm_pair(const GemmParams &p, int num_pairs, cudaStream_t st);
+cudaError_t umma_gemm_pair_init();
 
 // nb = 128-row weight sub-tiles per CTA tile (1 or 2).  Returns cudaSuccess or the launch error.
 cudaError_t launch_umma_gemm(int mode, int nb, const GemmParams &p, int num_ctas, cudaStream_t st);

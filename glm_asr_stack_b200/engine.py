@@ -1,0 +1,152 @@
+"""ctypes mirrors of the engine structures that cross the decode entry points, and helpers that
+build them from torch tensors (reference: Infer-engine/include/types.h, kv_pool.h; C layout in
+include/glmasr_engine_types.h).  Used by the tests and the benchmark to call
+``decoder_decode_step_batched`` exactly as the engine's ``decode_batch`` does
+(Infer-engine/src/engine.c:1880-1982).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_int, c_int64, c_size_t, c_void_p
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib
+from .weights import DTYPE_BF16, DTYPE_FP32, DTYPE_FP8, DTYPE_UINT8
+
+MAX_DIMS = 4
+MAX_WEIGHTS = 2048
+
+
+class CTensor(Structure):
+    _fields_ = [("data", c_void_p), ("dtype", c_int), ("ndim", c_int), ("shape", c_int64 * MAX_DIMS),
+                ("nbytes", c_size_t)]
+
+
+class CModelConfig(Structure):
+    _fields_ = [(n, c_int) for n in ("enc_hidden", "enc_layers", "enc_heads", "enc_head_dim", "enc_ffn",
+                                     "num_mel_bins", "max_audio_frames", "proj_mid", "dec_hidden", "dec_layers",
+                                     "dec_heads", "dec_kv_heads", "dec_head_dim", "dec_ffn", "vocab_size",
+                                     "max_position_embeddings", "audio_token_id")] + \
+               [("eos_ids", c_int * 4), ("pad_token_id", c_int), ("max_new_tokens", c_int)]
+
+
+class CWeightStore(Structure):
+    _fields_ = [("names", c_char_p * MAX_WEIGHTS), ("tensors", CTensor * MAX_WEIGHTS), ("count", c_int)]
+
+
+class CKVPool(Structure):
+    _fields_ = [("k_cache", c_void_p), ("v_cache", c_void_p), ("d_block_tables", c_void_p), ("max_seqs", c_int),
+                ("max_blocks_per_seq", c_int), ("free_stack", POINTER(c_int)), ("free_top", c_int),
+                ("num_blocks", c_int), ("block_size", c_int), ("num_layers", c_int), ("kv_heads", c_int),
+                ("head_dim", c_int), ("kv_head_stride", c_int), ("block_stride", c_int), ("layer_stride", c_int),
+                ("per_layer_bytes", c_size_t)]
+
+
+class CBlockTable(Structure):
+    _fields_ = [("d_table", c_void_p), ("max_blocks", c_int), ("num_blocks", c_int), ("h_table", POINTER(c_int)),
+                ("seq_idx", c_int)]
+
+
+_TAGS = {torch.float32: DTYPE_FP32, torch.bfloat16: DTYPE_BF16, torch.uint8: DTYPE_UINT8,
+         torch.float8_e4m3fn: DTYPE_FP8}
+
+
+class WeightStore:
+    """Owns the tensors and the C ``WeightStore`` that points at them."""
+
+    def __init__(self):
+        self.c = CWeightStore()
+        self.c.count = 0
+        self.keep: Dict[str, torch.Tensor] = {}
+
+    def add(self, name: str, t: torch.Tensor, dtype: Optional[int] = None):
+        i = self.c.count
+        assert i < MAX_WEIGHTS
+        self.keep[name] = t
+        self.c.names[i] = name.encode()
+        ct = self.c.tensors[i]
+        ct.data = t.data_ptr()
+        ct.dtype = _TAGS[t.dtype] if dtype is None else dtype
+        ct.ndim = t.dim()
+        for d in range(t.dim()):
+            ct.shape[d] = t.shape[d]
+        ct.nbytes = t.numel() * t.element_size()
+        self.c.count = i + 1
+
+    def add_fp4(self, prefix: str, w, input_scale: Optional[float] = None):
+        """The five tensors of one FP4 projection under the checkpoint's names."""
+        dev = w.w_packed.device
+        self.add(f"{prefix}.weight", w.w_packed)
+        self.add(f"{prefix}.weight_scale", w.w_scales, DTYPE_FP8)
+        self.add(f"{prefix}.weight_scale_2", torch.tensor([w.w_global_scale], dtype=torch.float32, device=dev))
+        if input_scale is not None:
+            self.add(f"{prefix}.input_scale", torch.tensor([input_scale], dtype=torch.float32, device=dev))
+
+
+def model_config(hidden=2048, layers=28, heads=16, kv_heads=4, head_dim=128, ffn=6144, vocab=59264) -> CModelConfig:
+    c = CModelConfig()
+    c.dec_hidden, c.dec_layers, c.dec_heads, c.dec_kv_heads = hidden, layers, heads, kv_heads
+    c.dec_head_dim, c.dec_ffn, c.vocab_size = head_dim, ffn, vocab
+    c.max_position_embeddings = 8192
+    return c
+
+
+class KVPool:
+    """Paged KV pool with the reference's layout (Infer-engine/src/kv_pool.c:35-120): K and V each one
+    allocation [layers][num_blocks][block_size][kv_heads][head_dim] bf16, device block tables
+    [max_seqs, max_blocks_per_seq] int32, a host LIFO of free block ids."""
+
+    def __init__(self, num_blocks, block_size, num_layers, kv_heads, head_dim, max_seqs, max_blocks_per_seq,
+                 device="cuda"):
+        row = kv_heads * head_dim
+        self.k = torch.zeros((num_layers, num_blocks, block_size, row), dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.tables = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32, device=device)
+        self.free = list(range(num_blocks - 1, -1, -1))
+        self._stack = (c_int * num_blocks)(*range(num_blocks))
+        c = CKVPool()
+        c.k_cache, c.v_cache, c.d_block_tables = self.k.data_ptr(), self.v.data_ptr(), self.tables.data_ptr()
+        c.max_seqs, c.max_blocks_per_seq = max_seqs, max_blocks_per_seq
+        c.free_stack = ctypes.cast(self._stack, POINTER(c_int))
+        c.free_top, c.num_blocks, c.block_size, c.num_layers = num_blocks, num_blocks, block_size, num_layers
+        c.kv_heads, c.head_dim, c.kv_head_stride = kv_heads, head_dim, row
+        c.block_stride = block_size * row
+        c.layer_stride = num_blocks * block_size * row
+        c.per_layer_bytes = num_blocks * block_size * row * 2
+        self.c = c
+        self.block_size, self.max_blocks_per_seq = block_size, max_blocks_per_seq
+
+
+class BlockTables:
+    """``BlockTable[num_seqs]`` with host mirrors; row i of the pool's device table belongs to sequence i."""
+
+    def __init__(self, pool: KVPool, tables: List[List[int]]):
+        n = len(tables)
+        self.arr = (CBlockTable * n)()
+        self._host = []
+        host = torch.full((n, pool.max_blocks_per_seq), -1, dtype=torch.int32)
+        for i, blocks in enumerate(tables):
+            h = (c_int * pool.max_blocks_per_seq)(*([-1] * pool.max_blocks_per_seq))
+            for j, b in enumerate(blocks):
+                h[j] = b
+                host[i, j] = b
+            self._host.append(h)
+            bt = self.arr[i]
+            bt.d_table = pool.tables.data_ptr() + i * pool.max_blocks_per_seq * 4
+            bt.max_blocks, bt.num_blocks = pool.max_blocks_per_seq, len(blocks)
+            bt.h_table = ctypes.cast(h, POINTER(c_int))
+            bt.seq_idx = i
+        pool.tables[:n].copy_(host.to(pool.tables.device))
+
+
+def decode_step(ws: WeightStore, cfg: CModelConfig, pool: KVPool, bts: BlockTables, hidden: torch.Tensor,
+                d_seq_lens: torch.Tensor, h_seq_lens):
+    """Call decoder_decode_step_batched on a contiguous [num_seqs, hidden] batch (updated in place).
+    h_seq_lens: ctypes int array (updated in place)."""
+    lib = _lib.load()
+    n = hidden.shape[0]
+    ptrs = (c_void_p * n)(*[hidden.data_ptr() + i * hidden.shape[1] * 2 for i in range(n)])
+    lib.decoder_decode_step_batched(None, ctypes.byref(ws.c), ptrs, ctypes.byref(pool.c), bts.arr,
+                                    c_void_p(d_seq_lens.data_ptr()), h_seq_lens, n, None, None, ctypes.byref(cfg))

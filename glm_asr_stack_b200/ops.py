@@ -7,6 +7,7 @@ torch is used only for device memory; every computation happens inside libglmasr
 from __future__ import annotations
 
 import ctypes
+import weakref
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -20,6 +21,30 @@ MODE_W4A16 = 1
 EPI_STORE = 0
 EPI_SILU_GATE = 1
 EPI_RESIDUAL = 2
+
+
+_tracked = {}
+
+
+def _forget(ptr: int):
+    _tracked.pop(ptr, None)
+    try:
+        _lib.load().glmasr_fp4_forget(ctypes.c_void_p(ptr))
+    except Exception:
+        pass
+
+
+def _track_scales(w_scales: Optional[torch.Tensor]):
+    """The library caches the re-tiled copy of a weight's scales by device pointer.  torch may
+    hand the same address to a different tensor later, so drop the cache entry when the tensor
+    that owned the address goes away (the C host calls glmasr_fp4_forget from safetensors_free)."""
+    if w_scales is None:
+        return
+    ptr = w_scales.data_ptr()
+    fin = _tracked.get(ptr)
+    if fin is not None and fin.alive:
+        return
+    _tracked[ptr] = weakref.finalize(w_scales, _forget, ptr)
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -104,6 +129,7 @@ def nvfp4_linear(out: torch.Tensor, x: torch.Tensor, w_packed: torch.Tensor, w_s
     Returns 0 on success, -1 when the reference would (bad sizes, missing scales, K % 16,
     input_scale <= 0); ``out`` is untouched in that case."""
     lib = _lib.load()
+    _track_scales(w_scales)
     M = x.shape[0] if M is None else M
     K = x.shape[1] if K is None else K
     N = w_packed.shape[0] if N is None else N
@@ -180,6 +206,45 @@ def lm_head_argmax_batched(hidden: torch.Tensor, lm_weight: torch.Tensor) -> tor
     return tokens
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None):
+    """reference: rmsnorm, Infer-engine/cuda/kernels.cu:252-295."""
+    lib = _lib.load()
+    _check(x, torch.bfloat16, "x")
+    out = torch.empty_like(x) if out is None else out
+    lib.rmsnorm(_ptr(out), _ptr(x), _ptr(weight), float(eps), x.shape[0], x.shape[1])
+    return out
+
+
+def embedding_lookup(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """reference: embedding_lookup, Infer-engine/cuda/kernels.cu:712-736 (ids int32 on the device)."""
+    lib = _lib.load()
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.bfloat16, device=table.device)
+    lib.embedding_lookup(_ptr(out), _ptr(table), _ptr(ids), ids.numel(), table.shape[1])
+    return out
+
+
+def rope_single_token(t: torch.Tensor, positions: torch.Tensor, n_heads: int, head_dim: int) -> torch.Tensor:
+    """In place; reference: rope_batched_single_token_kernel, Infer-engine/cuda/decoder.cu:605-632."""
+    _lib.load().glmasr_rope_single_token(_ptr(t), _ptr(positions), t.shape[0], n_heads, head_dim)
+    return t
+
+
+def reshape_and_cache(k_cache, v_cache, key, value, slot_mapping, num_kv_heads, head_dim, block_size):
+    """reference: reshape_and_cache, Infer-engine/cuda/paged_kv.cu:70-97, 424-438."""
+    _lib.load().reshape_and_cache(_ptr(k_cache), _ptr(v_cache), _ptr(key), _ptr(value), _ptr(slot_mapping),
+                                  key.shape[0], num_kv_heads, head_dim, block_size)
+
+
+def paged_decode_attention(query, k_cache, v_cache, block_tables, seq_lens, num_q_heads, num_kv_heads, head_dim,
+                           block_size) -> torch.Tensor:
+    """reference: paged_decode_attention, Infer-engine/cuda/paged_kv.cu:440-519."""
+    out = torch.empty_like(query)
+    _lib.load().paged_decode_attention(_ptr(out), _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                       _ptr(seq_lens), query.shape[0], num_q_heads, num_kv_heads, head_dim,
+                                       block_size, block_tables.shape[1])
+    return out
+
+
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     lib = _lib.load()
     _check(logits, torch.bfloat16, "logits")
@@ -235,6 +300,8 @@ def fp4_linear_fused(mode: int, x: torch.Tensor, weights: Sequence[Fp4Tensor], e
     n_out = weights[0].N if epilogue == EPI_SILU_GATE else sum(w.N for w in weights)
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    for w in weights:
+        _track_scales(w.w_scales)
     arr = (Fp4Weight * len(weights))(*[w.c_struct() for w in weights])
     scratch = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if (
         pre_quant_scale is not None and mode == MODE_W4A16) else None
@@ -247,6 +314,8 @@ def fp4_linear_fused(mode: int, x: torch.Tensor, weights: Sequence[Fp4Tensor], e
 
 
 def make_layer_weights(q, k, v, o, gate, up, down, hidden: int, ffn: int) -> LayerWeights:
+    for w in (q, k, v, o, gate, up, down):
+        _track_scales(w.w_scales)
     return LayerWeights(q.c_struct(), k.c_struct(), v.c_struct(), o.c_struct(), gate.c_struct(), up.c_struct(),
                         down.c_struct(), float(q.input_scale), float(o.input_scale), float(gate.input_scale),
                         float(down.input_scale), hidden, ffn)
@@ -301,6 +370,7 @@ def set_stream(stream: Optional[torch.cuda.Stream]):
 
 
 def prepack(w: Fp4Tensor) -> int:
+    _track_scales(w.w_scales)
     return _lib.load().glmasr_fp4_prepack(_ptr(w.w_scales), w.N, w.K)
 
 

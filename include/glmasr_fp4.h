@@ -88,7 +88,44 @@ void lm_head_argmax_batched(void *handle, const uint16_t *hidden, const uint16_t
 /* Infer-engine/include/cuda_kernels.h:182, Infer-engine/cuda/kernels.cu:1461-1475. */
 void lm_head_cleanup(void);
 
+/* ---- decode step and its glue (layout of the structs: include/glmasr_engine_types.h) ---- */
+
+/* Infer-engine/include/cuda_kernels.h:23-24, Infer-engine/cuda/kernels.cu:252-295.  Bit-exact
+ * (same summation order as the reference's one-warp-per-row kernel); out may alias x. */
+void rmsnorm(uint16_t *out, const uint16_t *x, const uint16_t *weight, float eps, int rows, int dim);
+
+/* Infer-engine/include/cuda_kernels.h:42-43, Infer-engine/cuda/kernels.cu:712-736. */
+void embedding_lookup(uint16_t *out, const uint16_t *table, const int *ids, int n, int dim);
+
+/* Infer-engine/cuda/paged_kv.cu:424-438 (kernel :70-97): scatter K/V rows [num_tokens, kv_heads*head_dim]
+ * to slot_mapping[token] = block * block_size + offset of the paged cache. */
+void reshape_and_cache(uint16_t *key_cache, uint16_t *value_cache, const uint16_t *key, const uint16_t *value,
+                       const int64_t *slot_mapping, int num_tokens, int num_kv_heads, int head_dim,
+                       int block_size);
+
+/* Infer-engine/cuda/paged_kv.cu:440-519 (kernels :99-422): paged GQA decode attention, one query
+ * token per sequence, scale 1/sqrt(head_dim), seq_lens counts the tokens to attend to.
+ * head_dim must be 128 and q heads a multiple (<= 8x) of kv heads, otherwise exit(1). */
+void paged_decode_attention(uint16_t *out, const uint16_t *query, const uint16_t *key_cache,
+                            const uint16_t *value_cache, const int *block_tables, const int *seq_lens,
+                            int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                            int max_blocks_per_seq);
+
+/* Infer-engine/include/cuda_kernels.h:164-170, Infer-engine/cuda/decoder.cu:1849-2173.
+ * ws: WeightStore*, cfg: ModelConfig*, pool: KVPool*, bts: BlockTable[num_seqs]; handle and
+ * dequant_buf are ignored.  GLMASR_USE_CUTLASS_NVFP4 selects W4A4 as in the reference. */
+void decoder_decode_step_batched(void *handle, const void *ws, uint16_t **query_ptrs, void *pool, void *bts,
+                                 int *d_seq_lens, int *h_seq_lens, int num_seqs, int *seq_indices,
+                                 uint16_t *dequant_buf, const void *cfg);
+
 /* ======================= 2. additive entry points ======================= */
+
+/* Rotate-half RoPE (theta 10000) of one new token per sequence, in place on [num_seqs, n_heads*head_dim],
+ * position = positions[seq] (the reference's rope_batched_single_token_kernel,
+ * Infer-engine/cuda/decoder.cu:605-632, which has no host entry point of its own). */
+void glmasr_rope_single_token(uint16_t *tensor, const int *positions, int num_seqs, int n_heads, int head_dim);
+/* Forget the per-layer pointer table built from a WeightStore (call before freeing the store). */
+void glmasr_decoder_forget_weights(void);
 
 #define GLMASR_MODE_W4A4  0   /* nvfp4_linear arithmetic */
 #define GLMASR_MODE_W4A16 1   /* fp4_linear arithmetic   */

@@ -32,6 +32,12 @@ class RefLib:
         for f in (L.fp4_dequant_to_bf16, L.fp4_linear, L.bf16_linear, L.silu_mul_split_packed, L.residual_add,
                   L.lm_head_argmax_batched):
             f.restype = None
+        L.rmsnorm.argtypes = [P, P, P, c_float, c_int, c_int]
+        L.rmsnorm.restype = None
+        L.reshape_and_cache.argtypes = [P, P, P, P, P, c_int, c_int, c_int, c_int]
+        L.reshape_and_cache.restype = None
+        L.paged_decode_attention.argtypes = [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]
+        L.paged_decode_attention.restype = None
         # the reference's fp4_linear / bf16_linear take a cublasHandle_t
         self.cublas = ctypes.CDLL("libcublas.so.12")
         self.handle = c_void_p()
@@ -72,6 +78,24 @@ class RefLib:
                                    self._p(scales), input_scale, g, self._p(pre), None, M, N, K)
         torch.cuda.synchronize()
         return rc, out
+
+    def rmsnorm(self, x, w, eps=1e-5):
+        out = torch.empty_like(x)
+        self.lib.rmsnorm(self._p(out), self._p(x), self._p(w), eps, x.shape[0], x.shape[1])
+        torch.cuda.synchronize()
+        return out
+
+    def reshape_and_cache(self, kc, vc, k, v, slots, kv_heads, head_dim, block_size):
+        self.lib.reshape_and_cache(self._p(kc), self._p(vc), self._p(k), self._p(v), self._p(slots), k.shape[0],
+                                   kv_heads, head_dim, block_size)
+        torch.cuda.synchronize()
+
+    def paged_decode_attention(self, q, kc, vc, bt, lens, qh, kvh, hd, bs):
+        out = torch.empty_like(q)
+        self.lib.paged_decode_attention(self._p(out), self._p(q), self._p(kc), self._p(vc), self._p(bt), self._p(lens),
+                                        q.shape[0], qh, kvh, hd, bs, bt.shape[1])
+        torch.cuda.synchronize()
+        return out
 
     def silu_mul_split_packed(self, packed):
         M, N2 = packed.shape

@@ -1,0 +1,228 @@
+"""GPU parity of the decode step's glue kernels and of decoder_decode_step_batched, against the CPU
+oracle and (where oracle/_ref is built) the reference's own kernels on the same inputs.
+
+Tolerances: RMSNorm, KV write, embedding are bit-exact; RoPE is compared within one bf16 ulp (numpy's
+float32 cos/sin/pow are not CUDA's); attention and the whole step are floating point with a different
+summation order: relative error <= 1e-2 (the path's stated bar), in practice ~2e-3.
+"""
+import ctypes
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import decoder_oracle as do
+import fp4_oracle as o
+import ref_lib
+from conftest import ROOT
+from gpu_util import REL_TOL_TIGHT, REL_TOL_VS_ORACLE, bits_of, to_dev_bf16, ulp_diff
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from glm_asr_stack_b200 import ops as _ops
+    return _ops
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return ref_lib.RefLib() if ref_lib.available() else None
+
+
+def rnd_bits(rng, shape, scale=1.0):
+    return o.f32_to_bf16_bits((rng.standard_normal(shape) * scale).astype(np.float32))
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 2048), (7, 256), (256, 2048), (3, 96)])
+def test_rmsnorm_bit_exact(ops, ref, rows, dim):
+    rng = np.random.default_rng(rows)
+    x, w = rnd_bits(rng, (rows, dim), 3.0), rnd_bits(rng, (dim,), 1.0)
+    got = bits_of(ops.rmsnorm(to_dev_bf16(x), to_dev_bf16(w)))
+    assert np.array_equal(got, do.rmsnorm(x, w))
+    if ref is not None:
+        assert np.array_equal(got, bits_of(ref.rmsnorm(to_dev_bf16(x), to_dev_bf16(w))))
+    xd = to_dev_bf16(x)
+    ops.rmsnorm(xd, to_dev_bf16(w), out=xd)                 # in place, as the decoder drivers call it
+    assert np.array_equal(bits_of(xd), got)
+
+
+def test_rope_single_token(ops):
+    rng = np.random.default_rng(1)
+    n, heads, hd = 9, 16, 128
+    t = rnd_bits(rng, (n, heads * hd))
+    pos = np.array([0, 1, 2, 17, 200, 449, 650, 4095, 8191], np.int32)
+    got = bits_of(ops.rope_single_token(to_dev_bf16(t), torch.from_numpy(pos).cuda(), heads, hd))
+    want = do.rope_single_token(t, pos, heads, hd)
+    assert ulp_diff(got, want).max() <= 1 or o.rel_err(got, want) < 2e-3
+    assert np.array_equal(got[0], t[0])                      # position 0 is the identity
+
+
+def _paged_case(rng, n_seqs, kvh, hd, bs, max_ctx, num_blocks):
+    lens = rng.integers(1, max_ctx + 1, n_seqs).astype(np.int32)
+    lens[0] = 1
+    max_blocks = (max_ctx + bs - 1) // bs + 1
+    perm = rng.permutation(num_blocks)
+    bt = np.full((n_seqs, max_blocks), -1, np.int32)
+    used = 0
+    for s in range(n_seqs):
+        nb = (lens[s] + bs - 1) // bs
+        bt[s, :nb] = perm[used:used + nb]
+        used += nb
+    assert used <= num_blocks
+    kc = rnd_bits(rng, (num_blocks * bs, kvh * hd))
+    vc = rnd_bits(rng, (num_blocks * bs, kvh * hd))
+    return lens, bt, kc, vc
+
+
+@pytest.mark.parametrize("qh,kvh,bs", [(16, 4, 16), (8, 8, 16), (16, 4, 128), (4, 1, 8)])
+def test_paged_decode_attention(ops, ref, qh, kvh, bs):
+    rng = np.random.default_rng(qh * 100 + bs)
+    hd, n = 128, 12
+    lens, bt, kc, vc = _paged_case(rng, n, kvh, hd, bs, 450, 500 * 16 // bs + n)
+    lens[1] = 0                                              # empty sequence -> zeros
+    q = rnd_bits(rng, (n, qh * hd))
+    args = (to_dev_bf16(q), to_dev_bf16(kc), to_dev_bf16(vc), torch.from_numpy(bt).cuda(), torch.from_numpy(lens).cuda())
+    got = bits_of(ops.paged_decode_attention(*args, qh, kvh, hd, bs))
+    want = do.paged_decode_attention(q, kc, vc, bt, lens, qh, kvh, hd, bs)
+    assert o.rel_err(got, want) <= REL_TOL_TIGHT
+    assert not got[1].any()
+    if ref is not None:
+        r = bits_of(ref.paged_decode_attention(*args, qh, kvh, hd, bs))
+        assert o.rel_err(r, want) <= REL_TOL_TIGHT           # pins the oracle to the reference kernel
+        assert o.rel_err(got, r) <= REL_TOL_TIGHT
+
+
+def test_paged_attention_masks_negative_blocks(ops):
+    rng = np.random.default_rng(5)
+    qh, kvh, hd, bs, n = 16, 4, 128, 16, 3
+    lens, bt, kc, vc = _paged_case(rng, n, kvh, hd, bs, 100, 64)
+    lens[:] = 40
+    bt[:, :3] = rng.permutation(64)[:9].reshape(3, 3)
+    bt[2, 1] = -1                                            # a hole in the table: its 16 tokens are skipped
+    q = rnd_bits(rng, (n, qh * hd))
+    got = bits_of(ops.paged_decode_attention(to_dev_bf16(q), to_dev_bf16(kc), to_dev_bf16(vc),
+                                             torch.from_numpy(bt).cuda(), torch.from_numpy(lens).cuda(), qh, kvh, hd, bs))
+    assert o.rel_err(got, do.paged_decode_attention(q, kc, vc, bt, lens, qh, kvh, hd, bs)) <= REL_TOL_TIGHT
+
+
+def test_reshape_and_cache_bit_exact(ops, ref):
+    rng = np.random.default_rng(6)
+    kvh, hd, bs, nblk, n = 4, 128, 16, 20, 33
+    slots = rng.permutation(nblk * bs)[:n].astype(np.int64)
+    k, v = rnd_bits(rng, (n, kvh * hd)), rnd_bits(rng, (n, kvh * hd))
+    kc = np.zeros((nblk * bs, kvh * hd), np.uint16)
+    vc = np.zeros_like(kc)
+    do.reshape_and_cache(kc, vc, k, v, slots)
+    kd, vd = torch.zeros((nblk * bs, kvh * hd), dtype=torch.bfloat16, device="cuda"), None
+    vd = torch.zeros_like(kd)
+    ops.reshape_and_cache(kd, vd, to_dev_bf16(k), to_dev_bf16(v), torch.from_numpy(slots).cuda(), kvh, hd, bs)
+    assert np.array_equal(bits_of(kd), kc) and np.array_equal(bits_of(vd), vc)
+    if ref is not None:
+        kr, vr = torch.zeros_like(kd), torch.zeros_like(kd)
+        ref.reshape_and_cache(kr, vr, to_dev_bf16(k), to_dev_bf16(v), torch.from_numpy(slots).cuda(), kvh, hd, bs)
+        assert torch.equal(kr, kd) and torch.equal(vr, vd)
+
+
+def test_embedding_lookup(ops):
+    rng = np.random.default_rng(7)
+    table = rnd_bits(rng, (100, 256))
+    ids = np.array([5, 0, 99, 5, 42], np.int32)
+    got = bits_of(ops.embedding_lookup(to_dev_bf16(table), torch.from_numpy(ids).cuda()))
+    assert np.array_equal(got, table[ids])
+
+
+# ---------------------------------------------------------------------------------------------
+# whole decode step on a small model (hidden 256 = 2 heads x 128, 1 kv head, ffn 512, 2 layers)
+# ---------------------------------------------------------------------------------------------
+def run_decode_step_case(w4a4: bool):
+    from glm_asr_stack_b200 import engine, ops
+    rng = np.random.default_rng(11)
+    H, F, QH, KVH, HD, L, bs, n = 256, 512, 2, 1, 128, 2, 16, 5
+    cached = np.array([0, 15, 16, 37, 200], np.int32)
+    num_blocks, max_blocks = 64, 16
+    names = [("self_attn.q_proj", H, H), ("self_attn.k_proj", KVH * HD, H), ("self_attn.v_proj", KVH * HD, H),
+             ("self_attn.o_proj", H, H), ("mlp.gate_proj", F, H), ("mlp.up_proj", F, H), ("mlp.down_proj", H, F)]
+    ws = engine.WeightStore()
+    layers = []
+    isc = 0.02
+    for l in range(L):
+        Lw = {}
+        for i, (nm, N, K) in enumerate(names):
+            pw, sw, g = o.seeded_weight(N, K, 100 * l + i)
+            w = ops.Fp4Tensor(torch.from_numpy(pw).cuda(), torch.from_numpy(sw).cuda(), g)
+            ws.add_fp4(f"language_model.model.layers.{l}.{nm}", w, isc)
+            Lw[nm.split(".")[1].split("_")[0]] = (pw, sw, g)
+        for nm in ("input_layernorm", "post_attention_layernorm"):
+            nb = rnd_bits(rng, (H,), 0.2) + 0                                   # weights around 0 -> add 1 below
+            nb = o.f32_to_bf16_bits(o.bf16_bits_to_f32(nb) + 1.0)
+            ws.add(f"language_model.model.layers.{l}.{nm}.weight", to_dev_bf16(nb))
+            Lw["norm1" if nm == "input_layernorm" else "norm2"] = nb
+        layers.append(Lw)
+    fn = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
+    ws.add("language_model.model.norm.weight", to_dev_bf16(fn))
+    cfg = engine.model_config(H, L, QH, KVH, HD, F, 1000)
+    pool = engine.KVPool(num_blocks, bs, L, KVH, HD, max_seqs=8, max_blocks_per_seq=max_blocks)
+    # block tables: enough blocks for cached + 1 tokens, taken from a permutation
+    perm = rng.permutation(num_blocks).tolist()
+    tables = []
+    for c in cached:
+        nb = (int(c) + 1 + bs - 1) // bs
+        tables.append([perm.pop() for _ in range(nb)])
+    bts = engine.BlockTables(pool, tables)
+    bt_np = np.full((n, max_blocks), -1, np.int32)
+    for i, t in enumerate(tables):
+        bt_np[i, :len(t)] = t
+    # pre-existing cache contents
+    kc0 = rnd_bits(rng, (L, num_blocks * bs, KVH * HD))
+    vc0 = rnd_bits(rng, (L, num_blocks * bs, KVH * HD))
+    pool.k.copy_(to_dev_bf16(kc0).view(pool.k.shape))
+    pool.v.copy_(to_dev_bf16(vc0).view(pool.v.shape))
+    hidden = rnd_bits(rng, (n, H))
+    hd_dev = to_dev_bf16(hidden)
+    d_lens = torch.from_numpy(cached.copy()).cuda()
+    h_lens = (ctypes.c_int * n)(*cached.tolist())
+    engine.decode_step(ws, cfg, pool, bts, hd_dev, d_lens, h_lens)
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    # oracle
+    slots = np.array([bt_np[i, cached[i] // bs] * bs + cached[i] % bs for i in range(n)], np.int64)
+    if w4a4:
+        lin = lambda x, w: o.nvfp4_linear(x, w[0], w[1], isc, w[2])
+    else:
+        lin = lambda x, w: o.linear_o1(x, *w)
+    kc, vc = [kc0[l].copy() for l in range(L)], [vc0[l].copy() for l in range(L)]
+    want = do.decode_step(hidden, layers, fn, kc, vc, bt_np, cached, slots, QH, KVH, HD, bs, lin)
+    got = bits_of(hd_dev)
+    err = o.rel_err(got, want)
+    assert err <= REL_TOL_VS_ORACLE, err
+    assert o.cosine(got, want) >= 0.999
+    assert list(h_lens) == (cached + 1).tolist() and d_lens.cpu().numpy().tolist() == (cached + 1).tolist()
+    # the new token's K/V landed in its slot, everything else is untouched
+    for l in range(L):
+        kd = bits_of(pool.k[l].reshape(num_blocks * bs, -1))
+        mask = np.ones(num_blocks * bs, bool)
+        mask[slots] = False
+        assert np.array_equal(kd[mask], kc0[l][mask])
+        assert o.rel_err(kd[slots], kc[l][slots]) <= REL_TOL_VS_ORACLE
+        assert o.rel_err(bits_of(pool.v[l].reshape(num_blocks * bs, -1))[slots], vc[l][slots]) <= REL_TOL_VS_ORACLE
+    return err
+
+
+def test_decode_step_w4a16_vs_oracle():
+    os.environ.pop("GLMASR_USE_CUTLASS_NVFP4", None)
+    run_decode_step_case(False)
+
+
+def test_decode_step_w4a4_vs_oracle_in_subprocess():
+    """The W4A4 switch is read once per process (as in the reference), so run it in a child."""
+    env = dict(os.environ, GLMASR_USE_CUTLASS_NVFP4="1")
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_gpu_decoder as t; print('ERR', t.run_decode_step_case(True))"
+            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")))
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ERR" in r.stdout

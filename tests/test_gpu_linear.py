@@ -257,3 +257,46 @@ def test_layer_proj_device_and_host_agree(ops):
             act = o.silu_mul_split_packed(np.concatenate([o.linear_o1(h1, *npw["gate"]), o.linear_o1(h1, *npw["up"])], 1))
             h2 = o.residual_add(o.linear_o1(act, *npw["down"]), h1)
             assert o.rel_err(bits_of(dev), h2) <= REL_TOL_VS_ORACLE
+
+
+# ---- W4A4 on CTA pairs (cta_group::2): taken when M >= 512 and there is a 256x256 tile for every pair ----
+@pytest.mark.parametrize("M,N,K", [(2560, 2048, 512), (2500, 2304, 256), (640, 8192, 1024)])
+def test_pair_kernel_plain(ops, M, N, K):
+    pw, sw, g = o.seeded_weight(N, K, 500 + N)
+    x = o.seeded_activation(M, K, 600 + M)
+    isc = o.default_input_scale(x)
+    out = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    assert ops.nvfp4_linear(out, to_dev_bf16(x), to_dev_u8(pw), to_dev_u8(sw), isc, g) == 0
+    got = bits_of(out)
+    o2 = o.nvfp4_linear(x, pw, sw, isc, g)
+    assert o.rel_err(got, o2) <= REL_TOL_TIGHT
+    assert np.percentile(ulp_diff(got, o2), 99) <= 1
+    assert ops.status() == 0
+
+
+def test_pair_kernel_fused_epilogues(ops):
+    M, K = 3300, 512
+    x = o.seeded_activation(M, K, 700)
+    isc = o.default_input_scale(x)
+    xd = to_dev_bf16(x)
+    # q|k|v segments with different per-tensor scales: 8 + 2 + 2 sub-tiles -> 6 tiles x 13 row pairs
+    ws = [o.seeded_weight(n, K, 710 + i) for i, n in enumerate((1024, 256, 256))]
+    out = bits_of(ops.fp4_linear_fused(ops.MODE_W4A4, xd, [dev_weight(ops, *w) for w in ws], input_scale=isc))
+    col = 0
+    for (pw, sw, g), n in zip(ws, (1024, 256, 256)):
+        assert o.rel_err(out[:, col:col + n], o.nvfp4_linear(x, pw, sw, isc, g)) <= REL_TOL_TIGHT, col
+        col += n
+    # gate|up + SiLU
+    wg, wu = o.seeded_weight(1024, K, 720), o.seeded_weight(1024, K, 721)
+    act = bits_of(ops.fp4_linear_fused(ops.MODE_W4A4, xd, [dev_weight(ops, *wg), dev_weight(ops, *wu)],
+                                       epilogue=ops.EPI_SILU_GATE, input_scale=isc))
+    want = o.silu_mul_split_packed(np.concatenate([o.nvfp4_linear(x, wg[0], wg[1], isc, wg[2]),
+                                                   o.nvfp4_linear(x, wu[0], wu[1], isc, wu[2])], axis=1))
+    assert o.rel_err(act, want) <= REL_TOL_VS_ORACLE and o.cosine(act, want) >= 0.9999
+    # residual
+    w = o.seeded_weight(2048, K, 730)
+    res = o.seeded_activation(M, 2048, 731)
+    out = bits_of(ops.fp4_linear_fused(ops.MODE_W4A4, xd, [dev_weight(ops, *w)], epilogue=ops.EPI_RESIDUAL,
+                                       residual=to_dev_bf16(res), input_scale=isc))
+    assert o.rel_err(out, o.residual_add(o.nvfp4_linear(x, w[0], w[1], isc, w[2]), res)) <= REL_TOL_TIGHT
+    assert ops.status() == 0
