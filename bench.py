@@ -115,6 +115,100 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args, rank, local_rank, world):
+    """BASELINE config 2: one batched decode step of the 28-layer decoder + FP4 lm_head + arg-max for
+    256 sequences with paged bf16 KV (16-token pages, context 200-450).  tok/s = sequences / step time."""
+    os.environ["GLMASR_USE_CUTLASS_NVFP4"] = "1" if args.mode == "w4a4" else "0"
+    import torch
+
+    from glm_asr_stack_b200 import engine, ops, workloads
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    model = workloads.build_decoder(layers=args.layers)
+    state = workloads.build_decode_state(model.cfg, num_seqs=args.seqs)
+    cfg, lm, n, vocab = model.cfg, model.lm_head, args.seqs, model.cfg.vocab_size
+    gen = torch.Generator(device="cpu").manual_seed(3)
+    ids_host = torch.randint(0, vocab, (n,), generator=gen, dtype=torch.int32).pin_memory()
+    ids = ids_host.cuda()
+    logits = torch.empty((n, vocab), dtype=torch.bfloat16, device="cuda")
+    tok_host = torch.empty(n, dtype=torch.int32).pin_memory()
+
+    def step(ids_dev):
+        state.reset_lengths()                      # same context every step: the step rewrites the same KV slot
+        hidden = ops.embedding_lookup(model.embed, ids_dev)
+        engine.decode_step(model.ws, cfg, state.pool, state.bts, hidden, state.d_seq_lens, state.h_seq_lens)
+        if args.mode == "w4a4":
+            assert ops.nvfp4_linear(logits, hidden, lm.w_packed, lm.w_scales, model.lm_head_input_scale,
+                                    lm.w_global_scale) == 0
+        else:
+            ops.fp4_linear(hidden, lm.w_packed, lm.w_scales, lm.w_global_scale, out=logits)
+        return ops.argmax_rows(logits)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(ids)
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    l0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(ids)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = ops.launch_count() - l0
+    clocks = sampler.stop()
+    # end to end: token ids from pinned host memory in, next-token ids back to the host
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok_host.copy_(step(ids_host.cuda(non_blocking=True)), non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    H, KV = cfg.dec_hidden, cfg.dec_kv_heads * cfg.dec_head_dim
+    # algorithmic bytes per step: FP4 weights once, K and V of every cached token once, the new token's K/V,
+    # embedding rows, logits written then read by the arg-max
+    bytes_step = model.weight_bytes + state.kv_read_bytes + n * KV * 2 * 2 * cfg.dec_layers + n * H * 2 + 2 * n * vocab * 2
+    peaks = measured_peaks()
+    peak = peaks["hbm_gbs"] if peaks else 6650.0
+    if rank == 0:
+        gbs = bytes_step / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode_tok_per_s", "value": world * n / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
+            "config": {"workload": f"config2: batched decode step, {cfg.dec_layers} layers, {n} sequences, paged bf16 KV "
+                                   "(16-token pages, context 200-450), FP4 lm_head over 59264 + arg-max",
+                       "l2": f"{bytes_step / 1e9:.2f} GB touched per step > 126 MB L2"},
+            "e2e": {"value": world * n / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": n * 4,
+                    "d2h_bytes_per_step": n * 4, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "whole decode step (weights + KV stream)", "achieved": gbs, "peak": peak,
+                         "unit": "GB/s", "frac": gbs / peak, "traffic": None, "bytes_per_step": bytes_step,
+                         "weight_bytes": model.weight_bytes, "kv_read_bytes": state.kv_read_bytes,
+                         "peak_source": "measured HBM copy bandwidth (MEASURED_PEAKS.json)" if peaks else "fallback"},
+        }), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -124,6 +218,10 @@ def main():
     ap.add_argument("--mode", default="w4a4", choices=["w4a4", "w4a16"])
     ap.add_argument("--rows", type=int, default=M_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="layer", choices=["layer", "decode"],
+                    help="layer = BASELINE config 1 (default, the headline); decode = BASELINE config 2")
+    ap.add_argument("--seqs", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=28)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -133,6 +231,10 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+
+    if args.workload == "decode":
+        run_decode(args, rank, local_rank, world)
         return
 
     import torch

@@ -50,6 +50,7 @@ struct PrepackedScales {
 static std::unordered_map<const void *, PrepackedScales> g_prepack;
 
 cudaStream_t current_stream() { return g_stream; }
+void note_launches(int n) { g_launches += n; }
 
 int *device_status_word() {
     if (g_status == nullptr) {
@@ -73,6 +74,8 @@ void *workspace_slot(int slot, size_t bytes) {
 }
 void *workspace(size_t bytes) { return workspace_slot(0, bytes); }
 
+static void clear_tmap_cache();
+
 void free_all_private_state() {
     cudaDeviceSynchronize();
     for (int i = 0; i < kSlots; ++i) {
@@ -82,6 +85,7 @@ void free_all_private_state() {
     }
     for (auto &kv : g_prepack) cudaFree(kv.second.tiled);
     g_prepack.clear();
+    clear_tmap_cache();
     if (g_status) cudaFree(g_status);
     g_status = nullptr;
 }
@@ -137,6 +141,15 @@ static bool use_pair_kernel() {
     return v == 1;
 }
 
+static bool no_tma_store() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_NO_TMA_STORE");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 static bool force_simt() {
     static int v = -1;
     if (v < 0) {
@@ -166,20 +179,53 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major tensor [rows, inner] of `elem_bytes`-byte elements, row pitch `pitch_bytes`;
-// boxes of box_rows x box_inner elements.
+// boxes of box_rows x box_inner elements.  Encoding a descriptor is a driver call of several
+// microseconds and a decode step needs ~900 of them over the same few buffers, so encoded
+// descriptors are cached by their full parameter tuple.
+struct TmapKey {
+    const void *base;
+    uint64_t inner, rows, pitch;
+    uint32_t box_inner, box_rows;
+    int dt, swizzle;
+    bool operator==(const TmapKey &o) const {
+        return base == o.base && inner == o.inner && rows == o.rows && pitch == o.pitch && box_inner == o.box_inner &&
+               box_rows == o.box_rows && dt == o.dt && swizzle == o.swizzle;
+    }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey &k) const {
+        uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull;
+        h ^= (k.inner + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        h ^= (k.rows * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2));
+        h ^= (k.pitch + ((uint64_t)k.box_inner << 32) + ((uint64_t)k.box_rows << 16) + (uint64_t)(k.dt * 4 + k.swizzle) + (h << 6));
+        return (size_t)h;
+    }
+};
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
+static void clear_tmap_cache() { g_tmaps.clear(); }
+
 static bool make_tmap(CUtensorMap *tm, const void *base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner,
                       uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
     if (((uintptr_t)base & 15) != 0 || (pitch_bytes & 15) != 0) return false;
+    (void)elem_bytes;
+    const TmapKey key = {base, inner, rows, pitch_bytes, box_inner, box_rows, (int)dt, swizzle128 ? 1 : 0};
+    auto it = g_tmaps.find(key);
+    if (it != g_tmaps.end()) {
+        *tm = it->second;
+        return true;
+    }
     const cuuint64_t dims[2] = {inner, rows};
     const cuuint64_t strides[1] = {pitch_bytes};
     const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    (void)elem_bytes;
     const CUresult r = encode_fn()(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE,
                                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    if (r != CUDA_SUCCESS) return false;
+    if (g_tmaps.size() > 16384) g_tmaps.clear();
+    g_tmaps.emplace(key, *tm);
+    return true;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -461,6 +507,14 @@ static int run_fused(const FusedArgs &a) {
                 g_pair_ready = true;
             }
             p.num_n_tiles = n_tiles;
+            // epilogue through shared memory + bulk tensor stores when the output can be described to TMA
+            bool tma_ok = aligned16(a.out) && (a.ldo % 8) == 0 && !no_tma_store();
+            for (int i = 0; i < p.num_segs && a.epi != EPI_SILU_GATE; ++i)
+                if (i + 1 < p.num_segs && (p.seg_rows[i] % 8) != 0) tma_ok = false;   // segment column offsets stay 16-byte aligned
+            if (tma_ok)
+                tma_ok = make_tmap(&p.tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.n_out, (uint64_t)a.M,
+                                   (uint64_t)a.ldo * 2, 64, 32, true);
+            p.tma_store = tma_ok ? 1 : 0;
             TimedLaunch tl;
             if (g_profile) {
                 cudaEventCreate(&tl.start);

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "decoder_ops.cuh"
 
@@ -266,6 +267,16 @@ bool launch_paged_decode_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     const int group = num_q_heads / num_kv_heads;
     if (group > 8 || (ldq % 4) != 0 || (ldo % 4) != 0) return false;
     if (num_seqs <= 0) return true;
+    // default: the tensor-core flash-decoding kernel; GLMASR_ATTN_SCALAR=1 keeps the scalar one (comparison runs)
+    static int scalar = -1;
+    if (scalar < 0) {
+        const char *e = getenv("GLMASR_ATTN_SCALAR");
+        scalar = (e && e[0] == '1') ? 1 : 0;
+    }
+    if (!scalar && launch_paged_decode_attention_mma(out, ldo, query, ldq, key_cache, value_cache, block_tables, seq_lens,
+                                                     num_seqs, num_q_heads, num_kv_heads, head_dim, block_size,
+                                                     max_blocks_per_seq, st))
+        return true;
     const float scale = 1.0f / sqrtf((float)head_dim);
     dim3 grid(num_kv_heads, num_seqs);
     paged_decode_attention_h128_kernel<<<grid, 32 * group, 0, st>>>(out, ldo, query, ldq, key_cache, value_cache,

@@ -23,6 +23,12 @@ bool launch_paged_decode_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloa
                                    const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
                                    int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
                                    cudaStream_t st);
+// Flash-decoding variant (paged_attention.cu): cp.async-staged tiles + warp-level tensor-core MMA.
+bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *query, int ldq,
+                                       const __nv_bfloat16 *key_cache, const __nv_bfloat16 *value_cache,
+                                       const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
+                                       int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                                       cudaStream_t st);
 void launch_embedding_lookup(__nv_bfloat16 *out, const __nv_bfloat16 *table, const int *ids, int n, int dim,
                              cudaStream_t st);
 // out[i, :] = src_rows[i][:]  /  dst_rows[i][:] = in[i, :]   (device arrays of row pointers)

@@ -211,11 +211,13 @@ enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
 extern "C" void rmsnorm(uint16_t *out, const uint16_t *x, const uint16_t *weight, float eps, int rows, int dim) {
     launch_rmsnorm((__nv_bfloat16 *)out, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)weight, eps, rows, dim,
                    current_stream());
+    note_launches(1);
     GLMASR_CUDA_CHECK(cudaGetLastError());
 }
 
 extern "C" void embedding_lookup(uint16_t *out, const uint16_t *table, const int *ids, int n, int dim) {
     launch_embedding_lookup((__nv_bfloat16 *)out, (const __nv_bfloat16 *)table, ids, n, dim, current_stream());
+    note_launches(1);
     GLMASR_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -358,6 +360,7 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
             silu_elementwise_mul(act, act + (size_t)M * F, M * F);
         }
         single_proj(hid, H, act, F, R.down, M, hid, scratch);
+        note_launches(6);   // 2 norms, 2 RoPE, cache write, attention (the projections count themselves)
     }
 
     launch_rmsnorm((__nv_bfloat16 *)hid, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)refs.final_norm, 1e-5f, M, H, st);
@@ -366,6 +369,7 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     } else {
         launch_scatter_rows((__nv_bfloat16 *const *)d_ptrs, (const __nv_bfloat16 *)hid, M, H, st);
     }
+    note_launches(2);
     for (int s = 0; s < M; ++s) h_seq_lens[s] = h_total[s];
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_seq_lens, d_total, (size_t)M * sizeof(int), cudaMemcpyDeviceToDevice, st));
     GLMASR_CUDA_CHECK(cudaGetLastError());

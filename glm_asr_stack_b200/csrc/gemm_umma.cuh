@@ -29,6 +29,8 @@ struct alignas(64) GemmParams {
     CUtensorMap tm_bs[kMaxSegments];    // W4A16: row-major e4m3 scales [N_s, K/16], 128-row x 16-byte boxes
     CUtensorMap tm_sfa;                 // W4A4 pair kernel: tiled activation scales as [chunks, 128 x u32], 4-chunk boxes
     CUtensorMap tm_sfb[kMaxSegments];   // W4A4 pair kernel: tiled weight scales, same view
+    CUtensorMap tm_out;                 // pair kernel: output as [M, n_out] bf16, 32-row x 64-column boxes, 128B swizzle
+    int tma_store;                      // 1: the epilogue stages tiles in shared memory and stores them through tm_out
     const uint8_t *sfa;                 // W4A4: activation scales, 128x4-tiled
     const uint8_t *sfb[kMaxSegments];   // W4A4: weight scales, 128x4-tiled
     float alpha[kMaxSegments];          // applied to the fp32 accumulator of that segment

@@ -51,7 +51,8 @@ struct PairCfg {
     static constexpr int SFB_COL = SFA_COL + 16;          // 464 .. 495
     static constexpr int TMEM_COLS = 512;
     static constexpr int BAR_BYTES = 1024;
-    static constexpr int SMEM_BYTES = 1024 + BAR_BYTES + STAGES * STAGE_BYTES;
+    static constexpr int OUT_STAGE_BYTES = 32 * 128;      // per epilogue warp: 32 rows x 64 bf16, 128B-swizzled
+    static constexpr int SMEM_BYTES = 1024 + BAR_BYTES + STAGES * STAGE_BYTES + EPI_WARPS * OUT_STAGE_BYTES;
     static constexpr uint32_t TX_BYTES_PAIR = 2 * STAGE_BYTES;
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
@@ -222,6 +223,34 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
         const int half = (warp - 2) >> 2;
         const uint32_t tempty0 = mapa_shared(tempty_bar(0), 0);      // tempty[a] = tempty0 + 8 a
         const uint32_t tovl0 = mapa_shared(tovl_bar, 0);
+        // output staging: each lane writes its row's 16-byte chunks at (chunk ^ (row & 7)), the layout a
+        // 128B-swizzled TMA store reads back, so the warp's 32 x 64 tile leaves as one bulk store
+        const uint32_t out_stage = tiles + C::STAGES * C::STAGE_BYTES + (uint32_t)(warp - 2) * C::OUT_STAGE_BYTES;
+        const bool store_leader = elect_one();
+        auto stage_chunk = [&](const float (&v)[32], int hch) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t *>(&b);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                sts128(out_stage + (uint32_t)lane * 128 + ((((uint32_t)(hch * 4 + j)) ^ ((uint32_t)lane & 7u)) << 4),
+                       make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+        };
+        auto stage_begin = [&]() {          // the previous store of this warp must have finished reading the buffer
+            if (store_leader) bulk_wait_read_all();
+            __syncwarp();
+        };
+        auto stage_flush = [&](int col, int row0) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (store_leader) {
+                tma_store_2d(&p.tm_out, out_stage, col, row0);
+                bulk_commit_group();
+            }
+        };
         uint32_t acc_it = 0;
         for (int tile = pair; tile < total_tiles; tile += num_pairs) {
             const int m_tile = (tile % num_m_pairs) * 2 + (int)rank;
@@ -283,6 +312,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 }
                 tmem_ld_wait();
                 release_acc();
+                const bool box_tma = p.tma_store && (sg.ncols - half * 64) >= 64;
+                if (box_tma) stage_begin();
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     float v[32];
@@ -294,8 +325,10 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                     }
                     const int c0 = half * 64 + ch * 32;
                     const int nvalid = sg.ncols - c0;
-                    if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
+                    if (box_tma) stage_chunk(v, ch);
+                    else if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
                 }
+                if (box_tma && !(p.debug & 4)) stage_flush(sg.col0 + half * 64, m_tile * 128 + quad * 32);
             } else {
                 const SubTile st = resolve_subtile(p, n_tile, half, 2);
                 const float alpha = p.alpha[st.seg];
@@ -324,32 +357,42 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 tmem_ld_wait();
                 release_acc();
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    const int c0 = ch * 32;
-                    const int nvalid = st.ncols - c0;
-                    if (!(row_ok && nvalid > 0)) continue;
-                    const int col = st.col0 + c0;
-                    float v[32];
+                for (int bx = 0; bx < 2; ++bx) {
+                    const bool box_tma = p.tma_store && (st.ncols - bx * 64) >= 64;
+                    if (box_tma) stage_begin();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[ch][i]) * alpha;
-                    if (p.bias != nullptr) {
-                        float b[32];
-                        load_row_chunk(p.bias + col, b, nvalid);
+                    for (int hc = 0; hc < 2; ++hc) {
+                        const int ch = bx * 2 + hc;
+                        const int c0 = ch * 32;
+                        const int nvalid = st.ncols - c0;
+                        const int col = st.col0 + c0;
+                        const bool live = row_ok && nvalid > 0;
+                        float v[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] += b[i];
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[ch][i]) * alpha;
+                        if (p.bias != nullptr && nvalid > 0) {
+                            float b[32];
+                            load_row_chunk(p.bias + col, b, nvalid);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += b[i];
+                        }
+                        if (p.epi == EPI_RESIDUAL && live) {
+                            float res[32];
+                            load_row_chunk(p.residual + (size_t)row * p.ldo + col, res, nvalid);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
+                        }
+                        if (box_tma) stage_chunk(v, hc);
+                        else if (live && !(p.debug & 4)) store_row_chunk(out_row + col, v, nvalid);
                     }
-                    if (p.epi == EPI_RESIDUAL) {
-                        float res[32];
-                        load_row_chunk(p.residual + (size_t)row * p.ldo + col, res, nvalid);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
-                    }
-                    if (!(p.debug & 4)) store_row_chunk(out_row + col, v, nvalid);
+                    if (box_tma && !(p.debug & 4)) stage_flush(st.col0 + bx * 64, m_tile * 128 + quad * 32);
                 }
             }
             DBG_ACC(2);
             ++acc_it;
         }
+        if (store_leader) bulk_wait_all();      // this warp's bulk stores are complete before the CTA exits
+        __syncwarp();
         if (dbg && warp == 2 && lane == 0 && rank == 0)
             for (int i = 0; i < 3; ++i) p.dbg_cycles[pair * 16 + 8 + i] = dbg_acc[i];
     }

