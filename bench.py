@@ -156,7 +156,8 @@ def run_decode(args, rank, local_rank, world):
     for _ in range(args.warmup):
         step(ids)
     torch.cuda.synchronize()
-    assert ops.status() == 0
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
@@ -287,7 +288,8 @@ def main():
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
-    assert ops.status() == 0
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
 
     # ---- device-resident timing -----------------------------------------------------------
     sampler = ClockSampler(local_rank)
@@ -350,7 +352,8 @@ def main():
         e2e_s = float(t.item())
     e2e_val = world * layer_flops(M) * args.steps / e2e_s / 1e12
     bytes_io = M * HIDDEN * 2
-    assert ops.status() == 0
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
 
     if rank == 0:
         line = {

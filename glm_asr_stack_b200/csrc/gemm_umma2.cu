@@ -13,7 +13,7 @@
 //   full[s]    in CTA 0 only; CTA 0's producer announces the bytes of both CTAs, every load of
 //              either CTA credits that barrier
 //   empty[s]   in each CTA; the MMA thread (CTA 0) commits to both after the stage's MMAs
-//   tfull      in each CTA; committed to both when a tile's last MMA is issued
+//   tfull[a]   in each CTA, one per accumulator; committed to both when a tile's last MMA is issued
 //   tempty[a]  in CTA 0; the epilogue warps of both CTAs arrive on it once accumulator a has
 //              been drained into registers
 //   tovl       in CTA 0; the epilogue warps that own the 64 tensor-memory columns shared by the two
@@ -67,9 +67,12 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
     const uint32_t bar = smem_base;
     auto full_bar = [&](int s) { return bar + 8u * (uint32_t)s; };
     auto empty_bar = [&](int s) { return bar + 8u * (uint32_t)(C::STAGES + s); };
-    const uint32_t tfull_bar = bar + 8u * (uint32_t)(2 * C::STAGES);
-    auto tempty_bar = [&](int a) { return bar + 8u * (uint32_t)(2 * C::STAGES + 1 + a); };
-    const uint32_t tovl_bar = bar + 8u * (uint32_t)(2 * C::STAGES + 3);
+    // One "accumulator full" barrier per accumulator: with a single shared one, an epilogue warp still
+    // storing tile t-1 could miss phase t altogether (tile t+1 needs only the early releases), see the
+    // barrier back at its old parity and wait for a tile that cannot start without that warp.
+    auto tfull_bar = [&](int a) { return bar + 8u * (uint32_t)(2 * C::STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar + 8u * (uint32_t)(2 * C::STAGES + 2 + a); };
+    const uint32_t tovl_bar = bar + 8u * (uint32_t)(2 * C::STAGES + 4);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + 512);
     volatile int *abort_word = reinterpret_cast<volatile int *>(smem_gen + 520);
     const uint32_t tiles = smem_base + C::BAR_BYTES;
@@ -85,7 +88,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(tfull_bar, 1);
+        mbar_init(tfull_bar(0), 1);
+        mbar_init(tfull_bar(1), 1);
         mbar_init(tempty_bar(0), 2 * C::EPI_WARPS);
         mbar_init(tempty_bar(1), 2 * C::EPI_WARPS);
         mbar_init(tovl_bar, C::EPI_WARPS);                 // 4 warps of each CTA own the shared columns
@@ -159,7 +163,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             const bool leader_lane = elect_one();
             constexpr uint32_t idesc = idesc_nvfp4(256, C::BN);
             const uint32_t empty0_peer = mapa_shared(empty_bar(0), 1);
-            const uint32_t tfull_peer = mapa_shared(tfull_bar, 1);
+            const uint32_t tfull0_peer = mapa_shared(tfull_bar(0), 1);
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
@@ -210,8 +214,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 }
                 if (!ok) break;
                 if (leader_lane) {
-                    umma_commit_pair(tfull_bar);
-                    umma_commit_pair(tfull_peer);
+                    umma_commit_pair(tfull_bar(acc));
+                    umma_commit_pair(tfull0_peer + 8u * (uint32_t)acc);
                 }
                 ++acc_it;
             }
@@ -255,16 +259,16 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
         for (int tile = pair; tile < total_tiles; tile += num_pairs) {
             const int m_tile = (tile % num_m_pairs) * 2 + (int)rank;
             const int n_tile = tile / num_m_pairs;
-            const uint32_t aph = acc_it & 1u;
+            const int acc = acc_it & 1;
+            const uint32_t aph = (acc_it >> 1) & 1u;
             DBG_T0();
-            bool ok = mbar_wait(tfull_bar, aph, abort_word, ST_TIMEOUT_EPILOGUE);
+            bool ok = mbar_wait(tfull_bar(acc), aph, abort_word, ST_TIMEOUT_EPILOGUE);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             DBG_ACC(0);
             tc_fence_after();
             const int row = m_tile * 128 + quad * 32 + lane;
             const bool row_ok = row < p.M;
-            const int acc = acc_it & 1;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_STRIDE);
             __nv_bfloat16 *out_row = p.out + (size_t)row * p.ldo;
             // the shared physical columns [192, 256) are tile columns [192, 256) of acc0 (second half)

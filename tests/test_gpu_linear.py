@@ -300,3 +300,31 @@ def test_pair_kernel_fused_epilogues(ops):
                                        residual=to_dev_bf16(res), input_scale=isc))
     assert o.rel_err(out, o.residual_add(o.nvfp4_linear(x, w[0], w[1], isc, w[2]), res)) <= REL_TOL_TIGHT
     assert ops.status() == 0
+
+
+def test_pair_kernel_repeat_launches_stay_identical(ops):
+    """Many tiles per CTA pair, many back-to-back launches of all three epilogues with different
+    store pressure: every launch must produce the same bits and no bounded wait may expire.  (An
+    epilogue warp that is late by a whole tile must still see that tile's accumulator barrier.)"""
+    from glm_asr_stack_b200 import synth
+    M, K = 10000, 2048
+    x = synth.seeded_activation(M, K, 900)
+    isc = synth.default_input_scale(x)
+    wg = synth.seeded_weight_fast(6144, K, 901)
+    wu = synth.seeded_weight_fast(6144, K, 902)
+    wo = synth.seeded_weight_fast(2048, K, 903)
+    res = synth.seeded_activation(M, 2048, 904)
+    first = None
+    for it in range(60):
+        a = ops.fp4_linear_fused(ops.MODE_W4A4, x, [wg, wu], epilogue=ops.EPI_SILU_GATE, input_scale=isc)
+        b = ops.fp4_linear_fused(ops.MODE_W4A4, x, [wg, wu], input_scale=isc)
+        c = ops.fp4_linear_fused(ops.MODE_W4A4, x, [wo], epilogue=ops.EPI_RESIDUAL, residual=res, input_scale=isc)
+        sums = (a.view(torch.int16).to(torch.int64).sum().item(), b.view(torch.int16).to(torch.int64).sum().item(),
+                c.view(torch.int16).to(torch.int64).sum().item())
+        if first is None:
+            first = (a.clone(), b.clone(), c.clone(), sums)
+        else:
+            assert sums == first[3], it
+            if it % 20 == 19:
+                assert torch.equal(a, first[0]) and torch.equal(b, first[1]) and torch.equal(c, first[2])
+    assert ops.status() == 0
