@@ -131,6 +131,78 @@ __device__ __forceinline__ void load_row_chunk(const __nv_bfloat16 *src, float (
     }
 }
 
+// ---- compact forms for kernels whose epilogue must stay small in the instruction cache ------------
+// 32 bf16 values of one row chunk, packed two per register.
+struct Packed16 {
+    uint32_t w[16];
+};
+
+__device__ __forceinline__ Packed16 pack_bf16(const float (&v)[32]) {
+    Packed16 pk;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        pk.w[i] = *reinterpret_cast<const uint32_t *>(&b);
+    }
+    return pk;
+}
+
+__device__ __forceinline__ void unpack_bf16(const Packed16 &pk, float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        v[2 * i] = __uint_as_float(pk.w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(pk.w[i] & 0xFFFF0000u);
+    }
+}
+
+// Rare paths (row tails, unaligned pointers), kept out of line on purpose.
+static __device__ __noinline__ void store_packed_any(__nv_bfloat16 *dst, Packed16 pk, int nvalid) {
+    uint16_t *d = reinterpret_cast<uint16_t *>(dst);
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+        if (i < nvalid) d[i] = (uint16_t)(pk.w[i >> 1] >> ((i & 1) * 16));
+}
+
+static __device__ __noinline__ Packed16 load_packed_any(const __nv_bfloat16 *src, int nvalid) {
+    const uint16_t *s16 = reinterpret_cast<const uint16_t *>(src);
+    Packed16 pk;
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t lo = 2 * i < nvalid ? s16[2 * i] : 0u;
+        const uint32_t hi = 2 * i + 1 < nvalid ? s16[2 * i + 1] : 0u;
+        pk.w[i] = lo | (hi << 16);
+    }
+    return pk;
+}
+
+// Row chunk to global memory: 32-byte stores when the chunk is whole and 32-byte aligned.
+__device__ __forceinline__ void store_packed(__nv_bfloat16 *dst, const Packed16 &pk, int nvalid) {
+    if (nvalid >= 32 && (((uintptr_t)dst & 31) == 0)) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * i),
+                         "r"(pk.w[8 * i]), "r"(pk.w[8 * i + 1]), "r"(pk.w[8 * i + 2]), "r"(pk.w[8 * i + 3]),
+                         "r"(pk.w[8 * i + 4]), "r"(pk.w[8 * i + 5]), "r"(pk.w[8 * i + 6]), "r"(pk.w[8 * i + 7])
+                         : "memory");
+    } else {
+        store_packed_any(dst, pk, nvalid);
+    }
+}
+
+__device__ __forceinline__ Packed16 load_packed(const __nv_bfloat16 *src, int nvalid) {
+    if (nvalid >= 32 && (((uintptr_t)src & 15) == 0)) {
+        Packed16 pk;
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 q = s4[i];
+            pk.w[4 * i] = q.x, pk.w[4 * i + 1] = q.y, pk.w[4 * i + 2] = q.z, pk.w[4 * i + 3] = q.w;
+        }
+        return pk;
+    }
+    return load_packed_any(src, nvalid);
+}
+
 __device__ __forceinline__ float silu_gate(float g, float u) {
     // (g * sigmoid(g)) * u as in the reference SiLU-gate (Infer-engine/cuda/kernels.cu:1259-1263), with
     // the hardware exponential and reciprocal: the fused epilogue is compared with the reference

@@ -231,17 +231,11 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
         // 128B-swizzled TMA store reads back, so the warp's 32 x 64 tile leaves as one bulk store
         const uint32_t out_stage = tiles + C::STAGES * C::STAGE_BYTES + (uint32_t)(warp - 2) * C::OUT_STAGE_BYTES;
         const bool store_leader = elect_one();
-        auto stage_chunk = [&](const float (&v)[32], int hch) {
-            uint32_t w[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                w[i] = *reinterpret_cast<const uint32_t *>(&b);
-            }
+        auto stage_packed = [&](const Packed16 &pk, int hch) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 sts128(out_stage + (uint32_t)lane * 128 + ((((uint32_t)(hch * 4 + j)) ^ ((uint32_t)lane & 7u)) << 4),
-                       make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+                       make_uint4(pk.w[4 * j], pk.w[4 * j + 1], pk.w[4 * j + 2], pk.w[4 * j + 3]));
         };
         auto stage_begin = [&]() {          // the previous store of this warp must have finished reading the buffer
             if (store_leader) bulk_wait_read_all();
@@ -286,108 +280,121 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 DBG_ACC(1);
             };
 
+            // The epilogue is written for a small instruction footprint: every warp runs the same
+            // loop bodies (one 32-column chunk, or one pair of chunks, per iteration; addresses at run
+            // time) instead of separately unrolled code per accumulator, per half and per owner.  With
+            // each path unrolled the kernel's code was several times the instruction cache, and
+            // fetching it, not the arithmetic, set the time of a tile's epilogue.
             if (p.epi == EPI_SILU_GATE) {
                 // gate columns [64*half, +64) pair with up columns [128 + 64*half, +64)
                 const SubTile sg = resolve_subtile(p, n_tile, 0, 2);
                 const float ag = p.alpha[0], au = p.alpha[1];
-                uint32_t rg[2][32], ru[2][32];
-                if (owns_shared) {
-                    if (acc == 0) {
-#pragma unroll
-                        for (int ch = 0; ch < 2; ++ch) tmem_ld_x32(t_row + 128 + half * 64 + ch * 32, ru[ch]);
-                        tmem_ld_wait();
-                        release_shared();
-#pragma unroll
-                        for (int ch = 0; ch < 2; ++ch) tmem_ld_x32(t_row + half * 64 + ch * 32, rg[ch]);
-                    } else {
-#pragma unroll
-                        for (int ch = 0; ch < 2; ++ch) tmem_ld_x32(t_row + half * 64 + ch * 32, rg[ch]);
-                        tmem_ld_wait();
-                        release_shared();
-#pragma unroll
-                        for (int ch = 0; ch < 2; ++ch) tmem_ld_x32(t_row + 128 + half * 64 + ch * 32, ru[ch]);
-                    }
-                } else {
-#pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
-                        tmem_ld_x32(t_row + half * 64 + ch * 32, rg[ch]);
-                        tmem_ld_x32(t_row + 128 + half * 64 + ch * 32, ru[ch]);
-                    }
-                }
-                tmem_ld_wait();
-                release_acc();
+                const uint32_t g_col = t_row + half * 64, u_col = t_row + 128 + half * 64;
                 const bool box_tma = p.tma_store && (sg.ncols - half * 64) >= 64;
-                if (box_tma) stage_begin();
+                // The owner's chunks in the shared columns (its up columns in accumulator 0, its gate
+                // columns in accumulator 1) are read first, scaled, rounded and kept packed.
+                const bool kept_is_gate = acc == 1;
+                Packed16 kept[2];
+                if (owns_shared) {
+                    uint32_t k0[32], k1[32];
+                    const uint32_t c = kept_is_gate ? g_col : u_col;
+                    tmem_ld_x32(c, k0);
+                    tmem_ld_x32(c + 32, k1);
+                    tmem_ld_wait();
+                    release_shared();
+                    const float sk = kept_is_gate ? ag : au;
+                    float f[32];
 #pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(k0[i]) * sk;
+                    kept[0] = pack_bf16(f);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(k1[i]) * sk;
+                    kept[1] = pack_bf16(f);
+                }
+                if (box_tma) stage_begin();
+#pragma unroll 1
                 for (int ch = 0; ch < 2; ++ch) {
+                    float g[32], u[32];
+                    if (!owns_shared) {
+                        uint32_t a[32], b[32];
+                        tmem_ld_x32(g_col + ch * 32, a);
+                        tmem_ld_x32(u_col + ch * 32, b);
+                        tmem_ld_wait();
+                        if (ch == 1) release_acc();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            g[i] = bf16_round(__uint_as_float(a[i]) * ag);
+                            u[i] = bf16_round(__uint_as_float(b[i]) * au);
+                        }
+                    } else {
+                        uint32_t a[32];
+                        tmem_ld_x32((kept_is_gate ? u_col : g_col) + ch * 32, a);
+                        tmem_ld_wait();
+                        if (ch == 1) release_acc();
+                        Packed16 k;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) k.w[i] = ch == 0 ? kept[0].w[i] : kept[1].w[i];
+                        float fk[32];
+                        unpack_bf16(k, fk);
+                        const float sa = kept_is_gate ? au : ag;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float x = bf16_round(__uint_as_float(a[i]) * sa);
+                            g[i] = kept_is_gate ? fk[i] : x;
+                            u[i] = kept_is_gate ? x : fk[i];
+                        }
+                    }
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float g = bf16_round(__uint_as_float(rg[ch][i]) * ag);
-                        const float u = bf16_round(__uint_as_float(ru[ch][i]) * au);
-                        v[i] = silu_gate(g, u);
-                    }
+                    for (int i = 0; i < 32; ++i) v[i] = silu_gate(g[i], u[i]);
+                    const Packed16 pk = pack_bf16(v);
                     const int c0 = half * 64 + ch * 32;
                     const int nvalid = sg.ncols - c0;
-                    if (box_tma) stage_chunk(v, ch);
-                    else if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
+                    if (box_tma) stage_packed(pk, ch);
+                    else if (row_ok && nvalid > 0 && !(p.debug & 4)) store_packed(out_row + sg.col0 + c0, pk, nvalid);
                 }
                 if (box_tma && !(p.debug & 4)) stage_flush(sg.col0 + half * 64, m_tile * 128 + quad * 32);
             } else {
                 const SubTile st = resolve_subtile(p, n_tile, half, 2);
                 const float alpha = p.alpha[st.seg];
-                uint32_t r[4][32];
-                if (owns_shared) {
-                    const int first = acc == 0 ? 2 : 0;       // the two 32-column groups inside the shared columns
-                    if (first == 2) {
-                        tmem_ld_x32(t_row + half * 128 + 64, r[2]);
-                        tmem_ld_x32(t_row + half * 128 + 96, r[3]);
-                        tmem_ld_wait();
-                        release_shared();
-                        tmem_ld_x32(t_row + half * 128 + 0, r[0]);
-                        tmem_ld_x32(t_row + half * 128 + 32, r[1]);
-                    } else {
-                        tmem_ld_x32(t_row + half * 128 + 0, r[0]);
-                        tmem_ld_x32(t_row + half * 128 + 32, r[1]);
-                        tmem_ld_wait();
-                        release_shared();
-                        tmem_ld_x32(t_row + half * 128 + 64, r[2]);
-                        tmem_ld_x32(t_row + half * 128 + 96, r[3]);
-                    }
-                } else {
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) tmem_ld_x32(t_row + half * 128 + ch * 32, r[ch]);
-                }
-                tmem_ld_wait();
-                release_acc();
-#pragma unroll
-                for (int bx = 0; bx < 2; ++bx) {
+                // the owner's shared columns are its chunks 2, 3 (accumulator 0) or 0, 1 (accumulator 1):
+                // that 64-column box goes first
+                const int first_box = (owns_shared && acc == 0) ? 1 : 0;
+#pragma unroll 1
+                for (int k = 0; k < 2; ++k) {
+                    const int bx = k ^ first_box;
+                    uint32_t r[2][32];
+                    tmem_ld_x32(t_row + half * 128 + bx * 64, r[0]);
+                    tmem_ld_x32(t_row + half * 128 + bx * 64 + 32, r[1]);
+                    tmem_ld_wait();
+                    if (k == 1) release_acc();
+                    else if (owns_shared) release_shared();
                     const bool box_tma = p.tma_store && (st.ncols - bx * 64) >= 64;
                     if (box_tma) stage_begin();
 #pragma unroll
                     for (int hc = 0; hc < 2; ++hc) {
-                        const int ch = bx * 2 + hc;
-                        const int c0 = ch * 32;
+                        const int c0 = bx * 64 + hc * 32;
                         const int nvalid = st.ncols - c0;
                         const int col = st.col0 + c0;
                         const bool live = row_ok && nvalid > 0;
                         float v[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[ch][i]) * alpha;
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[hc][i]) * alpha;
                         if (p.bias != nullptr && nvalid > 0) {
                             float b[32];
-                            load_row_chunk(p.bias + col, b, nvalid);
+                            unpack_bf16(load_packed(p.bias + col, nvalid), b);
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] += b[i];
                         }
                         if (p.epi == EPI_RESIDUAL && live) {
                             float res[32];
-                            load_row_chunk(p.residual + (size_t)row * p.ldo + col, res, nvalid);
+                            unpack_bf16(load_packed(p.residual + (size_t)row * p.ldo + col, nvalid), res);
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
                         }
-                        if (box_tma) stage_chunk(v, hc);
-                        else if (live && !(p.debug & 4)) store_row_chunk(out_row + col, v, nvalid);
+                        const Packed16 pk = pack_bf16(v);
+                        if (box_tma) stage_packed(pk, hc);
+                        else if (live && !(p.debug & 4)) store_packed(out_row + col, pk, nvalid);
                     }
                     if (box_tma && !(p.debug & 4)) stage_flush(st.col0 + bx * 64, m_tile * 128 + quad * 32);
                 }

@@ -196,9 +196,12 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on an mbarrier that may live in the other CTA of the pair.
+// Arrive on an mbarrier that may live in the other CTA of the pair.  CTA-scope release (the
+// default): the barriers signalled this way hand over tensor memory, whose ordering comes from
+// tcgen05.wait / tcgen05.fence, not generic-proxy data.  A cluster-scope release made every
+// arrive wait ~1000-1700 cycles for the SM's outstanding memory traffic.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 2-D tiled load into THIS CTA's shared memory whose completion bytes are credited to an
 // mbarrier of either CTA of the pair (cluster address).  Plain load: one destination CTA.
