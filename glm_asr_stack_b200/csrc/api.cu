@@ -99,7 +99,8 @@ enum Slot : int {
     WS_TMP = 5,       // SIMT-path epilogue staging
     WS_L_QKV = 6, WS_L_H1 = 7, WS_L_ACT = 8, WS_L_IN = 9, WS_L_OUT = 10,
     WS_WDEQ = 11,
-    WS_DBG = 12,      // cycle counters of timing experiments     // W4A16 large-M: dequantised bf16 weights
+    WS_DBG = 12,      // cycle counters of timing experiments
+    WS_L_ACTQ = 13, WS_L_ACTSF = 14,   // layer path: quantised SiLU-gate output handed to the down projection
 };
 
 static int num_sms() {
@@ -145,6 +146,17 @@ static bool no_tma_store() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("GLMASR_NO_TMA_STORE");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+// GLMASR_NO_FUSED_ACT_QUANT=1: the layer path writes the bf16 activation and quantises it with the
+// stand-alone kernel (for A/B comparisons against the quantising epilogue)
+static bool no_fused_act_quant() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_NO_FUSED_ACT_QUANT");
         v = (e && e[0] == '1') ? 1 : 0;
     }
     return v == 1;
@@ -277,6 +289,12 @@ struct FusedArgs {
     const __nv_bfloat16 *residual;
     const __nv_bfloat16 *bias;
     int M, K;
+    // W4A4 only.  xq / xq_sf: the activation is already quantised (e2m1 bytes [M, K/2] + tiled
+    // scales), x is ignored.  q_out / q_out_sf: EPI_SILU_GATE writes its result quantised with
+    // q_out_input_scale for the next GEMM instead of bf16 to out (pair kernel only).
+    const uint8_t *xq, *xq_sf;
+    uint8_t *q_out, *q_out_sf;
+    float q_out_input_scale;
 };
 
 static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
@@ -383,7 +401,10 @@ static int run_fused(const FusedArgs &a) {
         if (a.epi == EPI_SILU_GATE && (a.num_w != 2 || a.w[0].N != a.w[1].N)) return -1;
         if (a.epi == EPI_RESIDUAL && (a.num_w != 1 || a.residual == nullptr)) return -1;
     }
-    if (!tensor_core_eligible(a)) return run_simt(a);
+    if (!tensor_core_eligible(a)) {
+        if (a.xq != nullptr || a.q_out != nullptr) return -1;   // quantised hand-over exists on the tensor-core path only
+        return run_simt(a);
+    }
 
     // W4A16 with many rows: the in-kernel dequant (repeated for every 128-row tile) becomes the
     // bottleneck, so do what the reference does -- dequantise each weight once to bf16
@@ -432,10 +453,14 @@ static int run_fused(const FusedArgs &a) {
     const __nv_bfloat16 *x = a.x;
     int ldx = a.ldx;
     if (a.mode == GEMM_W4A4) {
-        uint8_t *xq = (uint8_t *)workspace_slot(WS_XQ, (size_t)a.M * a.K / 2);
-        uint8_t *xsf = (uint8_t *)workspace_slot(WS_XSF, tiled_sf_bytes(a.M, a.K));
-        launch_quantize_act(xq, nullptr, xsf, a.x, a.pre, a.input_scale, a.M, a.K, a.ldx, g_stream);
-        ++g_launches;
+        const uint8_t *xq = a.xq, *xsf = a.xq_sf;
+        if (xq == nullptr) {
+            uint8_t *q = (uint8_t *)workspace_slot(WS_XQ, (size_t)a.M * a.K / 2);
+            uint8_t *sf = (uint8_t *)workspace_slot(WS_XSF, tiled_sf_bytes(a.M, a.K));
+            launch_quantize_act(q, nullptr, sf, a.x, a.pre, a.input_scale, a.M, a.K, a.ldx, g_stream);
+            ++g_launches;
+            xq = q, xsf = sf;
+        }
         if (!make_tmap(&p.tm_a, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 2, (uint64_t)a.M,
                        (uint64_t)a.K / 2, 128, 128, true))
             return -1;
@@ -515,6 +540,14 @@ static int run_fused(const FusedArgs &a) {
                 tma_ok = make_tmap(&p.tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.n_out, (uint64_t)a.M,
                                    (uint64_t)a.ldo * 2, 64, 32, true);
             p.tma_store = tma_ok ? 1 : 0;
+            if (a.q_out != nullptr) {
+                if (a.epi != EPI_SILU_GATE || (p.seg_rows[0] % 64) != 0 || !(a.q_out_input_scale > 0.0f)) return -1;
+                p.q_packed = a.q_out;
+                p.q_sf = a.q_out_sf;
+                p.q_inv_in = 1.0f / a.q_out_input_scale;
+                p.q_ld = p.seg_rows[0] / 2;
+                p.q_sf_chunks = p.seg_rows[0] / 64;
+            }
             TimedLaunch tl;
             if (g_profile) {
                 cudaEventCreate(&tl.start);
@@ -524,6 +557,7 @@ static int run_fused(const FusedArgs &a) {
                 tl.flops = 2.0 * a.M * (double)n_rows * a.K;
                 tl.bytes = (double)n_rows * a.K * 0.5625 + (double)a.M * a.K * 0.5625 + 2.0 * a.M * p.n_out +
                            (a.epi == EPI_RESIDUAL ? 2.0 * a.M * p.n_out : 0.0);
+                if (a.q_out != nullptr) tl.bytes -= (2.0 - 0.5625) * a.M * p.n_out;   // e2m1 + scales instead of bf16
                 cudaEventRecord(tl.start, g_stream);
             }
             if (launch_umma_gemm_pair(p, pairs, g_stream) != cudaSuccess) return -1;
@@ -535,6 +569,8 @@ static int run_fused(const FusedArgs &a) {
             return 0;
         }
     }
+
+    if (a.q_out != nullptr) return -1;      // the quantising epilogue exists in the pair kernel only
 
     // tile shape: two weight sub-tiles per CTA tile when that still fills the machine
     int nb;
@@ -778,6 +814,15 @@ extern "C" int glmasr_argmax_rows(const uint16_t *logits, int *out_tokens, int r
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+// True when gate|up (K = H, 2 x F columns, SiLU-gate) at M rows runs on the CTA-pair kernel, whose
+// epilogue can emit the down projection's quantised operand.  Mirrors the selection in run_fused.
+static bool silu_quant_fusable(int M, int H, int F) {
+    if (force_simt() || !use_pair_kernel() || no_fused_act_quant()) return false;
+    if (M < 512 || (H % 256) != 0 || (F % 256) != 0) return false;
+    const int m_pairs = ((M + 127) / 128 + 1) / 2;
+    return m_pairs * ((F + 127) / 128) >= num_sms() / 2;
+}
+
 static int layer_proj_device(int mode, uint16_t *hidden_out, const uint16_t *hidden_in, const glmasr_layer_weights *lw,
                              int M) {
     const int H = lw->hidden, F = lw->ffn;
@@ -795,6 +840,48 @@ static int layer_proj_device(int mode, uint16_t *hidden_out, const uint16_t *hid
     rc = glmasr_fp4_linear_fused(mode, h1, H, qkv, nqkv, &lw->o, 1, lw->in_o, nullptr, nullptr, GLMASR_EPI_RESIDUAL,
                                  hidden_in, M, H);
     if (rc != 0) return rc;
+    if (mode == GLMASR_MODE_W4A4 && silu_quant_fusable(M, H, F) && lw->in_down > 0.0f && lw->gate.w_scales != nullptr &&
+        lw->up.w_scales != nullptr && lw->down.w_scales != nullptr && lw->in_gate_up > 0.0f) {
+        // gate|up's SiLU-gate epilogue quantises its result for the down projection (the same bytes
+        // the stand-alone quantiser would produce from the bf16 activation), so the bf16
+        // intermediate is never written and the separate quantiser launch is gone
+        uint8_t *aq = (uint8_t *)workspace_slot(WS_L_ACTQ, (size_t)M * F / 2);
+        uint8_t *asf = (uint8_t *)workspace_slot(WS_L_ACTSF, tiled_sf_bytes(M, F));
+        FusedArgs g;
+        memset(&g, 0, sizeof(g));
+        g.mode = GEMM_W4A4;
+        g.out = (__nv_bfloat16 *)act;
+        g.ldo = F;
+        g.x = (const __nv_bfloat16 *)h1;
+        g.ldx = H;
+        g.w = gu;
+        g.num_w = 2;
+        g.input_scale = lw->in_gate_up;
+        g.epi = EPI_SILU_GATE;
+        g.M = M;
+        g.K = H;
+        g.q_out = aq;
+        g.q_out_sf = asf;
+        g.q_out_input_scale = lw->in_down;
+        rc = run_fused(g);
+        if (rc != 0) return rc;
+        FusedArgs d;
+        memset(&d, 0, sizeof(d));
+        d.mode = GEMM_W4A4;
+        d.out = (__nv_bfloat16 *)hidden_out;
+        d.ldo = H;
+        d.ldx = F;
+        d.xq = aq;
+        d.xq_sf = asf;
+        d.w = &lw->down;
+        d.num_w = 1;
+        d.input_scale = lw->in_down;
+        d.epi = EPI_RESIDUAL;
+        d.residual = (const __nv_bfloat16 *)h1;
+        d.M = M;
+        d.K = F;
+        return run_fused(d);
+    }
     rc = glmasr_fp4_linear_fused(mode, act, F, h1, H, gu, 2, lw->in_gate_up, nullptr, nullptr, GLMASR_EPI_SILU_GATE,
                                  nullptr, M, H);
     if (rc != 0) return rc;

@@ -131,24 +131,11 @@ __global__ void quantize_act_kernel(uint8_t *__restrict__ packed_out, uint8_t *_
             v[2 * j + 1] = v[2 * j + 1] * __uint_as_float(pw[j] & 0xFFFF0000u);
         }
     }
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    const float scale = amax > 0.0f ? __fdiv_rn(inv_in * amax, 6.0f) : 0.0f;
-    const __nv_fp8_e4m3 s8(scale);
-    const float scale_rounded = scale > 0.0f ? (float)s8 : 0.0f;
-    const float os = scale_rounded > 0.0f ? __fdiv_rn(inv_in, scale_rounded) : 0.0f;
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t q = __nv_cvt_float2_to_fp4x2(make_float2(v[2 * j] * os, v[2 * j + 1] * os), __NV_E2M1,
-                                                    cudaRoundNearest) & 0xFFu;
-        if (j < 4) lo |= q << (8 * j);
-        else hi |= q << (8 * (j - 4));
-    }
+    uint32_t lo, hi;
+    const uint32_t s8 = quantize_block16(v, inv_in, lo, hi);
     *reinterpret_cast<uint2 *>(packed_out + (size_t)r * (K >> 1) + (size_t)b * 8) = make_uint2(lo, hi);
-    if (scale_rowmajor) scale_rowmajor[(size_t)r * blocks_per_row + b] = s8.__x;
-    if (scale_swizzled) scale_swizzled[swizzled_sf_index(r, b, (blocks_per_row + 3) >> 2)] = s8.__x;
+    if (scale_rowmajor) scale_rowmajor[(size_t)r * blocks_per_row + b] = (uint8_t)s8;
+    if (scale_swizzled) scale_swizzled[swizzled_sf_index(r, b, (blocks_per_row + 3) >> 2)] = (uint8_t)s8;
 }
 
 void launch_quantize_act(uint8_t *packed_out, uint8_t *scale_rowmajor, uint8_t *scale_swizzled,

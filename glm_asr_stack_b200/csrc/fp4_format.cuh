@@ -28,4 +28,29 @@ __device__ __forceinline__ float e4m3_to_float_ref(uint32_t b) {
     return (b & 0x80u) ? -mag : mag;
 }
 
+// One 16-element block of the activation quantiser (reference: Infer-engine/cuda/nvfp4_cutlass.cu:35-87):
+//   amax = max |v| ; scale = (inv_in * amax) / 6 ; s8 = e4m3(scale) ; os = inv_in / float(s8)
+//   q_j = e2m1(v_j * os), even j in the low nibble.
+// Returns the e4m3 scale byte; lo / hi receive the 8 packed bytes.  Used by the stand-alone
+// quantiser and by GEMM epilogues that emit the next GEMM's operand directly, so both produce
+// the same bytes.
+__device__ __forceinline__ uint32_t quantize_block16(const float (&v)[16], float inv_in, uint32_t &lo, uint32_t &hi) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const float scale = amax > 0.0f ? __fdiv_rn(inv_in * amax, 6.0f) : 0.0f;
+    const __nv_fp8_e4m3 s8(scale);
+    const float scale_rounded = scale > 0.0f ? (float)s8 : 0.0f;
+    const float os = scale_rounded > 0.0f ? __fdiv_rn(inv_in, scale_rounded) : 0.0f;
+    lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t q = __nv_cvt_float2_to_fp4x2(make_float2(v[2 * j] * os, v[2 * j + 1] * os), __NV_E2M1,
+                                                    cudaRoundNearest) & 0xFFu;
+        if (j < 4) lo |= q << (8 * j);
+        else hi |= q << (8 * (j - 4));
+    }
+    return (uint32_t)s8.__x;
+}
+
 }  // namespace glmasr

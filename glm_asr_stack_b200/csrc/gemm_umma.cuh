@@ -44,6 +44,14 @@ struct alignas(64) GemmParams {
     const __nv_bfloat16 *residual;
     const __nv_bfloat16 *bias;
     int epi;
+    // EPI_SILU_GATE only, optional: emit the activation already quantised for the next W4A4 GEMM
+    // (e2m1 bytes [M, q_ld] + 128x4-tiled e4m3 scales with q_sf_chunks 512-byte chunks per row
+    // tile) instead of bf16.  Same bytes as the stand-alone quantiser run on the bf16 result.
+    uint8_t *q_packed;
+    uint8_t *q_sf;
+    float q_inv_in;                     // 1 / input_scale of the consuming GEMM
+    int q_ld;                           // bytes per packed row (= columns / 2)
+    int q_sf_chunks;                    // ceil(columns / 64)
     int num_m_tiles, num_n_tiles;
     int num_k_blocks;                   // K steps of 128 operand bytes per row (W4A4: 256 elements, else 64)
     int sf_k_chunks;                    // W4A4: 512-byte scale chunks per 128-row tile along K (= ceil(K/64))

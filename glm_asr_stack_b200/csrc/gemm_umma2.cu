@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 const SubTile sg = resolve_subtile(p, n_tile, 0, 2);
                 const float ag = p.alpha[0], au = p.alpha[1];
                 const uint32_t g_col = t_row + half * 64, u_col = t_row + 128 + half * 64;
-                const bool box_tma = p.tma_store && (sg.ncols - half * 64) >= 64;
+                const bool box_tma = p.tma_store && p.q_packed == nullptr && (sg.ncols - half * 64) >= 64;
                 // The owner's chunks in the shared columns (its up columns in accumulator 0, its gate
                 // columns in accumulator 1) are read first, scaled, rounded and kept packed.
                 const bool kept_is_gate = acc == 1;
@@ -347,9 +347,30 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = silu_gate(g[i], u[i]);
-                    const Packed16 pk = pack_bf16(v);
                     const int c0 = half * 64 + ch * 32;
                     const int nvalid = sg.ncols - c0;
+                    if (p.q_packed != nullptr) {
+                        // the next GEMM's operand: quantise the bf16-rounded products in 16-column blocks
+                        uint32_t q[4], sf = 0;
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            float blk[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) blk[j] = bf16_round(v[16 * b + j]);
+                            sf |= quantize_block16(blk, p.q_inv_in, q[2 * b], q[2 * b + 1]) << (8 * b);
+                        }
+                        if (row_ok && nvalid >= 32) {
+                            const int col = sg.col0 + c0;
+                            *reinterpret_cast<uint4 *>(p.q_packed + (size_t)row * p.q_ld + (col >> 1)) =
+                                make_uint4(q[0], q[1], q[2], q[3]);
+                            // tiled scale layout: chunk (row tile, col / 64), byte (row % 32) * 16 + (row / 32 % 4) * 4 + block
+                            uint8_t *sfp = p.q_sf + ((size_t)m_tile * p.q_sf_chunks + (col >> 6)) * 512 + lane * 16 +
+                                           quad * 4 + ((col >> 4) & 3);
+                            *reinterpret_cast<uint16_t *>(sfp) = (uint16_t)sf;
+                        }
+                        continue;
+                    }
+                    const Packed16 pk = pack_bf16(v);
                     if (box_tma) stage_packed(pk, ch);
                     else if (row_ok && nvalid > 0 && !(p.debug & 4)) store_packed(out_row + sg.col0 + c0, pk, nvalid);
                 }

@@ -328,3 +328,35 @@ def test_pair_kernel_repeat_launches_stay_identical(ops):
             if it % 20 == 19:
                 assert torch.equal(a, first[0]) and torch.equal(b, first[1]) and torch.equal(c, first[2])
     assert ops.status() == 0
+
+
+def test_layer_proj_quantising_epilogue_equals_unfused_chain(ops):
+    """At prefill sizes the layer path lets gate|up's SiLU-gate epilogue write the down projection's
+    quantised operand.  That must give exactly the bytes of the chain of separate calls (bf16
+    activation, stand-alone quantiser), and a row sample is checked against the CPU oracle's chain."""
+    from glm_asr_stack_b200 import synth
+    H, F, M = 2048, 6144, 2600            # 11 row pairs x 48 column tiles: the CTA-pair kernel; M tail of 40 rows
+    names = [("q", H, H), ("k", 512, H), ("v", 512, H), ("o", H, H), ("gate", F, H), ("up", F, H), ("down", H, F)]
+    w = {n: synth.seeded_weight_fast(N, K, 160 + i) for i, (n, N, K) in enumerate(names)}
+    x = synth.seeded_activation(M, H, 170)
+    isc = {"qkv": synth.default_input_scale(x), "o": 0.004, "gate_up": 0.004, "down": 0.002}
+    w["q"].input_scale = w["k"].input_scale = w["v"].input_scale = isc["qkv"]
+    w["o"].input_scale = isc["o"]
+    w["gate"].input_scale = w["up"].input_scale = isc["gate_up"]
+    w["down"].input_scale = isc["down"]
+    lw = ops.make_layer_weights(w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, F)
+    got = ops.layer_proj(ops.MODE_W4A4, x, lw)
+    qkv = ops.fp4_linear_fused(ops.MODE_W4A4, x, [w["q"], w["k"], w["v"]], input_scale=isc["qkv"])
+    h1 = ops.fp4_linear_fused(ops.MODE_W4A4, qkv[:, :H], [w["o"]], epilogue=ops.EPI_RESIDUAL, residual=x,
+                              input_scale=isc["o"])
+    act = ops.fp4_linear_fused(ops.MODE_W4A4, h1, [w["gate"], w["up"]], epilogue=ops.EPI_SILU_GATE,
+                               input_scale=isc["gate_up"])
+    want = ops.fp4_linear_fused(ops.MODE_W4A4, act, [w["down"]], epilogue=ops.EPI_RESIDUAL, residual=h1,
+                                input_scale=isc["down"])
+    assert torch.equal(got, want)
+    # the quantised hand-over itself: stand-alone quantiser on the bf16 activation, row sample vs oracle
+    rows = [0, 31, 127, 128, 2559, 2599]
+    pk, sc = ops.quantize_bf16_to_fp4(act[rows].contiguous(), isc["down"])
+    opk, osc = o.quantize_bf16_to_fp4(bits_of(act[rows]), isc["down"])
+    assert np.array_equal(pk.cpu().numpy(), opk) and np.array_equal(sc.cpu().numpy(), osc)
+    assert ops.status() == 0
