@@ -331,9 +331,15 @@ def main():
         peak, peak_src = peaks["bf16_tflops"], "measured bf16 burst (MEASURED_PEAKS.json)"
     else:
         peak, peak_src = 1590.0, "fallback bf16 burst"
-    roofline = {"bound": "tensor", "kernel": "umma_gemm_kernel (gate|up, SiLU-gate epilogue)", "achieved": achieved,
+    # DRAM bytes of one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one
+    # `ncu --set full` capture of this workload's gate|up launch at M = 10000, W4A4: 25.96 MB read + 1.01 MB
+    # written; the quantised output stays in L2).  Not captured for other modes or row counts.
+    traffic = 26.97e6 if (args.mode == "w4a4" and M == M_TOKENS) else None
+    kname = ("umma_gemm_pair_kernel (gate|up, SiLU-gate + quantising epilogue)" if args.mode == "w4a4"
+             else "umma_gemm_kernel (gate|up, SiLU-gate epilogue)")
+    roofline = {"bound": "tensor", "kernel": kname, "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
-                "traffic": None, "launch_ms": top_ms, "gemm_ms_per_step": all_ms,
+                "traffic": traffic, "launch_ms": top_ms, "gemm_ms_per_step": all_ms,
                 "achieved_gbs": top[0][2] / (top_ms * 1e-3) / 1e9,
                 "frac_of_measured_bf16": (achieved / peaks["bf16_tflops"]) if peaks else None}
 
@@ -370,7 +376,7 @@ def main():
                     "ms_per_step": e2e_s / args.steps * 1e3},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         }
-        if not args.no_cpu_baseline and world >= 1:
+        if not args.no_cpu_baseline and world == 1:
             tf, sec, threads = cpu_reference_leg(2, 1, 512)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"512 of {M_TOKENS} rows, all four projections, full weights, "
