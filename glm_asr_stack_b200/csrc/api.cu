@@ -391,6 +391,10 @@ static int run_simt(const FusedArgs &a) {
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+// Row count that picks the W4A16 route while a larger call is being served in row chunks, so that
+// every chunk takes the route (and gives the bytes) of the whole call.
+static int g_route_rows = 0;
+
 static int run_fused(const FusedArgs &a) {
     if (a.M <= 0 || a.K <= 0) return -1;
     if (a.mode != GEMM_BF16) {
@@ -409,7 +413,7 @@ static int run_fused(const FusedArgs &a) {
     // W4A16 with many rows: the in-kernel dequant (repeated for every 128-row tile) becomes the
     // bottleneck, so do what the reference does -- dequantise each weight once to bf16
     // (Infer-engine/cuda/kernels.cu:1316) -- and run the bf16 GEMM on the result.
-    if (a.mode == GEMM_W4A16 && a.M >= w4a16_dequant_once_rows()) {
+    if (a.mode == GEMM_W4A16 && (a.M > g_route_rows ? a.M : g_route_rows) >= w4a16_dequant_once_rows()) {
         size_t elems = 0;
         for (int i = 0; i < a.num_w; ++i) elems += (size_t)a.w[i].N * a.K;
         __nv_bfloat16 *wd = (a.weight_scratch != nullptr && a.num_w == 1)
@@ -895,16 +899,77 @@ extern "C" int glmasr_fp4_layer_proj(int mode, uint16_t *hidden_out, const uint1
     return layer_proj_device(mode, hidden_out, hidden_in, lw, M);
 }
 
+// Host-buffer call: the rows are independent, so the call is cut into row chunks and the three
+// legs of consecutive chunks overlap -- chunk i+1 crosses PCIe host->device while chunk i is
+// computed and chunk i-1 goes device->host (the link is full duplex).  Same bytes as one pass.
+static cudaStream_t g_copy_in = nullptr, g_copy_out = nullptr;
+static constexpr int kMaxHostChunks = 16;
+static cudaEvent_t g_ev_in[kMaxHostChunks], g_ev_done[kMaxHostChunks];
+
+static int host_chunks(int M) {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_HOST_CHUNKS");
+        v = (e && e[0]) ? atoi(e) : 8;
+        if (v < 1) v = 1;
+        if (v > kMaxHostChunks) v = kMaxHostChunks;
+    }
+    return M >= 2048 ? v : 1;
+}
+
 extern "C" int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16_t *hidden_in_host,
                                           const glmasr_layer_weights *lw, int M) {
     if (hidden_out_host == nullptr || hidden_in_host == nullptr || lw == nullptr || M <= 0) return -1;
-    const size_t bytes = (size_t)M * lw->hidden * 2;
-    uint16_t *din = (uint16_t *)workspace_slot(WS_L_IN, bytes);
-    uint16_t *dout = (uint16_t *)workspace_slot(WS_L_OUT, bytes);
-    if (cudaMemcpyAsync(din, hidden_in_host, bytes, cudaMemcpyHostToDevice, g_stream) != cudaSuccess) return -1;
-    const int rc = layer_proj_device(mode, dout, din, lw, M);
-    if (rc != 0) return rc;
-    if (cudaMemcpyAsync(hidden_out_host, dout, bytes, cudaMemcpyDeviceToHost, g_stream) != cudaSuccess) return -1;
+    const size_t row_bytes = (size_t)lw->hidden * 2;
+    const size_t bytes = (size_t)M * row_bytes;
+    uint8_t *din = (uint8_t *)workspace_slot(WS_L_IN, bytes);
+    uint8_t *dout = (uint8_t *)workspace_slot(WS_L_OUT, bytes);
+    const int chunks = host_chunks(M);
+    if (chunks == 1) {
+        if (cudaMemcpyAsync(din, hidden_in_host, bytes, cudaMemcpyHostToDevice, g_stream) != cudaSuccess) return -1;
+        const int rc = layer_proj_device(mode, (uint16_t *)dout, (const uint16_t *)din, lw, M);
+        if (rc != 0) return rc;
+        if (cudaMemcpyAsync(hidden_out_host, dout, bytes, cudaMemcpyDeviceToHost, g_stream) != cudaSuccess) return -1;
+        return cudaStreamSynchronize(g_stream) == cudaSuccess ? 0 : -1;
+    }
+    if (g_copy_in == nullptr) {
+        if (cudaStreamCreateWithFlags(&g_copy_in, cudaStreamNonBlocking) != cudaSuccess) return -1;
+        if (cudaStreamCreateWithFlags(&g_copy_out, cudaStreamNonBlocking) != cudaSuccess) return -1;
+        for (int i = 0; i < kMaxHostChunks; ++i) {
+            if (cudaEventCreateWithFlags(&g_ev_in[i], cudaEventDisableTiming) != cudaSuccess) return -1;
+            if (cudaEventCreateWithFlags(&g_ev_done[i], cudaEventDisableTiming) != cudaSuccess) return -1;
+        }
+    }
+    // whole 256-row tile pairs per chunk
+    int rows_per = ((M + chunks - 1) / chunks + 255) / 256 * 256;
+    // everything queued so far on the compute stream (it may still use the staging buffers) comes first
+    if (cudaEventRecord(g_ev_done[0], g_stream) != cudaSuccess) return -1;
+    if (cudaStreamWaitEvent(g_copy_in, g_ev_done[0], 0) != cudaSuccess) return -1;
+    int n = 0;
+    for (int r0 = 0; r0 < M; r0 += rows_per, ++n) {
+        const int rows = M - r0 < rows_per ? M - r0 : rows_per;
+        const size_t off = (size_t)r0 * row_bytes;
+        if (cudaMemcpyAsync(din + off, (const uint8_t *)hidden_in_host + off, (size_t)rows * row_bytes,
+                            cudaMemcpyHostToDevice, g_copy_in) != cudaSuccess)
+            return -1;
+        if (cudaEventRecord(g_ev_in[n], g_copy_in) != cudaSuccess) return -1;
+    }
+    n = 0;
+    for (int r0 = 0; r0 < M; r0 += rows_per, ++n) {
+        const int rows = M - r0 < rows_per ? M - r0 : rows_per;
+        const size_t off = (size_t)r0 * row_bytes;
+        if (cudaStreamWaitEvent(g_stream, g_ev_in[n], 0) != cudaSuccess) return -1;
+        g_route_rows = M;
+        const int rc = layer_proj_device(mode, (uint16_t *)(dout + off), (const uint16_t *)(din + off), lw, rows);
+        g_route_rows = 0;
+        if (rc != 0) return rc;
+        if (cudaEventRecord(g_ev_done[n], g_stream) != cudaSuccess) return -1;
+        if (cudaStreamWaitEvent(g_copy_out, g_ev_done[n], 0) != cudaSuccess) return -1;
+        if (cudaMemcpyAsync((uint8_t *)hidden_out_host + off, dout + off, (size_t)rows * row_bytes,
+                            cudaMemcpyDeviceToHost, g_copy_out) != cudaSuccess)
+            return -1;
+    }
+    if (cudaStreamSynchronize(g_copy_out) != cudaSuccess) return -1;
     return cudaStreamSynchronize(g_stream) == cudaSuccess ? 0 : -1;
 }
 

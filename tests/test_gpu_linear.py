@@ -360,3 +360,24 @@ def test_layer_proj_quantising_epilogue_equals_unfused_chain(ops):
     opk, osc = o.quantize_bf16_to_fp4(bits_of(act[rows]), isc["down"])
     assert np.array_equal(pk.cpu().numpy(), opk) and np.array_equal(sc.cpu().numpy(), osc)
     assert ops.status() == 0
+
+
+def test_layer_proj_host_chunked_equals_device(ops):
+    """From 2048 rows the host-buffer call is cut into row chunks whose copies and compute overlap;
+    the result must be the bytes of the single device-resident pass (rows are independent)."""
+    from glm_asr_stack_b200 import synth
+    H, F, M = 1024, 3072, 2600
+    names = [("q", H, H), ("k", 256, H), ("v", 256, H), ("o", H, H), ("gate", F, H), ("up", F, H), ("down", H, F)]
+    w = {n: synth.seeded_weight_fast(N, K, 260 + i) for i, (n, N, K) in enumerate(names)}
+    for t in w.values():
+        t.input_scale = 0.01
+    lw = ops.make_layer_weights(w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, F)
+    x = synth.seeded_activation(M, H, 270)
+    hin = x.cpu().pin_memory()
+    for mode in (ops.MODE_W4A4, ops.MODE_W4A16):
+        dev = ops.layer_proj(mode, x, lw)
+        for _ in range(3):                       # repeated calls reuse the staging buffers and events
+            hout = torch.zeros_like(hin).pin_memory()
+            ops.layer_proj_host(mode, hin, hout, lw)
+            assert torch.equal(dev.cpu(), hout), mode
+    assert ops.status() == 0
