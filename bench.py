@@ -21,6 +21,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+from glm_asr_stack_b200 import replicas  # noqa: E402  (host-side rank logic; loads the C-ABI library, no GPU needed)
+
 HIDDEN, FFN, KV, M_TOKENS = 2048, 6144, 512, 10000
 METRIC, UNIT = "fp4_linear_tflops", "TFLOP/s"
 WORKLOAD = "config1: one decoder layer of FP4 projections at prefill, M=10000, hidden 2048, qkv N=3072, o N=2048, gate-up N=12288 (+SiLU), down K=6144 (+residual)"
@@ -124,10 +126,7 @@ def run_decode(args, rank, local_rank, world):
     from glm_asr_stack_b200 import engine, ops, workloads
 
     torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
     model = workloads.build_decoder(layers=args.layers)
     state = workloads.build_decode_state(model.cfg, num_seqs=args.seqs)
     cfg, lm, n, vocab = model.cfg, model.lm_head, args.seqs, model.cfg.vocab_size
@@ -178,10 +177,8 @@ def run_decode(args, rank, local_rank, world):
         tok_host.copy_(step(ids_host.cuda(non_blocking=True)), non_blocking=True)
         torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
-    if dist is not None:
-        t = torch.tensor([ms, e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+    ms = replicas.max_over_ranks(ms, dist, "cuda")
+    e2e_ms = replicas.max_over_ranks(e2e_ms, dist, "cuda")
     H, KV = cfg.dec_hidden, cfg.dec_kv_heads * cfg.dec_head_dim
     # algorithmic bytes per step: FP4 weights once, K and V of every cached token once, the new token's K/V,
     # embedding rows, logits written then read by the arg-max
@@ -191,13 +188,13 @@ def run_decode(args, rank, local_rank, world):
     if rank == 0:
         gbs = bytes_step / (ms * 1e-3) / 1e9
         print(json.dumps({
-            "metric": "decode_tok_per_s", "value": world * n / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "metric": "decode_tok_per_s", "value": replicas.whole_job_rate(n, world, ms * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
             "config": {"workload": f"config2: batched decode step, {cfg.dec_layers} layers, {n} sequences, paged bf16 KV "
                                    "(16-token pages, context 200-450), FP4 lm_head over 59264 + arg-max",
                        "l2": f"{bytes_step / 1e9:.2f} GB touched per step > 126 MB L2"},
-            "e2e": {"value": world * n / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": n * 4,
+            "e2e": {"value": replicas.whole_job_rate(n, world, e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": n * 4,
                     "d2h_bytes_per_step": n * 4, "ms_per_step": e2e_ms},
             "gpu_launches": int(launches), "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "whole decode step (weights + KV stream)", "achieved": gbs, "peak": peak,
@@ -226,9 +223,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank, local_rank, world = replicas.rank_info()
 
     if args.impl == "reference":
         run_reference(args, rank)
@@ -245,10 +240,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path")
     torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
 
     mode = ops.MODE_W4A4 if args.mode == "w4a4" else ops.MODE_W4A16
     M = args.rows
@@ -305,12 +297,9 @@ def main():
     ms_total = e0.elapsed_time(e1)
     launches = ops.launch_count() - launches0
     clocks = sampler.stop()
-    if dist is not None:
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    ms_total = replicas.max_over_ranks(ms_total, dist, "cuda")
     ms_step = ms_total / args.steps
-    value = world * layer_flops(M) / (ms_step * 1e-3) / 1e12
+    value = replicas.whole_job_rate(layer_flops(M), world, ms_step * 1e-3) / 1e12
 
     # ---- per-launch kernel timing for the roofline (separate pass, events around each GEMM) ----
     ops.profile_enable(True)
@@ -352,11 +341,8 @@ def main():
         ops.layer_proj_host(mode, hin[i % 2], hout, layers[i % n_sets])
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_val = world * layer_flops(M) * args.steps / e2e_s / 1e12
+    e2e_s = replicas.max_over_ranks(e2e_s, dist, "cuda")
+    e2e_val = replicas.whole_job_rate(layer_flops(M), world, e2e_s / args.steps) / 1e12
     bytes_io = M * HIDDEN * 2
     _st = ops.status()
     assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
