@@ -62,6 +62,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // swizzled byte offset of 16-byte chunk c (0..15) of row r (0..15) inside a 4 KB tile
 __device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * kRowBytes + ((c ^ (r & 7)) << 4)); }
 
+// PAGE_ALIGNED: block_size is a multiple of the 16-token tile, so a tile lies in one page: one block-table
+// lookup and one division per tile instead of one per row, and row addresses by pointer increments.
+template <bool PAGE_ALIGNED>
 __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel(
     __nv_bfloat16 *__restrict__ out, int ldo, const __nv_bfloat16 *__restrict__ query, int ldq,
     const __nv_bfloat16 *__restrict__ key_cache, const __nv_bfloat16 *__restrict__ value_cache,
@@ -111,17 +114,36 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
         const int tile = warp + kWarps * i;
         const uint32_t kdst = ring + (uint32_t)(i % kStages) * (2 * kTileBytes);
         const uint32_t vdst = kdst + kTileBytes;
+        const int c = lane & 15;                        // 16-byte chunk of the row
+        if (PAGE_ALIGNED) {
+            const int t0 = tile * kTile;
+            const int page = t0 / block_size;
+            const int blk = bt[page];
+            const bool page_ok = blk >= 0;
+            const int r0 = lane >> 4;
+            size_t off = page_ok ? ((size_t)blk * block_size + (size_t)(t0 - page * block_size) + r0) * row_elems + head_off + c * 8 : 0;
+            const int rows_left = seq_len - t0;         // rows r < rows_left exist
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int r = j * 2 + (lane >> 4);          // row of the tile
-            const int c = lane & 15;                    // 16-byte chunk of the row
-            const int t = tile * kTile + r;
-            int blk = -1;
-            if (t < seq_len) blk = bt[t / block_size];
-            const bool valid = blk >= 0;
-            const size_t base = valid ? ((size_t)blk * block_size + (size_t)(t % block_size)) * row_elems + head_off + c * 8 : 0;
-            cp_async16_zfill(kdst + tile_off(r, c), key_cache + base, valid);
-            cp_async16_zfill(vdst + tile_off(r, c), value_cache + base, valid);
+            for (int j = 0; j < 8; ++j) {
+                const int r = j * 2 + r0;
+                const bool valid = page_ok && r < rows_left;
+                const size_t o = valid ? off : 0;
+                cp_async16_zfill(kdst + tile_off(r, c), key_cache + o, valid);
+                cp_async16_zfill(vdst + tile_off(r, c), value_cache + o, valid);
+                off += 2 * row_elems;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r = j * 2 + (lane >> 4);          // row of the tile
+                const int t = tile * kTile + r;
+                int blk = -1;
+                if (t < seq_len) blk = bt[t / block_size];
+                const bool valid = blk >= 0;
+                const size_t base = valid ? ((size_t)blk * block_size + (size_t)(t % block_size)) * row_elems + head_off + c * 8 : 0;
+                cp_async16_zfill(kdst + tile_off(r, c), key_cache + base, valid);
+                cp_async16_zfill(vdst + tile_off(r, c), value_cache + base, valid);
+            }
         }
     };
 
@@ -158,10 +180,11 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
         // this lane holds, for query head g, the scores of tokens t0 + {2tq, 2tq+1, 8+2tq, 9+2tq}
         float sc[4] = {s0[0], s0[1], s1[0], s1[1]};
         float tmax = -INFINITY;
+        const bool tile_page_ok = PAGE_ALIGNED ? bt[t0 / block_size] >= 0 : true;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int t = t0 + (e >> 1) * 8 + tq * 2 + (e & 1);
-            const bool ok = t < seq_len && bt[t / block_size] >= 0;
+            const bool ok = PAGE_ALIGNED ? (tile_page_ok && t < seq_len) : (t < seq_len && bt[t / block_size] >= 0);
             sc[e] = ok ? sc[e] * scale : -INFINITY;
             tmax = fmaxf(tmax, sc[e]);
         }
@@ -241,16 +264,23 @@ bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_b
     if (num_seqs <= 0) return true;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(paged_decode_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(paged_decode_attention_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kAttnSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(paged_decode_attention_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kAttnSmem) != cudaSuccess)
             return false;
         configured = true;
     }
     const float scale = 1.0f / sqrtf((float)head_dim);
     dim3 grid(num_kv_heads, num_seqs);
-    paged_decode_attention_mma_kernel<<<grid, kWarps * 32, kAttnSmem, st>>>(out, ldo, query, ldq, key_cache, value_cache,
-                                                                           block_tables, seq_lens, num_kv_heads, group,
-                                                                           block_size, max_blocks_per_seq, scale);
+    if (block_size % kTile == 0)
+        paged_decode_attention_mma_kernel<true><<<grid, kWarps * 32, kAttnSmem, st>>>(
+            out, ldo, query, ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
+            max_blocks_per_seq, scale);
+    else
+        paged_decode_attention_mma_kernel<false><<<grid, kWarps * 32, kAttnSmem, st>>>(
+            out, ldo, query, ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
+            max_blocks_per_seq, scale);
     return true;
 }
 

@@ -79,7 +79,7 @@ def _paged_case(rng, n_seqs, kvh, hd, bs, max_ctx, num_blocks):
     return lens, bt, kc, vc
 
 
-@pytest.mark.parametrize("qh,kvh,bs", [(16, 4, 16), (8, 8, 16), (16, 4, 128), (4, 1, 8)])
+@pytest.mark.parametrize("qh,kvh,bs", [(16, 4, 16), (8, 8, 16), (16, 4, 128), (4, 1, 8), (16, 4, 48), (8, 2, 24)])
 def test_paged_decode_attention(ops, ref, qh, kvh, bs):
     rng = np.random.default_rng(qh * 100 + bs)
     hd, n = 128, 12
