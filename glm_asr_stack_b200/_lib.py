@@ -47,6 +47,8 @@ SIGNATURES = {
     "paged_decode_attention": (None, [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]),
     "decoder_decode_step_batched": (None, [P, P, P, P, P, P, P, c_int, P, P, P]),
     "glmasr_rope_single_token": (None, [P, P, c_int, c_int, c_int]),
+    "glmasr_rope_qk_cache": (c_int, [P, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int]),
+    "glmasr_rmsnorm_quant": (c_int, [P, P, P, P, c_float, c_float, c_int, c_int]),
     "glmasr_decoder_forget_weights": (None, []),
     "glmasr_fp4_linear_fused": (c_int, [c_int, P, c_int, P, c_int, POINTER(Fp4Weight), c_int, c_float, P, P,
                                         c_int, P, c_int, c_int]),

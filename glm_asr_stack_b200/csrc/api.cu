@@ -39,7 +39,7 @@ struct TimedLaunch {
 };
 static std::vector<TimedLaunch> g_timed;
 
-static constexpr int kSlots = 24;   // 0..12 used here, 13..23 by the decode step (decoder_step.cu)
+static constexpr int kSlots = 32;   // 0..12 and 24..25 used here, 13..23 and 26..31 by the decode step (decoder_step.cu)
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
 
@@ -100,7 +100,7 @@ enum Slot : int {
     WS_L_QKV = 6, WS_L_H1 = 7, WS_L_ACT = 8, WS_L_IN = 9, WS_L_OUT = 10,
     WS_WDEQ = 11,
     WS_DBG = 12,      // cycle counters of timing experiments
-    WS_L_ACTQ = 13, WS_L_ACTSF = 14,   // layer path: quantised SiLU-gate output handed to the down projection
+    WS_L_ACTQ = 24, WS_L_ACTSF = 25,   // layer path: quantised SiLU-gate output handed to the down projection
 };
 
 static int num_sms() {
@@ -609,6 +609,35 @@ static int run_fused(const FusedArgs &a) {
         g_timed.push_back(tl);
     }
     return 0;
+}
+
+size_t tiled_scale_bytes(int rows, int K) { return tiled_sf_bytes(rows, K); }
+
+// W4A4 GEMM whose activation has already been quantised (e2m1 bytes [M, K/2] + tiled scales) by
+// a producer kernel of this library.  Tensor-core path only; -1 when the shape cannot take it.
+int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
+                                 const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
+                                 const uint16_t *residual, int M, int K) {
+    if (out == nullptr || xq == nullptr || xq_sf == nullptr || weights == nullptr || !(input_scale > 0.0f)) return -1;
+    for (int i = 0; i < num_weights && i < kMaxSegments; ++i)
+        if (weights[i].w_scales == nullptr) return -1;
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = GEMM_W4A4;
+    a.out = (__nv_bfloat16 *)out;
+    a.ldo = ldo;
+    a.ldx = K;
+    a.xq = xq;
+    a.xq_sf = xq_sf;
+    a.w = weights;
+    a.num_w = num_weights;
+    a.input_scale = input_scale;
+    a.epi = epilogue;
+    a.residual = (const __nv_bfloat16 *)residual;
+    a.M = M;
+    a.K = K;
+    if (ldo < total_out_cols(a)) return -1;
+    return run_fused(a);
 }
 
 }  // namespace glmasr

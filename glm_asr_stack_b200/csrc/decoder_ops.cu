@@ -8,6 +8,7 @@
 #include <stdlib.h>
 
 #include "decoder_ops.cuh"
+#include "fp4_format.cuh"
 
 namespace glmasr {
 
@@ -103,6 +104,132 @@ void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int
     const int total = num_seqs * n_heads * (head_dim / 2);
     if (total <= 0) return;
     rope_single_token_kernel<<<(total + 255) / 256, 256, 0, st>>>(tensor, ld, col0, positions, num_seqs, n_heads, head_dim);
+}
+
+// --------------------------------------------------------------------------------------------
+// The decode step's three launches between the q|k|v projection and attention as one: RoPE on
+// the new token's q heads (in place), RoPE on its k heads, and the K / V rows written to the
+// paged cache (reference: rope_batched_single_token_kernel, decoder.cu:605-632, twice, then
+// reshape_and_cache, paged_kv.cu:70-97).  One CTA per sequence; the 64 (cos, sin) pairs of the
+// position are computed once with the reference's float expressions and shared by all heads,
+// so every value is bit-equal to the three separate kernels.  The rotated k is also written back
+// in place, as the separate kernels leave it.
+// --------------------------------------------------------------------------------------------
+__global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *__restrict__ positions,
+                                     const int64_t *__restrict__ slot_mapping, __nv_bfloat16 *__restrict__ key_cache,
+                                     __nv_bfloat16 *__restrict__ value_cache, int q_heads, int kv_heads, int head_dim) {
+    extern __shared__ float cs[];            // [half_dim] cos, [half_dim] sin
+    const int seq = blockIdx.x;
+    const int half_dim = head_dim / 2;
+    const int pos = positions[seq];
+    for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
+        const float inv_freq = 1.0f / powf(10000.0f, (2.0f * d) / head_dim);
+        const float theta = pos * inv_freq;
+        cs[d] = cosf(theta);
+        cs[half_dim + d] = sinf(theta);
+    }
+    __syncthreads();
+    __nv_bfloat16 *row = qkv + (size_t)seq * ld;
+    const int64_t slot = slot_mapping[seq];
+    const size_t row_elems = (size_t)kv_heads * head_dim;
+    __nv_bfloat16 *kdst = key_cache + (size_t)slot * row_elems;
+    __nv_bfloat16 *vdst = value_cache + (size_t)slot * row_elems;
+    const int q_pairs = q_heads * half_dim, k_pairs = kv_heads * half_dim;
+    for (int i = threadIdx.x; i < q_pairs + k_pairs; i += blockDim.x) {
+        const bool is_k = i >= q_pairs;
+        const int j = is_k ? i - q_pairs : i;
+        const int head = j / half_dim, d = j % half_dim;
+        __nv_bfloat16 *base = row + (is_k ? k_col : 0) + head * head_dim;
+        const float v0 = __bfloat162float(base[d]);
+        const float v1 = __bfloat162float(base[d + half_dim]);
+        const float cos_t = cs[d], sin_t = cs[half_dim + d];
+        const __nv_bfloat16 r0 = __float2bfloat16(v0 * cos_t - v1 * sin_t);
+        const __nv_bfloat16 r1 = __float2bfloat16(v0 * sin_t + v1 * cos_t);
+        base[d] = r0;
+        base[d + half_dim] = r1;
+        if (is_k) {
+            kdst[head * head_dim + d] = r0;
+            kdst[head * head_dim + d + half_dim] = r1;
+        }
+    }
+    // V row: 16 bytes per thread (the launcher checks the alignment)
+    const int chunks = (int)(row_elems / 8);
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x)
+        reinterpret_cast<uint4 *>(vdst)[c] = reinterpret_cast<const uint4 *>(row + v_col)[c];
+}
+
+bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *positions,
+                          const int64_t *slot_mapping, __nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, int num_seqs,
+                          int q_heads, int kv_heads, int head_dim, cudaStream_t st) {
+    const int row_elems = kv_heads * head_dim;
+    if (num_seqs <= 0) return true;
+    if ((head_dim % 2) != 0 || (row_elems % 8) != 0 || (ld % 8) != 0 || (v_col % 8) != 0 ||
+        (((uintptr_t)qkv | (uintptr_t)value_cache) & 15) != 0)
+        return false;
+    rope_qk_cache_kernel<<<num_seqs, 256, (size_t)head_dim * sizeof(float), st>>>(qkv, ld, k_col, v_col, positions, slot_mapping,
+                                                                             key_cache, value_cache, q_heads, kv_heads,
+                                                                             head_dim);
+    return true;
+}
+
+// --------------------------------------------------------------------------------------------
+// RMSNorm whose result goes straight into the next W4A4 GEMM: same normalisation as rmsnorm_kernel
+// (bit-equal bf16 values), then the activation quantiser on 16-element blocks of that bf16 row
+// (quantize_block16) with the scales written in the 128x4-tiled layout.  One CTA per row.
+// --------------------------------------------------------------------------------------------
+__global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf, int sf_chunks,
+                                     const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ weight,
+                                     float eps, float inv_in, int rows, int dim) {
+    extern __shared__ __nv_bfloat16 row_s[];
+    __shared__ float rms_s;
+    const int row = blockIdx.x;
+    if (row >= rows) return;
+    const __nv_bfloat16 *xr = x + (size_t)row * dim;
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x)
+        reinterpret_cast<uint4 *>(row_s)[i] = reinterpret_cast<const uint4 *>(xr)[i];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float sum_sq = 0.0f;
+        for (int i = threadIdx.x; i < dim; i += 32) {
+            const float v = __bfloat162float(row_s[i]);
+            sum_sq += v * v;
+        }
+        for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
+        if (threadIdx.x == 0) rms_s = sqrtf(sum_sq / dim + eps);
+    }
+    __syncthreads();
+    const float rms = rms_s;
+    for (int b = threadIdx.x; b < dim / 16; b += blockDim.x) {
+        float v[16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 xv = reinterpret_cast<const uint4 *>(row_s)[2 * b + h];
+            const uint4 wv = reinterpret_cast<const uint4 *>(weight)[2 * b + h];
+            const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float a0 = __fdiv_rn(__uint_as_float(xs[j] << 16), rms) * __uint_as_float(ws[j] << 16);
+                const float a1 = __fdiv_rn(__uint_as_float(xs[j] & 0xFFFF0000u), rms) * __uint_as_float(ws[j] & 0xFFFF0000u);
+                v[8 * h + 2 * j] = __bfloat162float(__float2bfloat16(a0));
+                v[8 * h + 2 * j + 1] = __bfloat162float(__float2bfloat16(a1));
+            }
+        }
+        uint32_t lo, hi;
+        const uint32_t sf = quantize_block16(v, inv_in, lo, hi);
+        *reinterpret_cast<uint2 *>(q_packed + (size_t)row * (dim / 2) + (size_t)b * 8) = make_uint2(lo, hi);
+        const int rem = row & 127;
+        q_sf[((((size_t)(row >> 7) * sf_chunks + (b >> 2)) * 32 + (rem & 31)) * 4 + (rem >> 5)) * 4 + (b & 3)] = (uint8_t)sf;
+    }
+}
+
+bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps,
+                          float input_scale, int rows, int dim, cudaStream_t st) {
+    if (rows <= 0) return true;
+    if ((dim % 64) != 0 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)q_packed) & 15) != 0 || !(input_scale > 0.0f))
+        return false;
+    rmsnorm_quant_kernel<<<rows, 128, (size_t)dim * sizeof(__nv_bfloat16), st>>>(q_packed, q_sf, dim / 64, x, weight, eps,
+                                                                            1.0f / input_scale, rows, dim);
+    return true;
 }
 
 // --------------------------------------------------------------------------------------------

@@ -14,6 +14,15 @@ void launch_rmsnorm(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfloa
 // In place on `tensor` rows of pitch `ld`: heads [0, n_heads) of head_dim at column offset col0.
 void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int *positions, int num_seqs, int n_heads,
                               int head_dim, cudaStream_t st);
+// RoPE on q (columns [0, q_heads*head_dim)) and k (at k_col) of the new token's q|k|v row, in place, and the
+// K / V rows into the paged cache: the three launches between the projection and attention as one.
+// Returns false when the layout is not supported (alignment).
+bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *positions,
+                          const int64_t *slot_mapping, __nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, int num_seqs,
+                          int q_heads, int kv_heads, int head_dim, cudaStream_t st);
+// RMSNorm + activation quantiser for the next W4A4 GEMM: e2m1 bytes [rows, dim/2] and 128x4-tiled scales.
+bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps,
+                          float input_scale, int rows, int dim, cudaStream_t st);
 void launch_reshape_and_cache(__nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, const __nv_bfloat16 *key, int ldk,
                               const __nv_bfloat16 *value, int ldv, const int64_t *slot_mapping, int num_tokens,
                               int num_kv_heads, int head_dim, int block_size, cudaStream_t st);

@@ -29,6 +29,9 @@
 #include "runtime.cuh"
 
 namespace glmasr {
+int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
+                                 const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
+                                 const uint16_t *residual, int M, int K);   // api.cu
 
 struct ProjRef {
     int dtype = -1;                     // GLMASR_DTYPE_UINT8 (FP4) or GLMASR_DTYPE_BF16
@@ -196,13 +199,38 @@ static bool fused_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, const
     return rc == 0;
 }
 
+// RMSNorm feeding several same-input FP4 projections in W4A4: the norm kernel quantises its own
+// result (same bytes as norm, then the stand-alone quantiser) and the GEMM takes it as it is.
+// Returns false when the projections cannot share one quantised input; the caller then runs the
+// norm and the projections separately.
+static bool norm_then_fused_proj_w4a4(uint16_t *out, int ldo, const uint16_t *x, const uint16_t *norm_w, float eps,
+                                      const ProjRef *const *ps, int n, int epi, int M, int H, uint8_t *xq, uint8_t *xsf,
+                                      cudaStream_t st) {
+    if (!prefer_w4a4() || (H % 256) != 0) return false;
+    glmasr_fp4_weight w[3];
+    for (int i = 0; i < n; ++i) {
+        const ProjRef &p = *ps[i];
+        if (p.dtype != GLMASR_DTYPE_UINT8 || p.pre != nullptr || p.K != H || p.scales == nullptr ||
+            !(p.input_scale > 0.0f) || p.input_scale != ps[0]->input_scale)
+            return false;
+        w[i] = as_weight(p);
+    }
+    if (!launch_rmsnorm_quant(xq, xsf, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)norm_w, eps, ps[0]->input_scale,
+                              M, H, st))
+        return false;
+    note_launches(1);
+    const int rc = fp4_linear_w4a4_prequantized(out, ldo, xq, xsf, w, n, ps[0]->input_scale, epi, nullptr, M, H);
+    GLMASR_CHECK(rc == 0, "decoder projection on a quantised norm output failed (M=%d H=%d)", M, H);
+    return true;
+}
+
 }  // namespace glmasr
 
 using namespace glmasr;
 
 enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
     WS_D_HID = 13, WS_D_NORM = 14, WS_D_QKV = 15, WS_D_ATTN = 16, WS_D_ACT = 17, WS_D_SLOT = 18, WS_D_LENS = 19,
-    WS_D_BT = 20, WS_D_ROWS = 21, WS_D_PTRS = 22, WS_D_SCRATCH = 23,
+    WS_D_BT = 20, WS_D_ROWS = 21, WS_D_PTRS = 22, WS_D_SCRATCH = 23, WS_D_XQ = 26, WS_D_XSF = 27,
 };
 
 // ============================================================================================
@@ -250,6 +278,28 @@ extern "C" void glmasr_rope_single_token(uint16_t *tensor, const int *positions,
     launch_rope_single_token((__nv_bfloat16 *)tensor, n_heads * head_dim, 0, positions, num_seqs, n_heads, head_dim,
                              current_stream());
     GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+extern "C" int glmasr_rope_qk_cache(uint16_t *qkv, int ld, int k_col, int v_col, const int *positions,
+                                    const int64_t *slot_mapping, uint16_t *key_cache, uint16_t *value_cache, int num_seqs,
+                                    int q_heads, int kv_heads, int head_dim) {
+    if (qkv == nullptr || positions == nullptr || slot_mapping == nullptr || key_cache == nullptr || value_cache == nullptr)
+        return -1;
+    if (!launch_rope_qk_cache((__nv_bfloat16 *)qkv, ld, k_col, v_col, positions, slot_mapping, (__nv_bfloat16 *)key_cache,
+                              (__nv_bfloat16 *)value_cache, num_seqs, q_heads, kv_heads, head_dim, current_stream()))
+        return -1;
+    note_launches(1);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int glmasr_rmsnorm_quant(uint8_t *packed_out, uint8_t *tiled_scale_out, const uint16_t *x, const uint16_t *weight,
+                                    float eps, float input_scale, int rows, int dim) {
+    if (packed_out == nullptr || tiled_scale_out == nullptr || x == nullptr || weight == nullptr) return -1;
+    if (!launch_rmsnorm_quant(packed_out, tiled_scale_out, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)weight, eps,
+                              input_scale, rows, dim, current_stream()))
+        return -1;
+    note_launches(1);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 // ============================================================================================
@@ -309,6 +359,8 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     int *d_rows = (int *)workspace_slot(WS_D_ROWS, (size_t)M * sizeof(int));
     uint16_t **d_ptrs = (uint16_t **)workspace_slot(WS_D_PTRS, (size_t)M * sizeof(void *));
     uint16_t *scratch = (uint16_t *)workspace_slot(WS_D_SCRATCH, (size_t)M * (F > H ? F : H) * 2);
+    uint8_t *nq = (uint8_t *)workspace_slot(WS_D_XQ, (size_t)M * H / 2);
+    uint8_t *nsf = (uint8_t *)workspace_slot(WS_D_XSF, tiled_scale_bytes(M, H));
 
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_total, h_total.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
@@ -327,11 +379,13 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
         __nv_bfloat16 *k_base = (__nv_bfloat16 *)pool->k_cache + (size_t)l * pool->layer_stride;
         __nv_bfloat16 *v_base = (__nv_bfloat16 *)pool->v_cache + (size_t)l * pool->layer_stride;
 
-        launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st);
-
         // q | k | v into one [M, H + 2 KV] buffer
         const ProjRef *qkv_p[3] = {&R.q, &R.k, &R.v};
-        if (!fused_proj(qkv, NQKV, nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) {
+        int glue = 0;                       // launches of this layer outside the projections' own accounting
+        if (norm_then_fused_proj_w4a4(qkv, NQKV, hid, R.norm1, 1e-5f, qkv_p, 3, GLMASR_EPI_STORE, M, H, nq, nsf, st)) {
+            // done: norm + quantiser in one launch, GEMM on the quantised rows
+        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st),
+                   ++glue, !fused_proj(qkv, NQKV, nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) {
             single_proj(qkv, NQKV, nrm, H, R.q, M, nullptr, scratch);
             const ProjRef *kv_p[2] = {&R.k, &R.v};
             if (!fused_proj(qkv + H, NQKV, nrm, H, kv_p, 2, GLMASR_EPI_STORE, M)) {
@@ -340,10 +394,15 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
             }
         }
         // RoPE on q and k in place (position = cached length), KV write, attention over cached + 1 tokens
-        launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, 0, d_seq_lens, M, QH, HD, st);
-        launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, H, d_seq_lens, M, KVH, HD, st);
-        launch_reshape_and_cache(k_base, v_base, (const __nv_bfloat16 *)qkv + H, NQKV, (const __nv_bfloat16 *)qkv + H + KV,
-                                 NQKV, d_slot, M, KVH, HD, pool->block_size, st);
+        if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_seq_lens, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
+            glue += 1;
+        } else {
+            launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, 0, d_seq_lens, M, QH, HD, st);
+            launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, H, d_seq_lens, M, KVH, HD, st);
+            launch_reshape_and_cache(k_base, v_base, (const __nv_bfloat16 *)qkv + H, NQKV,
+                                     (const __nv_bfloat16 *)qkv + H + KV, NQKV, d_slot, M, KVH, HD, pool->block_size, st);
+            glue += 3;
+        }
         const bool ok = launch_paged_decode_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV, k_base,
                                                       v_base, d_bt, d_total, M, QH, KVH, HD, pool->block_size,
                                                       pool->max_blocks_per_seq, st);
@@ -352,15 +411,17 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
         // o + residual -> hid (residual is the pre-norm hidden state)
         single_proj(hid, H, att, H, R.o, M, hid, scratch);
 
-        launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st);
         const ProjRef *gu_p[2] = {&R.gate, &R.up};
-        if (!fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
+        if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
+            // done
+        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st),
+                   ++glue, !fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
             single_proj(act, F, nrm, H, R.gate, M, nullptr, scratch);
             single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
             silu_elementwise_mul(act, act + (size_t)M * F, M * F);
         }
         single_proj(hid, H, act, F, R.down, M, hid, scratch);
-        note_launches(6);   // 2 norms, 2 RoPE, cache write, attention (the projections count themselves)
+        note_launches(glue + 1);   // norms, RoPE / cache write, attention (the projections count themselves)
     }
 
     launch_rmsnorm((__nv_bfloat16 *)hid, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)refs.final_norm, 1e-5f, M, H, st);

@@ -16,6 +16,7 @@ void *workspace(size_t bytes);      // grow-only private device workspace (slot 
 void *workspace_slot(int slot, size_t bytes);
 void free_all_private_state();
 void note_launches(int n);          // launch accounting for kernels started outside api.cu
+size_t tiled_scale_bytes(int rows, int K);   // bytes of the 128x4-tiled scale layout for [rows, K]
 
 #define GLMASR_CUDA_CHECK(call)                                                              \
     do {                                                                                     \

@@ -229,6 +229,29 @@ def rope_single_token(t: torch.Tensor, positions: torch.Tensor, n_heads: int, he
     return t
 
 
+def rope_qk_cache(qkv: torch.Tensor, k_col: int, v_col: int, positions: torch.Tensor, slot_mapping: torch.Tensor,
+                  k_cache: torch.Tensor, v_cache: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int) -> torch.Tensor:
+    """RoPE on q and k of the new-token rows (in place) + K / V rows into the paged cache, one launch
+    (Infer-engine/cuda/decoder.cu:605-632 twice and cuda/paged_kv.cu:70-97)."""
+    rc = _lib.load().glmasr_rope_qk_cache(_ptr(qkv), qkv.stride(0), k_col, v_col, _ptr(positions), _ptr(slot_mapping),
+                                          _ptr(k_cache), _ptr(v_cache), qkv.shape[0], q_heads, kv_heads, head_dim)
+    if rc != 0:
+        raise ValueError("glmasr_rope_qk_cache rejected the layout")
+    return qkv
+
+
+def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, input_scale: float):
+    """rmsnorm + activation quantiser in one launch.  Returns (packed [rows, dim/2] u8, tiled scales u8)."""
+    rows, dim = x.shape
+    packed = torch.empty((rows, dim // 2), dtype=torch.uint8, device=x.device)
+    tiled = torch.zeros(((rows + 127) // 128) * (dim // 64) * 512, dtype=torch.uint8, device=x.device)
+    rc = _lib.load().glmasr_rmsnorm_quant(_ptr(packed), _ptr(tiled), _ptr(x), _ptr(weight), float(eps),
+                                          float(input_scale), rows, dim)
+    if rc != 0:
+        raise ValueError("glmasr_rmsnorm_quant rejected the arguments")
+    return packed, tiled
+
+
 def reshape_and_cache(k_cache, v_cache, key, value, slot_mapping, num_kv_heads, head_dim, block_size):
     """reference: reshape_and_cache, Infer-engine/cuda/paged_kv.cu:70-97, 424-438."""
     _lib.load().reshape_and_cache(_ptr(k_cache), _ptr(v_cache), _ptr(key), _ptr(value), _ptr(slot_mapping),

@@ -124,6 +124,20 @@ void decoder_decode_step_batched(void *handle, const void *ws, uint16_t **query_
  * position = positions[seq] (the reference's rope_batched_single_token_kernel,
  * Infer-engine/cuda/decoder.cu:605-632, which has no host entry point of its own). */
 void glmasr_rope_single_token(uint16_t *tensor, const int *positions, int num_seqs, int n_heads, int head_dim);
+/* The three launches between the q|k|v projection and attention of a decode step as one: RoPE on the q
+ * heads (columns [0, q_heads*head_dim)) and the k heads (at k_col) of every sequence's new-token row of
+ * qkv [num_seqs, ld], in place, and the K / V rows written to slot_mapping[seq] of the paged cache
+ * (Infer-engine/cuda/decoder.cu:605-632 twice + cuda/paged_kv.cu:70-97; same bytes).  Returns -1 for an
+ * unsupported layout (ld, v_col, kv_heads*head_dim multiples of 8; 16-byte aligned pointers). */
+int glmasr_rope_qk_cache(uint16_t *qkv, int ld, int k_col, int v_col, const int *positions,
+                         const int64_t *slot_mapping, uint16_t *key_cache, uint16_t *value_cache, int num_seqs,
+                         int q_heads, int kv_heads, int head_dim);
+/* rmsnorm (Infer-engine/cuda/kernels.cu rmsnorm_kernel) followed by the activation quantiser
+ * (cuda/nvfp4_cutlass.cu:35-87) in one launch: packed_out [rows, dim/2] e2m1 bytes and the scales in the
+ * 128x4-tiled layout (ceil(rows/128) * dim/64 * 512 bytes), the same bytes as rmsnorm then
+ * glmasr_quantize_bf16_to_fp4 + glmasr_swizzle_rowwise_scales.  dim % 64 == 0.  Returns -1 otherwise. */
+int glmasr_rmsnorm_quant(uint8_t *packed_out, uint8_t *tiled_scale_out, const uint16_t *x, const uint16_t *weight,
+                         float eps, float input_scale, int rows, int dim);
 /* Forget the per-layer pointer table built from a WeightStore (call before freeing the store). */
 void glmasr_decoder_forget_weights(void);
 

@@ -128,6 +128,57 @@ def test_reshape_and_cache_bit_exact(ops, ref):
         assert torch.equal(kr, kd) and torch.equal(vr, vd)
 
 
+def test_rope_qk_cache_equals_three_launches(ops):
+    """The fused RoPE(q) + RoPE(k) + cache-write launch leaves the same bytes as the three separate ones."""
+    rng = np.random.default_rng(8)
+    qh, kvh, hd, bs, nblk, n = 16, 4, 128, 16, 40, 37
+    H, KV = qh * hd, kvh * hd
+    qkv = rnd_bits(rng, (n, H + 2 * KV))
+    pos = rng.integers(0, 8192, n).astype(np.int32)
+    pos[0] = 0
+    slots = rng.permutation(nblk * bs)[:n].astype(np.int64)
+    posd, slotd = torch.from_numpy(pos).cuda(), torch.from_numpy(slots).cuda()
+    # three launches on dense copies of the slices
+    q = ops.rope_single_token(to_dev_bf16(qkv[:, :H].copy()), posd, qh, hd)
+    k = ops.rope_single_token(to_dev_bf16(qkv[:, H:H + KV].copy()), posd, kvh, hd)
+    v = to_dev_bf16(qkv[:, H + KV:].copy())
+    kc = torch.zeros((nblk * bs, KV), dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    ops.reshape_and_cache(kc, vc, k, v, slotd, kvh, hd, bs)
+    # one launch on the fused buffer
+    buf = to_dev_bf16(qkv)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc)
+    ops.rope_qk_cache(buf, H, H + KV, posd, slotd, kc2, vc2, qh, kvh, hd)
+    assert torch.equal(buf[:, :H], q) and torch.equal(buf[:, H:H + KV], k) and torch.equal(buf[:, H + KV:], v)
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc)
+    # and the oracle
+    assert np.array_equal(bits_of(buf[:, :H].contiguous()), bits_of(q))
+    want_q = do.rope_single_token(qkv[:, :H].copy(), pos, qh, hd)
+    assert ulp_diff(bits_of(buf[:, :H].contiguous()), want_q).max() <= 1 or o.rel_err(bits_of(buf[:, :H].contiguous()), want_q) < 2e-3
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 2048), (130, 256), (256, 2048)])
+def test_rmsnorm_quant_equals_norm_then_quantiser(ops, rows, dim):
+    """rmsnorm + quantiser in one launch = rmsnorm, then the stand-alone quantiser, then the scale re-tiling."""
+    rng = np.random.default_rng(rows + dim)
+    x, w = rnd_bits(rng, (rows, dim), 3.0), rnd_bits(rng, (dim,), 1.0)
+    isc = 0.003
+    normed = ops.rmsnorm(to_dev_bf16(x), to_dev_bf16(w))
+    pk, sc = ops.quantize_bf16_to_fp4(normed, isc)
+    tiled = ops.swizzle_rowwise_scales(sc)
+    got_pk, got_tiled = ops.rmsnorm_quant(to_dev_bf16(x), to_dev_bf16(w), 1e-5, isc)
+    assert torch.equal(got_pk, pk)
+    # compare the scale bytes of the real rows (padding rows of the last 128-row tile are not written)
+    a = got_tiled.cpu().numpy().reshape(-1, dim // 64, 32, 4, 4)
+    b = tiled.cpu().numpy().reshape(-1, dim // 64, 32, 4, 4)
+    for r in range(rows):
+        t, rem = divmod(r, 128)
+        assert np.array_equal(a[t, :, rem % 32, rem // 32, :], b[t, :, rem % 32, rem // 32, :]), r
+    # and the CPU oracle's chain
+    opk, osc = o.quantize_bf16_to_fp4(do.rmsnorm(x, w), isc)
+    assert np.array_equal(got_pk.cpu().numpy(), opk)
+
+
 def test_embedding_lookup(ops):
     rng = np.random.default_rng(7)
     table = rnd_bits(rng, (100, 256))
