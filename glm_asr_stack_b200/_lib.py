@@ -46,6 +46,9 @@ SIGNATURES = {
     "reshape_and_cache": (None, [P, P, P, P, P, c_int, c_int, c_int, c_int]),
     "paged_decode_attention": (None, [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]),
     "decoder_decode_step_batched": (None, [P, P, P, P, P, P, P, c_int, P, P, P]),
+    "decoder_prefill_paged_batched": (None, [P, P, P, c_int, c_int, P, P, P, P, P, P]),
+    "flash_fwd_vllm_gqa_available": (c_int, []),
+    "flash_fwd_vllm_gqa_launch": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, c_int]),
     "glmasr_rope_single_token": (None, [P, P, c_int, c_int, c_int]),
     "glmasr_rope_qk_cache": (c_int, [P, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int]),
     "glmasr_rmsnorm_quant": (c_int, [P, P, P, P, c_float, c_float, c_int, c_int]),

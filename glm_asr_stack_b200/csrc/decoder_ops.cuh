@@ -38,6 +38,13 @@ bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_b
                                        const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
                                        int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
                                        cudaStream_t st);
+// Variable-length GQA self-attention of a prefill batch (prefill_attention.cu): sequence s owns rows
+// [seq_offsets[s], +seq_lens[s]) of q / k / v / out (device arrays; seq_lens == NULL: seq_offsets is a
+// cumulative table of num_seqs + 1 entries); head_dim 128.
+bool launch_prefill_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *q, int ldq, const __nv_bfloat16 *k,
+                              int ldk, const __nv_bfloat16 *v, int ldv, const int *seq_offsets, const int *seq_lens,
+                              int num_seqs, int max_seq_len, int num_q_heads, int num_kv_heads, int head_dim, bool causal,
+                              cudaStream_t st);
 void launch_embedding_lookup(__nv_bfloat16 *out, const __nv_bfloat16 *table, const int *ids, int n, int dim,
                              cudaStream_t st);
 // out[i, :] = src_rows[i][:]  /  dst_rows[i][:] = in[i, :]   (device arrays of row pointers)

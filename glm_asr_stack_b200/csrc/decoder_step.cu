@@ -231,6 +231,7 @@ using namespace glmasr;
 enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
     WS_D_HID = 13, WS_D_NORM = 14, WS_D_QKV = 15, WS_D_ATTN = 16, WS_D_ACT = 17, WS_D_SLOT = 18, WS_D_LENS = 19,
     WS_D_BT = 20, WS_D_ROWS = 21, WS_D_PTRS = 22, WS_D_SCRATCH = 23, WS_D_XQ = 26, WS_D_XSF = 27,
+    WS_D_POS = 28, WS_D_OFFS = 29,
 };
 
 // ============================================================================================
@@ -433,6 +434,145 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     note_launches(2);
     for (int s = 0; s < M; ++s) h_seq_lens[s] = h_total[s];
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_seq_lens, d_total, (size_t)M * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+// The reference's attention plug-in entry points (Infer-engine/cuda/flash_fwd_vllm.h:21-30), served
+// by this library's own kernel: q / k / v rows of sequence s are [cu_seqlens[s], cu_seqlens[s+1]),
+// row strides in elements, out dense [total, q_heads * head_dim].  Returns 1 on success like the plug-in.
+extern "C" int flash_fwd_vllm_gqa_available(void) { return 1; }
+
+extern "C" int flash_fwd_vllm_gqa_launch(void *q, void *k, void *v, void *out, int total_seqlen, int max_seqlen, int q_heads,
+                                         int kv_heads, int head_dim, int q_row_stride, int k_row_stride, int v_row_stride,
+                                         int num_seqs, int *d_cu_seqlens, int is_causal) {
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || d_cu_seqlens == nullptr) return 0;
+    if (total_seqlen <= 0 || num_seqs <= 0) return 1;
+    if (!launch_prefill_attention((__nv_bfloat16 *)out, q_heads * head_dim, (const __nv_bfloat16 *)q, q_row_stride,
+                                  (const __nv_bfloat16 *)k, k_row_stride, (const __nv_bfloat16 *)v, v_row_stride,
+                                  d_cu_seqlens, nullptr, num_seqs, max_seqlen, q_heads, kv_heads, head_dim, is_causal != 0,
+                                  current_stream()))
+        return 0;
+    note_launches(1);
+    return cudaGetLastError() == cudaSuccess ? 1 : 0;
+}
+
+// ============================================================================================
+// decoder_prefill_paged_batched (reference: Infer-engine/cuda/decoder.cu:1219-1557)
+// ============================================================================================
+// Batched variable-length prefill, in place on hidden [total_tokens, H]: sequence s owns rows
+// [seq_offsets[s], seq_offsets[s] + seq_lens[s]) and the blocks of bts[s]; positions start at 0.
+// Per layer: RMSNorm -> q|k|v (one GEMM) -> RoPE(q, k) + K / V rows into the paged cache (one
+// launch) -> causal attention over the sequence's own tokens -> o + residual -> RMSNorm ->
+// gate|up with SiLU-gate -> down + residual; final RMSNorm.  seq_lens / seq_offsets are host arrays
+// as in the reference.
+extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, uint16_t *hidden, int total_tokens,
+                                              int num_seqs, const int *seq_lens, const int *seq_offsets, void *pool_v,
+                                              void *bts_v, uint16_t *dequant_buf, const void *cfg_v) {
+    (void)handle;
+    (void)dequant_buf;
+    const glmasr_WeightStore *ws = (const glmasr_WeightStore *)ws_v;
+    const glmasr_ModelConfig *cfg = (const glmasr_ModelConfig *)cfg_v;
+    glmasr_KVPool *pool = (glmasr_KVPool *)pool_v;
+    glmasr_BlockTable *bts = (glmasr_BlockTable *)bts_v;
+    GLMASR_CHECK(total_tokens > 0, "decoder_prefill_paged_batched requires tokens");
+    GLMASR_CHECK(num_seqs > 0, "decoder_prefill_paged_batched requires sequences");
+    GLMASR_CHECK(hidden != nullptr && seq_lens != nullptr && seq_offsets != nullptr && pool != nullptr && bts != nullptr,
+                 "decoder_prefill_paged_batched received null metadata");
+
+    const int H = cfg->dec_hidden, L = cfg->dec_layers, QH = cfg->dec_heads, KVH = cfg->dec_kv_heads;
+    const int HD = cfg->dec_head_dim, F = cfg->dec_ffn;
+    const int KV = KVH * HD, NQKV = H + 2 * KV, M = total_tokens;
+    GLMASR_CHECK(QH * HD == H, "decoder_prefill_paged_batched: heads * head_dim != hidden");
+    const ModelRefs &refs = model_refs(ws, L);
+    cudaStream_t st = current_stream();
+
+    // ---- host-side set-up: slot of every token, its position, the sequence table ----
+    std::vector<int64_t> h_slot((size_t)M, -1);
+    std::vector<int> h_pos((size_t)M, 0), h_meta((size_t)2 * num_seqs);
+    int max_len = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+        const int len = seq_lens[s], off = seq_offsets[s];
+        GLMASR_CHECK(len >= 0 && off >= 0 && off + len <= M, "decoder_prefill_paged_batched: sequence %d outside the batch", s);
+        GLMASR_CHECK(bts[s].h_table != nullptr, "decoder_prefill_paged_batched: bts[%d].h_table is NULL", s);
+        for (int t = 0; t < len; ++t) {
+            const int blk = t / pool->block_size;
+            GLMASR_CHECK(blk < bts[s].num_blocks, "Prefill block table too small for seq=%d tok=%d", s, t);
+            h_slot[(size_t)off + t] = (int64_t)bts[s].h_table[blk] * (int64_t)pool->block_size + (int64_t)(t % pool->block_size);
+            h_pos[(size_t)off + t] = t;
+        }
+        h_meta[s] = off;
+        h_meta[num_seqs + s] = len;
+        if (len > max_len) max_len = len;
+    }
+    GLMASR_CHECK(max_len > 0, "decoder_prefill_paged_batched max_seq_len invalid");
+    for (int t = 0; t < M; ++t)
+        GLMASR_CHECK(h_slot[t] >= 0, "decoder_prefill_paged_batched: token row %d belongs to no sequence", t);
+
+    uint16_t *nrm = (uint16_t *)workspace_slot(WS_D_NORM, (size_t)M * H * 2);
+    uint16_t *qkv = (uint16_t *)workspace_slot(WS_D_QKV, (size_t)M * NQKV * 2);
+    uint16_t *att = (uint16_t *)workspace_slot(WS_D_ATTN, (size_t)M * H * 2);
+    uint16_t *act = (uint16_t *)workspace_slot(WS_D_ACT, (size_t)M * 2 * F * 2);
+    uint16_t *scratch = (uint16_t *)workspace_slot(WS_D_SCRATCH, (size_t)M * (F > H ? F : H) * 2);
+    uint8_t *nq = (uint8_t *)workspace_slot(WS_D_XQ, (size_t)M * H / 2);
+    uint8_t *nsf = (uint8_t *)workspace_slot(WS_D_XSF, tiled_scale_bytes(M, H));
+    int64_t *d_slot = (int64_t *)workspace_slot(WS_D_SLOT, (size_t)M * sizeof(int64_t));
+    int *d_pos = (int *)workspace_slot(WS_D_POS, (size_t)M * sizeof(int));
+    int *d_meta = (int *)workspace_slot(WS_D_OFFS, (size_t)2 * num_seqs * sizeof(int));
+    // pageable host vectors: the copies have been staged when these calls return
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_pos, h_pos.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
+    GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_meta, h_meta.data(), (size_t)2 * num_seqs * sizeof(int), cudaMemcpyHostToDevice, st));
+
+    uint16_t *hid = hidden;
+    for (int l = 0; l < L; ++l) {
+        const LayerRef &R = refs.layers[l];
+        __nv_bfloat16 *k_base = (__nv_bfloat16 *)pool->k_cache + (size_t)l * pool->layer_stride;
+        __nv_bfloat16 *v_base = (__nv_bfloat16 *)pool->v_cache + (size_t)l * pool->layer_stride;
+        int glue = 0;
+
+        const ProjRef *qkv_p[3] = {&R.q, &R.k, &R.v};
+        if (norm_then_fused_proj_w4a4(qkv, NQKV, hid, R.norm1, 1e-5f, qkv_p, 3, GLMASR_EPI_STORE, M, H, nq, nsf, st)) {
+            // norm + quantiser in one launch, GEMM on the quantised rows
+        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st),
+                   ++glue, !fused_proj(qkv, NQKV, nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) {
+            single_proj(qkv, NQKV, nrm, H, R.q, M, nullptr, scratch);
+            const ProjRef *kv_p[2] = {&R.k, &R.v};
+            if (!fused_proj(qkv + H, NQKV, nrm, H, kv_p, 2, GLMASR_EPI_STORE, M)) {
+                single_proj(qkv + H, NQKV, nrm, H, R.k, M, nullptr, scratch);
+                single_proj(qkv + H + KV, NQKV, nrm, H, R.v, M, nullptr, scratch);
+            }
+        }
+        if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_pos, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
+            glue += 1;
+        } else {
+            launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, 0, d_pos, M, QH, HD, st);
+            launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, H, d_pos, M, KVH, HD, st);
+            launch_reshape_and_cache(k_base, v_base, (const __nv_bfloat16 *)qkv + H, NQKV,
+                                     (const __nv_bfloat16 *)qkv + H + KV, NQKV, d_slot, M, KVH, HD, pool->block_size, st);
+            glue += 3;
+        }
+        const bool ok = launch_prefill_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV,
+                                                 (const __nv_bfloat16 *)qkv + H, NQKV, (const __nv_bfloat16 *)qkv + H + KV,
+                                                 NQKV, d_meta, d_meta + num_seqs, num_seqs, max_len, QH, KVH, HD, true, st);
+        GLMASR_CHECK(ok, "decoder_prefill_paged_batched: unsupported attention shape");
+        glue += 1;
+
+        single_proj(hid, H, att, H, R.o, M, hid, scratch);
+
+        const ProjRef *gu_p[2] = {&R.gate, &R.up};
+        if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
+            // done
+        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st),
+                   ++glue, !fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
+            single_proj(act, F, nrm, H, R.gate, M, nullptr, scratch);
+            single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
+            silu_elementwise_mul(act, act + (size_t)M * F, M * F);
+        }
+        single_proj(hid, H, act, F, R.down, M, hid, scratch);
+        note_launches(glue);
+    }
+    launch_rmsnorm((__nv_bfloat16 *)hid, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)refs.final_norm, 1e-5f, M, H, st);
+    note_launches(1);
     GLMASR_CUDA_CHECK(cudaGetLastError());
 }
 

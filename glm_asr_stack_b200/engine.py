@@ -150,3 +150,33 @@ def decode_step(ws: WeightStore, cfg: CModelConfig, pool: KVPool, bts: BlockTabl
     ptrs = (c_void_p * n)(*[hidden.data_ptr() + i * hidden.shape[1] * 2 for i in range(n)])
     lib.decoder_decode_step_batched(None, ctypes.byref(ws.c), ptrs, ctypes.byref(pool.c), bts.arr,
                                     c_void_p(d_seq_lens.data_ptr()), h_seq_lens, n, None, None, ctypes.byref(cfg))
+
+
+def prefill_paged_batched(ws: WeightStore, cfg: CModelConfig, pool: KVPool, bts: BlockTables, hidden: torch.Tensor,
+                          seq_lens, seq_offsets):
+    """Call decoder_prefill_paged_batched on hidden [total_tokens, hidden] (updated in place).
+    seq_lens / seq_offsets: host sequences of ints, one entry per sequence (rows of sequence s are
+    [seq_offsets[s], seq_offsets[s] + seq_lens[s]))."""
+    lib = _lib.load()
+    n = len(seq_lens)
+    lens = (ctypes.c_int * n)(*[int(v) for v in seq_lens])
+    offs = (ctypes.c_int * n)(*[int(v) for v in seq_offsets])
+    lib.decoder_prefill_paged_batched(None, ctypes.byref(ws.c), c_void_p(hidden.data_ptr()), hidden.shape[0], n, lens, offs,
+                                      ctypes.byref(pool.c), bts.arr, None, ctypes.byref(cfg))
+    return hidden
+
+
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
+                      q_heads: int, kv_heads: int, head_dim: int, causal: bool = True) -> torch.Tensor:
+    """flash_fwd_vllm_gqa_launch: variable-length GQA self-attention; q / k / v may be column slices
+    (row strides are passed), cu_seqlens int32 [num_seqs + 1] on the device."""
+    lib = _lib.load()
+    total = q.shape[0]
+    out = torch.empty((total, q_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    ok = lib.flash_fwd_vllm_gqa_launch(c_void_p(q.data_ptr()), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()),
+                                       c_void_p(out.data_ptr()), total, int(max_seqlen), q_heads, kv_heads, head_dim,
+                                       q.stride(0), k.stride(0), v.stride(0), cu_seqlens.numel() - 1,
+                                       c_void_p(cu_seqlens.data_ptr()), 1 if causal else 0)
+    if ok != 1:
+        raise ValueError("flash_fwd_vllm_gqa_launch rejected the layout")
+    return out

@@ -120,6 +120,22 @@ void decoder_decode_step_batched(void *handle, const void *ws, uint16_t **query_
 
 /* ======================= 2. additive entry points ======================= */
 
+/* Batched variable-length prefill, in place on hidden [total_tokens, dec_hidden]
+ * (Infer-engine/cuda/decoder.cu:1219-1557; include/cuda_kernels.h): sequence s owns rows
+ * [seq_offsets[s], seq_offsets[s]+seq_lens[s]) (host arrays) and the blocks of bts[s]; writes every
+ * layer's K / V rows to the paged pool.  ws / pool / bts / cfg are the engine's WeightStore, KVPool,
+ * BlockTable[] and ModelConfig (layouts in glmasr_engine_types.h); handle and dequant_buf are unused. */
+void decoder_prefill_paged_batched(void *handle, const void *ws, uint16_t *hidden, int total_tokens, int num_seqs,
+                                   const int *seq_lens, const int *seq_offsets, void *pool, void *bts,
+                                   uint16_t *dequant_buf, const void *cfg);
+/* The attention plug-in's entry points (Infer-engine/cuda/flash_fwd_vllm.h:21-30) served by this library:
+ * variable-length GQA self-attention, head_dim 128, q / k / v rows of sequence s at
+ * [d_cu_seqlens[s], d_cu_seqlens[s+1]) with the given row strides (elements), out dense
+ * [total_seqlen, q_heads*head_dim].  Returns 1 on success, 0 otherwise, like the plug-in. */
+int flash_fwd_vllm_gqa_available(void);
+int flash_fwd_vllm_gqa_launch(void *q, void *k, void *v, void *out, int total_seqlen, int max_seqlen, int q_heads,
+                              int kv_heads, int head_dim, int q_row_stride, int k_row_stride, int v_row_stride,
+                              int num_seqs, int *d_cu_seqlens, int is_causal);
 /* Rotate-half RoPE (theta 10000) of one new token per sequence, in place on [num_seqs, n_heads*head_dim],
  * position = positions[seq] (the reference's rope_batched_single_token_kernel,
  * Infer-engine/cuda/decoder.cu:605-632, which has no host entry point of its own). */

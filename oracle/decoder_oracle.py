@@ -111,3 +111,53 @@ def decode_step(hidden_bits, layers, final_norm_bits, k_caches, v_caches, block_
         h = o.residual_add(linear(act, Lw["down"]), h)
         assert h.shape[1] == H and k.shape[1] == kvw
     return rmsnorm(h, final_norm_bits)
+
+
+def prefill_attention(q_bits, k_bits, v_bits, seq_offsets, seq_lens, n_q_heads, n_kv_heads, head_dim, causal=True):
+    """Per-sequence softmax(Q K^T / sqrt(d) [+ causal mask]) V with q head h reading kv head h // group, float64
+    (the attention step of Infer-engine/cuda/decoder.cu:1401-1441; gqa_attention's arithmetic)."""
+    q = o.bf16_bits_to_f32(q_bits).astype(np.float64)
+    k = o.bf16_bits_to_f32(k_bits).astype(np.float64)
+    v = o.bf16_bits_to_f32(v_bits).astype(np.float64)
+    T = q.shape[0]
+    out = np.zeros((T, n_q_heads * head_dim), np.float64)
+    group = n_q_heads // n_kv_heads
+    scale = 1.0 / np.sqrt(float(head_dim))
+    for off, ln in zip(seq_offsets, seq_lens):
+        if ln <= 0:
+            continue
+        rows = slice(off, off + ln)
+        for h in range(n_q_heads):
+            kv = h // group
+            Q = q[rows, h * head_dim:(h + 1) * head_dim]
+            K = k[rows, kv * head_dim:(kv + 1) * head_dim]
+            V = v[rows, kv * head_dim:(kv + 1) * head_dim]
+            s = (Q @ K.T) * scale
+            if causal:
+                s = np.where(np.tril(np.ones((ln, ln), bool)), s, -np.inf)
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            out[rows, h * head_dim:(h + 1) * head_dim] = (p @ V) / p.sum(axis=1, keepdims=True)
+    return o.f32_to_bf16_bits(out.astype(F32))
+
+
+def prefill(hidden_bits, layers, final_norm_bits, k_caches, v_caches, seq_offsets, seq_lens, slot_mapping,
+            n_q_heads, n_kv_heads, head_dim, linear):
+    """Infer-engine/cuda/decoder.cu:1219-1557: the layer sequence of a batched variable-length prefill.
+    Positions start at 0 in every sequence; caches are updated in place (slot_mapping per token row).
+    Returns the final-normed hidden states (bf16 bits)."""
+    h = hidden_bits.copy()
+    pos = np.zeros(h.shape[0], np.int32)
+    for off, ln in zip(seq_offsets, seq_lens):
+        pos[off:off + ln] = np.arange(ln)
+    for l, Lw in enumerate(layers):
+        x = rmsnorm(h, Lw["norm1"])
+        q = rope_single_token(linear(x, Lw["q"]), pos, n_q_heads, head_dim)
+        k = rope_single_token(linear(x, Lw["k"]), pos, n_kv_heads, head_dim)
+        v = linear(x, Lw["v"])
+        reshape_and_cache(k_caches[l], v_caches[l], k, v, slot_mapping)
+        a = prefill_attention(q, k, v, seq_offsets, seq_lens, n_q_heads, n_kv_heads, head_dim)
+        h = o.residual_add(linear(a, Lw["o"]), h)
+        x = rmsnorm(h, Lw["norm2"])
+        act = o.silu_mul_split_packed(np.concatenate([linear(x, Lw["gate"]), linear(x, Lw["up"])], axis=1))
+        h = o.residual_add(linear(act, Lw["down"]), h)
+    return rmsnorm(h, final_norm_bits)

@@ -281,3 +281,121 @@ def test_decode_step_w4a4_vs_oracle_in_subprocess():
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "ERR" in r.stdout
+
+
+# ---------------------------------------------------------------------------------------------
+# batched variable-length prefill
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("qh,kvh,causal", [(16, 4, True), (4, 4, True), (8, 1, False)])
+def test_prefill_attention_vs_oracle(qh, kvh, causal):
+    """flash_fwd_vllm_gqa_launch on strided q|k|v slices against the float64 per-sequence attention."""
+    from glm_asr_stack_b200 import engine
+    rng = np.random.default_rng(qh + kvh)
+    hd = 128
+    lens = [1, 63, 64, 65, 200, 394, 17]
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T, H, KV = int(offs[-1]), qh * hd, kvh * hd
+    qkv = rnd_bits(rng, (T, H + 2 * KV))
+    buf = to_dev_bf16(qkv)
+    got = bits_of(engine.prefill_attention(buf[:, :H], buf[:, H:H + KV], buf[:, H + KV:], torch.from_numpy(offs).cuda(),
+                                           max(lens), qh, kvh, hd, causal))
+    want = do.prefill_attention(qkv[:, :H], qkv[:, H:H + KV], qkv[:, H + KV:], offs[:-1], lens, qh, kvh, hd, causal)
+    assert o.rel_err(got, want) <= REL_TOL_TIGHT
+    # row by row: every query row within bf16 tolerance, the first row of a causal sequence is its own V row
+    for off, ln in zip(offs[:-1], lens):
+        assert o.rel_err(got[off:off + ln], want[off:off + ln]) <= REL_TOL_TIGHT
+        if causal:
+            v0 = qkv[off, H + KV:].reshape(kvh, hd)
+            assert np.array_equal(got[off].reshape(qh, hd), np.repeat(v0, qh // kvh, axis=0))
+
+
+def run_prefill_case(w4a4: bool):
+    """decoder_prefill_paged_batched on a small model against the oracle's layer sequence, then one decode
+    step on top of the cache the prefill wrote (the two drivers must agree on the cache layout)."""
+    from glm_asr_stack_b200 import engine, ops
+    rng = np.random.default_rng(21)
+    H, F, QH, KVH, HD, L, bs = 256, 512, 2, 1, 128, 2, 16
+    lens = [70, 1, 33, 130]
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)[:-1]
+    T, n = int(sum(lens)), len(lens)
+    num_blocks, max_blocks = 64, 16
+    names = [("self_attn.q_proj", H, H), ("self_attn.k_proj", KVH * HD, H), ("self_attn.v_proj", KVH * HD, H),
+             ("self_attn.o_proj", H, H), ("mlp.gate_proj", F, H), ("mlp.up_proj", F, H), ("mlp.down_proj", H, F)]
+    ws = engine.WeightStore()
+    layers = []
+    isc = 0.02
+    for l in range(L):
+        Lw = {}
+        for i, (nm, N, K) in enumerate(names):
+            pw, sw, g = o.seeded_weight(N, K, 300 + 100 * l + i)
+            ws.add_fp4(f"language_model.model.layers.{l}.{nm}",
+                       ops.Fp4Tensor(torch.from_numpy(pw).cuda(), torch.from_numpy(sw).cuda(), g), isc)
+            Lw[nm.split(".")[1].split("_")[0]] = (pw, sw, g)
+        for nm in ("input_layernorm", "post_attention_layernorm"):
+            nb = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
+            ws.add(f"language_model.model.layers.{l}.{nm}.weight", to_dev_bf16(nb))
+            Lw["norm1" if nm == "input_layernorm" else "norm2"] = nb
+        layers.append(Lw)
+    fn = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
+    ws.add("language_model.model.norm.weight", to_dev_bf16(fn))
+    cfg = engine.model_config(H, L, QH, KVH, HD, F, 1000)
+    pool = engine.KVPool(num_blocks, bs, L, KVH, HD, max_seqs=8, max_blocks_per_seq=max_blocks)
+    perm = rng.permutation(num_blocks).tolist()
+    tables = [[perm.pop() for _ in range((ln + 1 + bs - 1) // bs)] for ln in lens]     # room for one decoded token
+    bts = engine.BlockTables(pool, tables)
+    bt_np = np.full((n, max_blocks), -1, np.int32)
+    for i, t in enumerate(tables):
+        bt_np[i, :len(t)] = t
+    pool.k.zero_()
+    pool.v.zero_()
+    hidden = rnd_bits(rng, (T, H))
+    hd_dev = to_dev_bf16(hidden)
+    engine.prefill_paged_batched(ws, cfg, pool, bts, hd_dev, lens, offs.tolist())
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    lin = (lambda x, w: o.nvfp4_linear(x, w[0], w[1], isc, w[2])) if w4a4 else (lambda x, w: o.linear_o1(x, *w))
+    slots = np.concatenate([[bt_np[s, t // bs] * bs + t % bs for t in range(ln)] for s, ln in enumerate(lens)]).astype(np.int64)
+    kc = [np.zeros((num_blocks * bs, KVH * HD), np.uint16) for _ in range(L)]
+    vc = [np.zeros((num_blocks * bs, KVH * HD), np.uint16) for _ in range(L)]
+    want = do.prefill(hidden, layers, fn, kc, vc, offs, lens, slots, QH, KVH, HD, lin)
+    got = bits_of(hd_dev)
+    err = o.rel_err(got, want)
+    assert err <= REL_TOL_VS_ORACLE, err
+    assert o.cosine(got, want) >= 0.999
+    kv_tol = 5e-2 if w4a4 else REL_TOL_VS_ORACLE      # see run_decode_step_case for the W4A4 bound
+    for l in range(L):
+        kd = bits_of(pool.k[l].reshape(num_blocks * bs, -1))
+        mask = np.ones(num_blocks * bs, bool)
+        mask[slots] = False
+        assert not kd[mask].any()                       # rows of no token stay untouched
+        assert o.rel_err(kd[slots], kc[l][slots]) <= kv_tol
+        assert o.rel_err(bits_of(pool.v[l].reshape(num_blocks * bs, -1))[slots], vc[l][slots]) <= kv_tol
+    # one decode step on top of that cache: compare with the oracle continuing from the device's cache
+    cached = np.array(lens, np.int32)
+    nxt = rnd_bits(rng, (n, H))
+    nd = to_dev_bf16(nxt)
+    d_lens = torch.from_numpy(cached.copy()).cuda()
+    h_lens = (ctypes.c_int * n)(*cached.tolist())
+    kc_dev = [bits_of(pool.k[l].reshape(num_blocks * bs, -1)).copy() for l in range(L)]
+    vc_dev = [bits_of(pool.v[l].reshape(num_blocks * bs, -1)).copy() for l in range(L)]
+    engine.decode_step(ws, cfg, pool, bts, nd, d_lens, h_lens)
+    torch.cuda.synchronize()
+    dslots = np.array([bt_np[i, cached[i] // bs] * bs + cached[i] % bs for i in range(n)], np.int64)
+    want2 = do.decode_step(nxt, layers, fn, kc_dev, vc_dev, bt_np, cached, dslots, QH, KVH, HD, bs, lin)
+    assert o.rel_err(bits_of(nd), want2) <= REL_TOL_VS_ORACLE
+    assert ops.status() == 0
+    return err
+
+
+def test_prefill_w4a16_vs_oracle():
+    os.environ.pop("GLMASR_USE_CUTLASS_NVFP4", None)
+    run_prefill_case(False)
+
+
+def test_prefill_w4a4_vs_oracle_in_subprocess():
+    env = dict(os.environ, GLMASR_USE_CUTLASS_NVFP4="1")
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_gpu_decoder as t; print('ERR', t.run_prefill_case(True))"
+            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")))
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ERR" in r.stdout
