@@ -207,6 +207,85 @@ def run_decode(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_prefill(args, rank, local_rank, world):
+    """The whole batched prefill the config-1 projections belong to: 28 layers over 25 windows x 400 tokens
+    (10000 tokens) through decoder_prefill_paged_batched -- projections, RoPE + paged-cache write, causal
+    attention.  tok/s = prefilled tokens / step time; TFLOP/s counts the projections and the attention."""
+    os.environ["GLMASR_USE_CUTLASS_NVFP4"] = "1" if args.mode == "w4a4" else "0"
+    import torch
+
+    from glm_asr_stack_b200 import engine, ops, synth, workloads
+
+    torch.cuda.set_device(local_rank)
+    dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
+    model = workloads.build_decoder(layers=args.layers)
+    cfg = model.cfg
+    nseq = max(1, args.rows // 400)
+    st = workloads.build_prefill_state(cfg, num_seqs=nseq, seq_len=400)
+    T, H = st.total_tokens, cfg.dec_hidden
+    xs = [synth.seeded_activation(T, H, 31 + i) for i in range(2)]
+    hid = torch.empty_like(xs[0])
+    hin = xs[0].cpu().pin_memory()
+    hout = torch.empty_like(hin).pin_memory()
+
+    def step(i):
+        hid.copy_(xs[i % 2])
+        engine.prefill_paged_batched(model.ws, cfg, st.pool, st.bts, hid, st.seq_lens, st.seq_offsets)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    l0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = ops.launch_count() - l0
+    clocks = sampler.stop()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        hid.copy_(hin, non_blocking=True)
+        engine.prefill_paged_batched(model.ws, cfg, st.pool, st.bts, hid, st.seq_lens, st.seq_offsets)
+        hout.copy_(hid, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    ms = replicas.max_over_ranks(ms, dist, "cuda")
+    e2e_ms = replicas.max_over_ranks(e2e_ms, dist, "cuda")
+    QH, HD = cfg.dec_heads, cfg.dec_head_dim
+    attn_flops = sum(2 * 2 * QH * HD * (ln * (ln + 1) // 2) for ln in st.seq_lens)          # QK^T and PV, causal half
+    flops = cfg.dec_layers * (layer_flops(T) + attn_flops)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "prefill_tok_per_s", "value": replicas.whole_job_rate(T, world, ms * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
+            "config": {"workload": f"batched prefill, {cfg.dec_layers} layers, {nseq} sequences x 400 tokens = {T} tokens, "
+                                   "paged bf16 KV (16-token pages)",
+                       "l2": "weights of 28 layers (0.76 GB) and 41 MB of activations per layer > 126 MB L2"},
+            "tflops": replicas.whole_job_rate(flops, world, ms * 1e-3) / 1e12,
+            "e2e": {"value": replicas.whole_job_rate(T, world, e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": T * H * 2,
+                    "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -216,8 +295,9 @@ def main():
     ap.add_argument("--mode", default="w4a4", choices=["w4a4", "w4a16"])
     ap.add_argument("--rows", type=int, default=M_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="layer", choices=["layer", "decode"],
-                    help="layer = BASELINE config 1 (default, the headline); decode = BASELINE config 2")
+    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "prefill"],
+                    help="layer = BASELINE config 1 (default, the headline); decode = BASELINE config 2; "
+                         "prefill = the whole 28-layer batched prefill the config-1 projections belong to")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--layers", type=int, default=28)
     args = ap.parse_args()
@@ -231,6 +311,9 @@ def main():
 
     if args.workload == "decode":
         run_decode(args, rank, local_rank, world)
+        return
+    if args.workload == "prefill":
+        run_prefill(args, rank, local_rank, world)
         return
 
     import torch

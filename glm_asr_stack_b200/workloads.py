@@ -88,3 +88,28 @@ def build_decode_state(cfg, num_seqs=256, ctx_lo=200, ctx_hi=450, block_size=16,
     row_bytes = cfg.dec_kv_heads * cfg.dec_head_dim * 2
     kv_bytes = int((cached.astype(np.int64) + 1).sum()) * row_bytes * 2 * cfg.dec_layers
     return DecodeState(pool, bts, cached, d_lens, h_lens, kv_bytes)
+
+
+@dataclass
+class PrefillState:
+    pool: engine.KVPool
+    bts: engine.BlockTables
+    seq_lens: List[int]
+    seq_offsets: List[int]
+    total_tokens: int
+
+
+def build_prefill_state(cfg, num_seqs=25, seq_len=400, block_size=16, seed=4, device="cuda") -> PrefillState:
+    """A prefill batch as the reference's scheduler forms it: num_seqs windows of ~seq_len tokens packed
+    back to back (10000 tokens = 25 x 400 at the batch limit), each with its own blocks of a fresh pool."""
+    rng = np.random.default_rng(seed)
+    lens = [int(seq_len)] * num_seqs
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)[:-1].tolist()
+    need = [(ln + 1 + block_size - 1) // block_size for ln in lens]
+    num_blocks = sum(need) + 16
+    pool = engine.KVPool(num_blocks, block_size, cfg.dec_layers, cfg.dec_kv_heads, cfg.dec_head_dim, max(num_seqs, 1),
+                         max(need) + 1, device)
+    perm = rng.permutation(num_blocks).tolist()
+    tables = [[perm.pop() for _ in range(nb)] for nb in need]
+    bts = engine.BlockTables(pool, tables)
+    return PrefillState(pool, bts, lens, [int(o) for o in offs], int(sum(lens)))
