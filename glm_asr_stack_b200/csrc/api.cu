@@ -39,7 +39,7 @@ struct TimedLaunch {
 };
 static std::vector<TimedLaunch> g_timed;
 
-static constexpr int kSlots = 32;   // 0..12 and 24..25 used here, 13..23 and 26..31 by the decode step (decoder_step.cu)
+static constexpr int kSlots = 32;   // 0..12, 24..25, 30..31 used here, 13..23 and 26..29 by the decode step (decoder_step.cu)
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
 
@@ -60,6 +60,17 @@ int *device_status_word() {
     return g_status;
 }
 
+// 0: never, 1: everywhere except the chunked host-buffer call, 2: everywhere
+static int g_pdl_mode = -1;
+static bool g_pdl_suppressed = false;      // set while the chunked host-buffer call enqueues its kernels
+bool pdl_enabled() {
+    if (g_pdl_mode < 0) {
+        const char *e = getenv("GLMASR_PDL");
+        g_pdl_mode = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+    }
+    return g_pdl_mode == 2 || (g_pdl_mode == 1 && !g_pdl_suppressed);
+}
+
 void *workspace_slot(int slot, size_t bytes) {
     if (bytes > g_ws_bytes[slot]) {
         if (g_ws[slot]) {
@@ -73,6 +84,13 @@ void *workspace_slot(int slot, size_t bytes) {
     return g_ws[slot];
 }
 void *workspace(size_t bytes) { return workspace_slot(0, bytes); }
+// Same, zero-filled whenever it is (re)allocated; users keep it zero between their launches.
+static void *workspace_slot_zeroed(int slot, size_t bytes) {
+    const size_t before = g_ws_bytes[slot];
+    void *ptr = workspace_slot(slot, bytes);
+    if (g_ws_bytes[slot] != before) GLMASR_CUDA_CHECK(cudaMemsetAsync(ptr, 0, g_ws_bytes[slot], g_stream));
+    return ptr;
+}
 
 static void clear_tmap_cache();
 
@@ -100,7 +118,8 @@ enum Slot : int {
     WS_L_QKV = 6, WS_L_H1 = 7, WS_L_ACT = 8, WS_L_IN = 9, WS_L_OUT = 10,
     WS_WDEQ = 11,
     WS_DBG = 12,      // cycle counters of timing experiments
-    WS_L_ACTQ = 24, WS_L_ACTSF = 25,   // layer path: quantised SiLU-gate output handed to the down projection
+    WS_L_ACTQ = 24, WS_L_ACTSF = 25,
+    WS_PARTIAL = 30, WS_COUNTERS = 31,   // split-K partial accumulators and per-tile arrival counters   // layer path: quantised SiLU-gate output handed to the down projection
 };
 
 static int num_sms() {
@@ -160,6 +179,16 @@ static bool no_fused_act_quant() {
         v = (e && e[0] == '1') ? 1 : 0;
     }
     return v == 1;
+}
+
+// GLMASR_SPLIT_K=n forces the split-K factor of the small-M W4A4 GEMMs (1 = off); unset: chosen per shape
+static int split_k_override() {
+    static int v = -2;
+    if (v == -2) {
+        const char *e = getenv("GLMASR_SPLIT_K");
+        v = (e && e[0]) ? atoi(e) : -1;
+    }
+    return v;
 }
 
 static bool force_simt() {
@@ -588,7 +617,23 @@ static int run_fused(const FusedArgs &a) {
         p.num_n_tiles = (subtiles + nb - 1) / nb;
     }
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
-    const int ctas = total_tiles < num_sms() ? total_tiles : num_sms();
+    // Few tiles (decode: M <= 256): split K so that every SM streams a share of the weights
+    int split = 1;
+    if (a.mode == GEMM_W4A4 && total_tiles * 2 <= num_sms()) {
+        split = num_sms() / total_tiles;
+        if (split > 4) split = 4;
+        if (split > p.num_k_blocks / 2) split = p.num_k_blocks / 2;     // at least two K blocks per CTA
+        const int forced = split_k_override();
+        if (forced >= 0) split = forced < 1 ? 1 : (forced > p.num_k_blocks ? p.num_k_blocks : forced);
+        if (split < 1) split = 1;
+    }
+    if (split > 1) {
+        p.split_k = split;
+        p.partial = (float *)workspace_slot(WS_PARTIAL, (size_t)total_tiles * split * 128 * (128 * nb) * sizeof(float));
+        p.tile_counters = (int *)workspace_slot_zeroed(WS_COUNTERS, (size_t)total_tiles * sizeof(int));
+    }
+    const int work = total_tiles * split;
+    const int ctas = work < num_sms() ? work : num_sms();
     TimedLaunch tl;
     if (g_profile) {
         cudaEventCreate(&tl.start);
@@ -989,7 +1034,9 @@ extern "C" int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, c
         const size_t off = (size_t)r0 * row_bytes;
         if (cudaStreamWaitEvent(g_stream, g_ev_in[n], 0) != cudaSuccess) return -1;
         g_route_rows = M;
+        g_pdl_suppressed = true;    // kernels of one chunk overlapping the next chunk's copy-in wait measured slower
         const int rc = layer_proj_device(mode, (uint16_t *)(dout + off), (const uint16_t *)(din + off), lw, rows);
+        g_pdl_suppressed = false;
         g_route_rows = 0;
         if (rc != 0) return rc;
         if (cudaEventRecord(g_ev_done[n], g_stream) != cudaSuccess) return -1;

@@ -9,6 +9,7 @@
 
 #include "decoder_ops.cuh"
 #include "fp4_format.cuh"
+#include "runtime.cuh"
 
 namespace glmasr {
 
@@ -21,6 +22,8 @@ namespace glmasr {
 // --------------------------------------------------------------------------------------------
 __global__ void rmsnorm_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ x,
                                const __nv_bfloat16 *__restrict__ weight, float eps, int rows, int dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __nv_bfloat16 row_s[];
     __shared__ float rms_s;
     const int row = blockIdx.x;
@@ -71,7 +74,8 @@ __global__ void rmsnorm_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloa
 void launch_rmsnorm(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps, int rows,
                     int dim, cudaStream_t st) {
     if (rows <= 0 || dim <= 0) return;
-    rmsnorm_kernel<<<rows, 256, (size_t)dim * sizeof(__nv_bfloat16), st>>>(out, x, weight, eps, rows, dim);
+    GLMASR_PREFER_MAX_SMEM(rmsnorm_kernel);
+    launch_chained(rmsnorm_kernel, dim3(rows), dim3(256), (size_t)dim * sizeof(__nv_bfloat16), st, out, x, weight, eps, rows, dim);
 }
 
 // --------------------------------------------------------------------------------------------
@@ -81,6 +85,8 @@ void launch_rmsnorm(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfloa
 // --------------------------------------------------------------------------------------------
 __global__ void rope_single_token_kernel(__nv_bfloat16 *tensor, int ld, int col0, const int *__restrict__ positions,
                                          int num_seqs, int n_heads, int head_dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int half_dim = head_dim / 2;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= num_seqs * n_heads * half_dim) return;
@@ -103,7 +109,8 @@ void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int
                               int head_dim, cudaStream_t st) {
     const int total = num_seqs * n_heads * (head_dim / 2);
     if (total <= 0) return;
-    rope_single_token_kernel<<<(total + 255) / 256, 256, 0, st>>>(tensor, ld, col0, positions, num_seqs, n_heads, head_dim);
+    GLMASR_PREFER_MAX_SMEM(rope_single_token_kernel);
+    launch_chained(rope_single_token_kernel, dim3((total + 255) / 256), dim3(256), 0, st, tensor, ld, col0, positions, num_seqs, n_heads, head_dim);
 }
 
 // --------------------------------------------------------------------------------------------
@@ -118,6 +125,8 @@ void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int
 __global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *__restrict__ positions,
                                      const int64_t *__restrict__ slot_mapping, __nv_bfloat16 *__restrict__ key_cache,
                                      __nv_bfloat16 *__restrict__ value_cache, int q_heads, int kv_heads, int head_dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float cs[];            // [half_dim] cos, [half_dim] sin
     const int seq = blockIdx.x;
     const int half_dim = head_dim / 2;
@@ -166,7 +175,8 @@ bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, cons
     if ((head_dim % 2) != 0 || (row_elems % 8) != 0 || (ld % 8) != 0 || (v_col % 8) != 0 ||
         (((uintptr_t)qkv | (uintptr_t)value_cache) & 15) != 0)
         return false;
-    rope_qk_cache_kernel<<<num_seqs, 256, (size_t)head_dim * sizeof(float), st>>>(qkv, ld, k_col, v_col, positions, slot_mapping,
+    GLMASR_PREFER_MAX_SMEM(rope_qk_cache_kernel);
+    launch_chained(rope_qk_cache_kernel, dim3(num_seqs), dim3(256), (size_t)head_dim * sizeof(float), st, qkv, ld, k_col, v_col, positions, slot_mapping,
                                                                              key_cache, value_cache, q_heads, kv_heads,
                                                                              head_dim);
     return true;
@@ -180,6 +190,8 @@ bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, cons
 __global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf, int sf_chunks,
                                      const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ weight,
                                      float eps, float inv_in, int rows, int dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __nv_bfloat16 row_s[];
     __shared__ float rms_s;
     const int row = blockIdx.x;
@@ -227,7 +239,8 @@ bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 
     if (rows <= 0) return true;
     if ((dim % 64) != 0 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)q_packed) & 15) != 0 || !(input_scale > 0.0f))
         return false;
-    rmsnorm_quant_kernel<<<rows, 128, (size_t)dim * sizeof(__nv_bfloat16), st>>>(q_packed, q_sf, dim / 64, x, weight, eps,
+    GLMASR_PREFER_MAX_SMEM(rmsnorm_quant_kernel);
+    launch_chained(rmsnorm_quant_kernel, dim3(rows), dim3(128), (size_t)dim * sizeof(__nv_bfloat16), st, q_packed, q_sf, dim / 64, x, weight, eps,
                                                                             1.0f / input_scale, rows, dim);
     return true;
 }
@@ -241,6 +254,8 @@ __global__ void reshape_and_cache_kernel(__nv_bfloat16 *__restrict__ key_cache, 
                                          const __nv_bfloat16 *__restrict__ key, int ldk,
                                          const __nv_bfloat16 *__restrict__ value, int ldv,
                                          const int64_t *__restrict__ slot_mapping, int num_tokens, int row_elems) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int chunks = row_elems / 8;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= num_tokens * chunks) return;
@@ -273,7 +288,8 @@ void launch_reshape_and_cache(__nv_bfloat16 *key_cache, __nv_bfloat16 *value_cac
                      (((uintptr_t)value_cache & 15) == 0);
     if (vec) {
         const int total = num_tokens * (row_elems / 8);
-        reshape_and_cache_kernel<<<(total + 255) / 256, 256, 0, st>>>(key_cache, value_cache, key, ldk, value, ldv,
+        GLMASR_PREFER_MAX_SMEM(reshape_and_cache_kernel);
+        launch_chained(reshape_and_cache_kernel, dim3((total + 255) / 256), dim3(256), 0, st, key_cache, value_cache, key, ldk, value, ldv,
                                                                       slot_mapping, num_tokens, row_elems);
     } else {
         const int total = num_tokens * row_elems;
@@ -417,6 +433,8 @@ bool launch_paged_decode_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloa
 // --------------------------------------------------------------------------------------------
 __global__ void embedding_lookup_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ table,
                                         const int *__restrict__ ids, int n, int dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x;
     if (i >= n) return;
     const __nv_bfloat16 *row = table + (size_t)ids[i] * dim;
@@ -432,7 +450,8 @@ __global__ void embedding_lookup_kernel(__nv_bfloat16 *__restrict__ out, const _
 void launch_embedding_lookup(__nv_bfloat16 *out, const __nv_bfloat16 *table, const int *ids, int n, int dim,
                              cudaStream_t st) {
     if (n <= 0) return;
-    embedding_lookup_kernel<<<n, 256, 0, st>>>(out, table, ids, n, dim);
+    GLMASR_PREFER_MAX_SMEM(embedding_lookup_kernel);
+    launch_chained(embedding_lookup_kernel, dim3(n), dim3(256), 0, st, out, table, ids, n, dim);
 }
 
 __global__ void gather_rows_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *const *__restrict__ src_rows,
@@ -458,13 +477,16 @@ void launch_scatter_rows(__nv_bfloat16 *const *dst_rows, const __nv_bfloat16 *in
 
 __global__ void gather_block_tables_kernel(int *__restrict__ dst, const int *__restrict__ tables,
                                            const int *__restrict__ rows, int n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x;
     if (i >= n) return;
     const int *src = tables + (size_t)rows[i] * width;
     for (int d = threadIdx.x; d < width; d += blockDim.x) dst[(size_t)i * width + d] = src[d];
 }
 void launch_gather_block_tables(int *dst, const int *tables, const int *rows, int n, int width, cudaStream_t st) {
-    if (n > 0) gather_block_tables_kernel<<<n, 128, 0, st>>>(dst, tables, rows, n, width);
+    GLMASR_PREFER_MAX_SMEM(gather_block_tables_kernel);
+    if (n > 0) launch_chained(gather_block_tables_kernel, dim3(n), dim3(128), 0, st, dst, tables, rows, n, width);
 }
 
 }  // namespace glmasr

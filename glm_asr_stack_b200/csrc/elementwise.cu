@@ -106,6 +106,8 @@ __device__ __forceinline__ size_t swizzled_sf_index(int r, int c, int col_tiles)
 __global__ void quantize_act_kernel(uint8_t *__restrict__ packed_out, uint8_t *__restrict__ scale_rowmajor,
                                     uint8_t *__restrict__ scale_swizzled, const __nv_bfloat16 *__restrict__ x,
                                     const __nv_bfloat16 *__restrict__ pre, float inv_in, int M, int K, int ldx) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int blocks_per_row = K >> 4;
     const long long total = (long long)M * blocks_per_row;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -143,7 +145,8 @@ void launch_quantize_act(uint8_t *packed_out, uint8_t *scale_rowmajor, uint8_t *
                          int ldx, cudaStream_t st) {
     const long long total = (long long)M * (K / 16);
     if (total <= 0) return;
-    quantize_act_kernel<<<blocks_for(total, 256), 256, 0, st>>>(packed_out, scale_rowmajor, scale_swizzled, x, pre,
+    GLMASR_PREFER_MAX_SMEM(quantize_act_kernel);
+    launch_chained(quantize_act_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, st, packed_out, scale_rowmajor, scale_swizzled, x, pre,
                                                                 1.0f / input_scale, M, K, ldx);
 }
 
@@ -234,6 +237,8 @@ __device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bi) 
 
 __global__ void argmax_rows_kernel(const __nv_bfloat16 *__restrict__ logits, int *__restrict__ out_tokens, int rows,
                                    int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sh_val[256];
     __shared__ int sh_idx[256];
     const int row = blockIdx.x, tid = threadIdx.x;
@@ -285,7 +290,8 @@ __global__ void argmax_rows_kernel(const __nv_bfloat16 *__restrict__ logits, int
 
 void launch_argmax_rows(const __nv_bfloat16 *logits, int *out_tokens, int rows, int vocab, cudaStream_t st) {
     if (rows <= 0) return;
-    argmax_rows_kernel<<<rows, 256, 0, st>>>(logits, out_tokens, rows, vocab);
+    GLMASR_PREFER_MAX_SMEM(argmax_rows_kernel);
+    launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, logits, out_tokens, rows, vocab);
 }
 
 }  // namespace glmasr

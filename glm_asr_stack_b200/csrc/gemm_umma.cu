@@ -35,6 +35,7 @@
 #include "gemm_device.cuh"
 #include "gemm_umma.cuh"
 #include "ptx.cuh"
+#include "runtime.cuh"
 
 namespace glmasr {
 
@@ -106,6 +107,8 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const long long t_start = ((p.debug & 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -133,9 +136,14 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                 // set-up above touched no global memory; everything below may
+    const long long t_setup = ((p.debug & 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
 
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
     const int nkb = p.num_k_blocks;
+    // split-K: work item w = tile * S + split covers K blocks [split * nkb / S, (split + 1) * nkb / S)
+    const int S = (MODE == GEMM_W4A4 && p.split_k > 1) ? p.split_k : 1;
+    const int total_work = total_tiles * S;
     const bool dbg = (p.debug & 64) != 0 && p.dbg_cycles != nullptr;
     unsigned long long dbg_acc[4] = {0, 0, 0, 0};
 
@@ -145,7 +153,9 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
         const bool leader = elect_one();
         uint32_t it = 0, raw_it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+            const int tile = work / S, split = work - tile * S;
+            const int kb0 = split * nkb / S, kb1 = (split + 1) * nkb / S;
             const int m_tile = tile % p.num_m_tiles;
             const int n_tile = tile / p.num_m_tiles;
             SubTile st[NB];
@@ -162,7 +172,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                     sfb_src[h] = p.sfb[st[h].seg] + (size_t)rt * p.sf_k_chunks * C::SF_CHUNK;
                 }
             }
-            for (int kb = 0; kb < nkb; ++kb) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 if constexpr (MODE == GEMM_W4A16) {
                     if ((kb & 3) == 0) {
                         const int r = raw_it & 1;
@@ -222,7 +232,9 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
         constexpr uint32_t idesc = MODE == GEMM_W4A4 ? idesc_nvfp4(128, C::BN) : idesc_bf16(128, C::BN);
         uint32_t it = 0, acc_it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+            const int split = work % S;
+            const int kb0 = split * nkb / S, kb1 = (split + 1) * nkb / S;
             const int acc = acc_it % C::NUM_ACC;
             const uint32_t aph = (acc_it / C::NUM_ACC) & 1u;
             DBG_T0();
@@ -230,7 +242,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
             DBG_ACC(0);
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C::BN);
-            for (int kb = 0; kb < nkb; ++kb) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1u;
                 if (!mbar_wait_warp(full_bar(s), ph, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
@@ -262,7 +274,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                         if ((p.debug & 16) && k > 0) break;   // experiment: a quarter of the MMAs
                         const uint64_t adesc = adesc0 + (uint64_t)((k * 32) >> 4);
                         const uint64_t bdesc = bdesc0 + (uint64_t)((k * 32) >> 4);
-                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
                         if constexpr (MODE == GEMM_W4A4)
                             umma_nvfp4(d_tmem, adesc, bdesc, idesc, accumulate, sfa_t + 4 * k, sfb_t + 4 * NB * k);
                         else
@@ -285,7 +297,8 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
         constexpr int HC = C::BN / (C::EPI_WARPS / 4);   // columns per warp
         constexpr int NCH = HC / 32;             // 32-column groups per warp
         uint32_t acc_it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+            const int tile = work / S, split = work - tile * S;
             const int m_tile = tile % p.num_m_tiles;
             const int n_tile = tile / p.num_m_tiles;
             const int acc = acc_it % C::NUM_ACC;
@@ -307,6 +320,64 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                 DBG_ACC(1);
             };
 
+            // ---- split-K: dump the raw partial; the CTA that arrives last reduces and finishes the tile ----
+            bool from_partials = false;
+            if constexpr (MODE == GEMM_W4A4) {
+                if (S > 1) {
+                    const int rowt = quad * 32 + lane;
+                    float4 *mine = reinterpret_cast<float4 *>(p.partial + ((size_t)tile * S + split) * (size_t)(128 * C::BN));
+#pragma unroll 1
+                    for (int ch = 0; ch < NCH; ++ch) {
+                        uint32_t r[32];
+                        tmem_ld_x32(t_row + half * HC + ch * 32, r);
+                        tmem_ld_wait();
+                        const int c4 = (half * HC + ch * 32) >> 2;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            __stcg(mine + (size_t)(c4 + j) * 128 + rowt,
+                                   make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                    }
+                    release_acc();
+                    __threadfence();
+                    volatile int *flag = reinterpret_cast<volatile int *>(smem_gen + 528) + (acc_it & 1u);
+                    asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+                    if (warp == 2 && lane == 0) {
+                        const int old = atomicAdd(p.tile_counters + tile, 1);
+                        if (old == S - 1) p.tile_counters[tile] = 0;          // ready for the next launch
+                        *flag = old;
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+                    if (*flag != S - 1) {
+                        DBG_ACC(2);
+                        ++acc_it;
+                        continue;
+                    }
+                    __threadfence();
+                    from_partials = true;
+                }
+            }
+            // 32 columns of this lane's row, from tile column col0: the sum of the splits' partials in split order
+            auto load_sum = [&](int col0, uint32_t (&r)[32]) {
+                const int rowt = quad * 32 + lane;
+                float4 a[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < S; ++sp) {
+                    const float4 *ps = reinterpret_cast<const float4 *>(p.partial + ((size_t)tile * S + sp) * (size_t)(128 * C::BN));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 v = __ldcg(ps + (size_t)((col0 >> 2) + j) * 128 + rowt);
+                        a[j].x += v.x, a[j].y += v.y, a[j].z += v.z, a[j].w += v.w;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    r[4 * j] = __float_as_uint(a[j].x), r[4 * j + 1] = __float_as_uint(a[j].y);
+                    r[4 * j + 2] = __float_as_uint(a[j].z), r[4 * j + 3] = __float_as_uint(a[j].w);
+                }
+            };
+
             if (p.epi == EPI_SILU_GATE) {
                 if constexpr (NB == 2) {
                     // gate columns [GC*half, +GC) pair with up columns [128 + GC*half, +GC)
@@ -326,7 +397,15 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                         const int nvalid = sg.ncols - c0;
                         if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
                     };
-                    if constexpr (C::EARLY_RELEASE) {
+                    if (from_partials) {
+#pragma unroll 1
+                        for (int ch = 0; ch < GCH; ++ch) {
+                            uint32_t rg[32], ru[32];
+                            load_sum(half * GC + ch * 32, rg);
+                            load_sum(128 + half * GC + ch * 32, ru);
+                            finish_gate(rg, ru, ch);
+                        }
+                    } else if constexpr (C::EARLY_RELEASE) {
                         uint32_t rg[GCH][32], ru[GCH][32];
 #pragma unroll
                         for (int ch = 0; ch < GCH; ++ch) {
@@ -377,7 +456,14 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                     }
                     if (!(p.debug & 4)) store_row_chunk(out_row + col, v, nvalid);
                 };
-                if constexpr (C::EARLY_RELEASE) {
+                if (from_partials) {
+#pragma unroll 1
+                    for (int ch = 0; ch < NCH; ++ch) {
+                        uint32_t r[32];
+                        load_sum(half * HC + ch * 32, r);
+                        finish_chunk(r, ch);
+                    }
+                } else if constexpr (C::EARLY_RELEASE) {
                     uint32_t r[NCH][32];
 #pragma unroll
                     for (int ch = 0; ch < NCH; ++ch) tmem_ld_x32(t_row + half * HC + ch * 32, r[ch]);
@@ -451,6 +537,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
     }
 
     // ================================ teardown ==========================================
+    const long long t_roles = dbg ? clock64() : 0;
     tc_fence_before();
     __syncthreads();
     if (*abort_word != 0) {
@@ -461,6 +548,12 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
     if (warp == 1) {
         __syncwarp();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+        if (dbg && lane == 0) {
+            // kernel timeline of this CTA: set-up, role loops (this warp), teardown
+            p.dbg_cycles[blockIdx.x * 16 + 12] = (unsigned long long)(t_setup - t_start);
+            p.dbg_cycles[blockIdx.x * 16 + 13] = (unsigned long long)(t_roles - t_setup);
+            p.dbg_cycles[blockIdx.x * 16 + 14] = (unsigned long long)(clock64() - t_roles);
+        }
     }
 }
 
@@ -468,8 +561,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
 template <int MODE, int NB>
 static cudaError_t launch_one(const GemmParams &p, int num_ctas, cudaStream_t st) {
     using C = Cfg<MODE, NB>;
-    umma_gemm_kernel<MODE, NB><<<num_ctas, C::THREADS, C::SMEM_BYTES, st>>>(p);
-    return cudaGetLastError();
+    return launch_chained(umma_gemm_kernel<MODE, NB>, dim3(num_ctas), dim3(C::THREADS), (size_t)C::SMEM_BYTES, st, p);
 }
 
 template <int MODE, int NB>

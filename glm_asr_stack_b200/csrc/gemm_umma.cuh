@@ -52,6 +52,13 @@ struct alignas(64) GemmParams {
     float q_inv_in;                     // 1 / input_scale of the consuming GEMM
     int q_ld;                           // bytes per packed row (= columns / 2)
     int q_sf_chunks;                    // ceil(columns / 64)
+    // Split-K (single-CTA kernel, W4A4): every tile is computed by split_k CTAs over disjoint K ranges.
+    // Each writes its raw fp32 partial to `partial`; the CTA that finishes last (per-tile counter) adds
+    // the partials in split order and runs the epilogue, so the result does not depend on arrival order
+    // and no CTA ever waits for another.  split_k <= 1: off.
+    int split_k;
+    float *partial;                     // [tiles][split_k][128 x BN] fp32, column-quad major
+    int *tile_counters;                 // [tiles], zero between launches (the last CTA resets its tile's)
     int num_m_tiles, num_n_tiles;
     int num_k_blocks;                   // K steps of 128 operand bytes per row (W4A4: 256 elements, else 64)
     int sf_k_chunks;                    // W4A4: 512-byte scale chunks per 128-row tile along K (= ceil(K/64))

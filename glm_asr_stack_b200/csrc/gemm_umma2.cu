@@ -27,6 +27,7 @@
 #include "gemm_device.cuh"
 #include "gemm_umma.cuh"
 #include "ptx.cuh"
+#include "runtime.cuh"
 
 namespace glmasr {
 
@@ -41,7 +42,11 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 38912
     static constexpr int STAGES = 5;
     static constexpr int EPI_WARPS = 8;
-    static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+    // warp 0: producer of the activation tile and its scales; warp 1: MMA issuer; warps 2..9: epilogue;
+    // warp 10: producer of the weight half-tile and the weight scales.  Two producer warps halve the
+    // time between a stage being freed and its last load being issued (each TMA issue costs ~60 cycles).
+    static constexpr int PRODUCER_B_WARP = 2 + EPI_WARPS;
+    static constexpr int THREADS = (3 + EPI_WARPS) * 32;
     // Two accumulators that share 64 columns: acc0 = columns [0, 256), acc1 = [192, 448).  A tile's
     // MMAs may start as soon as the previous tile's epilogue has drained the 64 shared columns
     // (which it does first), instead of the whole accumulator.
@@ -80,6 +85,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
     const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs), 1 = peer
     const uint32_t peer = rank ^ 1u;
 
@@ -111,6 +117,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
     cluster_sync_all();                                // both CTAs' barriers exist before any remote signal
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                 // set-up above touched no global memory; everything below may
 
     const int num_pairs = gridDim.x >> 1;
     const int pair = blockIdx.x >> 1;
@@ -120,12 +127,15 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
     const bool dbg = (p.debug & 64) != 0 && p.dbg_cycles != nullptr;
     unsigned long long dbg_acc[4] = {0, 0, 0, 0};
 
-    if (warp == 0) {
-        // ================================ TMA producer (both CTAs) =======================
+    if (warp == 0 || warp == C::PRODUCER_B_WARP) {
+        // ================================ TMA producers (both CTAs) ======================
+        // debug & 256 (timing experiments): warp 0 issues everything and the second producer idles
+        const bool solo = (p.debug & 256) != 0;
+        const bool do_a = warp == 0, do_b = solo ? warp == 0 : warp == C::PRODUCER_B_WARP;
         const bool leader_lane = elect_one();
         const uint32_t full0 = mapa_shared(full_bar(0), 0);      // CTA 0's full[0]; full[s] = full0 + 8 s
         uint32_t it = 0;
-        bool ok = true;
+        bool ok = !(solo && warp == C::PRODUCER_B_WARP);
         for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
             const int m_tile = (tile % num_m_pairs) * 2 + (int)rank;     // this CTA's 128-row tile
             const int n_tile = tile / num_m_pairs;
@@ -143,20 +153,24 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 DBG_ACC(0);
                 const uint32_t sb = stage_base(s);
                 const uint32_t fb = full0 + 8u * (uint32_t)s;
+                const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
                 if (leader_lane) {
-                    if (rank == 0) mbar_expect_tx(full_bar(s), C::TX_BYTES_PAIR);
-                    tma_load_2d_pair(sb, &p.tm_a, fb, kb * 128, m_tile * 128);
-                    tma_load_2d_pair(sb + C::A_BYTES, &p.tm_b[mine.seg], fb, kb * 128, mine.row0);
-                    const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
-                    tma_load_2d_pair(sf, &p.tm_sfa, fb, 0, sfa_row + kb * 4);
-                    tma_load_2d_pair(sf + C::SF_TILE, &p.tm_sfb[st0.seg], fb, 0, sfb_row0 + kb * 4);
-                    tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
+                    if (do_a) {
+                        if (rank == 0) mbar_expect_tx(full_bar(s), C::TX_BYTES_PAIR);
+                        tma_load_2d_pair(sb, &p.tm_a, fb, kb * 128, m_tile * 128);
+                        tma_load_2d_pair(sf, &p.tm_sfa, fb, 0, sfa_row + kb * 4);
+                    }
+                    if (do_b) {
+                        tma_load_2d_pair(sb + C::A_BYTES, &p.tm_b[mine.seg], fb, kb * 128, mine.row0);
+                        tma_load_2d_pair(sf + C::SF_TILE, &p.tm_sfb[st0.seg], fb, 0, sfb_row0 + kb * 4);
+                        tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
+                    }
                 }
                 ++it;
                 DBG_ACC(1);
             }
         }
-        if (dbg && leader_lane && rank == 0) { p.dbg_cycles[pair * 16 + 0] = dbg_acc[0]; p.dbg_cycles[pair * 16 + 1] = dbg_acc[1]; }
+        if (dbg && leader_lane && rank == 0 && warp == 0) { p.dbg_cycles[pair * 16 + 0] = dbg_acc[0]; p.dbg_cycles[pair * 16 + 1] = dbg_acc[1]; }
     } else if (warp == 1) {
         // ================================ MMA issuer (CTA 0 only) ========================
         if (rank == 0) {
@@ -224,7 +238,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
     } else {
         // ================================ epilogue (both CTAs) ==========================
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 2) >> 2;       // warps 2..9 only: the second producer took its own branch above
         const uint32_t tempty0 = mapa_shared(tempty_bar(0), 0);      // tempty[a] = tempty0 + 8 a
         const uint32_t tovl0 = mapa_shared(tovl_bar, 0);
         // output staging: each lane writes its row's 16-byte chunks at (chunk ^ (row & 7)), the layout a
@@ -454,13 +468,15 @@ cudaError_t launch_umma_gemm_pair(const GemmParams &p, int num_pairs, cudaStream
     cfg.blockDim = dim3(PairCfg::THREADS, 1, 1);
     cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, umma_gemm_pair_kernel, p);
 }
 

@@ -20,6 +20,7 @@
 #include <stdint.h>
 
 #include "decoder_ops.cuh"
+#include "runtime.cuh"
 
 namespace glmasr {
 
@@ -71,6 +72,8 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
     const int *__restrict__ block_tables, const int *__restrict__ seq_lens, int num_kv_heads, int group,
     int block_size, int max_blocks_per_seq, float scale) {
     extern __shared__ __align__(1024) uint8_t smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int kv_head = blockIdx.x;
     const int seq = blockIdx.y;
     const int warp = threadIdx.x >> 5;
@@ -271,16 +274,18 @@ bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_b
             return false;
         configured = true;
     }
+    GLMASR_PREFER_MAX_SMEM(paged_decode_attention_mma_kernel<true>);
+    GLMASR_PREFER_MAX_SMEM(paged_decode_attention_mma_kernel<false>);
     const float scale = 1.0f / sqrtf((float)head_dim);
     dim3 grid(num_kv_heads, num_seqs);
     if (block_size % kTile == 0)
-        paged_decode_attention_mma_kernel<true><<<grid, kWarps * 32, kAttnSmem, st>>>(
-            out, ldo, query, ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
-            max_blocks_per_seq, scale);
+        launch_chained(paged_decode_attention_mma_kernel<true>, grid, dim3(kWarps * 32), (size_t)kAttnSmem, st, out, ldo, query,
+                       ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
+                       max_blocks_per_seq, scale);
     else
-        paged_decode_attention_mma_kernel<false><<<grid, kWarps * 32, kAttnSmem, st>>>(
-            out, ldo, query, ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
-            max_blocks_per_seq, scale);
+        launch_chained(paged_decode_attention_mma_kernel<false>, grid, dim3(kWarps * 32), (size_t)kAttnSmem, st, out, ldo, query,
+                       ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
+                       max_blocks_per_seq, scale);
     return true;
 }
 

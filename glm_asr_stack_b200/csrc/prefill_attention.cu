@@ -16,6 +16,7 @@
 #include <stdint.h>
 
 #include "decoder_ops.cuh"
+#include "runtime.cuh"
 
 namespace glmasr {
 
@@ -63,6 +64,8 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
                                                                const int *__restrict__ seq_lens, int group, float scale,
                                                                int causal) {
     extern __shared__ __align__(1024) uint8_t smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int seq = blockIdx.z, head = blockIdx.y, q0 = blockIdx.x * kQTile;
     // seq_lens == NULL: seq_offsets is a cumulative table of num_seqs + 1 entries (cu_seqlens)
     const int off = seq_offsets[seq];
@@ -244,10 +247,10 @@ bool launch_prefill_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *
             return false;
         configured = true;
     }
+    GLMASR_PREFER_MAX_SMEM(prefill_attention_kernel);
     const dim3 grid((max_seq_len + kQTile - 1) / kQTile, num_q_heads, num_seqs);
-    prefill_attention_kernel<<<grid, 128, kSmem, st>>>(out, ldo, q, ldq, k, ldk, v, ldv, seq_offsets, seq_lens,
-                                                       num_q_heads / num_kv_heads, 1.0f / sqrtf((float)head_dim),
-                                                       causal ? 1 : 0);
+    launch_chained(prefill_attention_kernel, grid, dim3(128), (size_t)kSmem, st, out, ldo, q, ldq, k, ldk, v, ldv, seq_offsets,
+                   seq_lens, num_q_heads / num_kv_heads, 1.0f / sqrtf((float)head_dim), causal ? 1 : 0);
     return true;
 }
 

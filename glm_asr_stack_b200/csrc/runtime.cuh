@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 namespace glmasr {
 
@@ -17,6 +18,50 @@ void *workspace_slot(int slot, size_t bytes);
 void free_all_private_state();
 void note_launches(int n);          // launch accounting for kernels started outside api.cu
 size_t tiled_scale_bytes(int rows, int K);   // bytes of the 128x4-tiled scale layout for [rows, K]
+
+// Ask once for the largest shared-memory carve-out for `kernel`.  The GEMM kernels need almost all
+// of an SM's shared memory; a small kernel launched between two of them with the default
+// preference makes the SM switch its L1 / shared split back and forth, which costs microseconds per
+// launch in a chain of 5-15 us kernels.  None of the glue kernels depends on L1 capacity.
+#define GLMASR_PREFER_MAX_SMEM(kernel)                                                                     \
+    do {                                                                                                   \
+        static bool done_ = false;                                                                         \
+        if (!done_) {                                                                                      \
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,                   \
+                                 (int)cudaSharedmemCarveoutMaxShared);                                     \
+            done_ = true;                                                                                  \
+        }                                                                                                  \
+    } while (0)
+
+// ---- programmatic dependent launch -------------------------------------------------------------
+// A chain of 5-40 us kernels on one stream pays a few microseconds per kernel boundary (launch
+// latency, block scheduling, set-up code).  Kernels launched through launch_chained() may become
+// resident while their predecessor is still draining: each of them calls pdl_launch_dependents()
+// first thing and pdl_wait() before it touches global memory, and pdl_wait() returns only when
+// every preceding kernel of the stream has completed and its writes are visible, so data
+// dependencies are exactly those of an ordinary stream.  GLMASR_PDL=0 turns the attribute off.
+bool pdl_enabled();
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 #define GLMASR_CUDA_CHECK(call)                                                              \
     do {                                                                                     \

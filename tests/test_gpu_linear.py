@@ -381,3 +381,36 @@ def test_layer_proj_host_chunked_equals_device(ops):
             ops.layer_proj_host(mode, hin, hout, lw)
             assert torch.equal(dev.cpu(), hout), mode
     assert ops.status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(256, 2048, 6144, "residual"), (256, 3072, 2048, "store"), (200, 512, 2048, "silu"),
+                                       (77, 640, 1024, "store"), (256, 2048, 2048, "residual")])
+def test_split_k_small_m_w4a4(ops, M, N, K, epi):
+    """Decode-sized W4A4 GEMMs have too few tiles for 148 SMs and run split along K: partials summed in a
+    fixed order by the CTA that finishes last.  Same bar as the unsplit kernel against O2, and repeated
+    launches must give identical bits (no dependence on which CTA arrives last)."""
+    x = o.seeded_activation(M, K, 40 + M)
+    isc = o.default_input_scale(x)
+    xd = to_dev_bf16(x)
+    if epi == "silu":
+        wg, wu = o.seeded_weight(N, K, 41), o.seeded_weight(N, K, 42)
+        f = lambda: ops.fp4_linear_fused(ops.MODE_W4A4, xd, [dev_weight(ops, *wg), dev_weight(ops, *wu)],
+                                         epilogue=ops.EPI_SILU_GATE, input_scale=isc)
+        want = o.silu_mul_split_packed(np.concatenate([o.nvfp4_linear(x, wg[0], wg[1], isc, wg[2]),
+                                                       o.nvfp4_linear(x, wu[0], wu[1], isc, wu[2])], axis=1))
+        tol = REL_TOL_VS_ORACLE
+    else:
+        w = o.seeded_weight(N, K, 43)
+        res = o.seeded_activation(M, N, 44) if epi == "residual" else None
+        f = lambda: ops.fp4_linear_fused(ops.MODE_W4A4, xd, [dev_weight(ops, *w)],
+                                         epilogue=ops.EPI_RESIDUAL if res is not None else ops.EPI_STORE,
+                                         residual=to_dev_bf16(res) if res is not None else None, input_scale=isc)
+        want = o.nvfp4_linear(x, w[0], w[1], isc, w[2])
+        if res is not None:
+            want = o.residual_add(want, res)
+        tol = REL_TOL_TIGHT
+    first = f()
+    assert o.rel_err(bits_of(first), want) <= tol
+    for _ in range(20):
+        assert torch.equal(f(), first)
+    assert ops.status() == 0
