@@ -181,7 +181,7 @@ static bool no_fused_act_quant() {
     return v == 1;
 }
 
-// GLMASR_SPLIT_K=n forces the split-K factor of the small-M W4A4 GEMMs (1 = off); unset: chosen per shape
+// GLMASR_SPLIT_K=n: split-K factor of the small-M W4A4 GEMMs (0 = chosen per shape); unset or 1: no split
 static int split_k_override() {
     static int v = -2;
     if (v == -2) {
@@ -617,14 +617,21 @@ static int run_fused(const FusedArgs &a) {
         p.num_n_tiles = (subtiles + nb - 1) / nb;
     }
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
-    // Few tiles (decode: M <= 256): split K so that every SM streams a share of the weights
+    // Few tiles (decode: M <= 256): K can be split so that every SM streams a share of the weights
+    // (GLMASR_SPLIT_K=n, or 0 for a per-shape choice).  Off unless asked for: at these sizes a launch is
+    // bound by its fixed latency (set-up, first loads, epilogue), not by the K loop, and the partials'
+    // round trip through L2 plus the last CTA's reduction cost more than the shorter loop saves
+    // (decode step 3.12 ms unsplit, 3.34 / 3.38 / 3.44 ms with 2 / 3 / per-shape splits).
     int split = 1;
-    if (a.mode == GEMM_W4A4 && total_tiles * 2 <= num_sms()) {
-        split = num_sms() / total_tiles;
-        if (split > 4) split = 4;
-        if (split > p.num_k_blocks / 2) split = p.num_k_blocks / 2;     // at least two K blocks per CTA
+    if (a.mode == GEMM_W4A4 && total_tiles * 2 <= num_sms() && split_k_override() >= 0) {
         const int forced = split_k_override();
-        if (forced >= 0) split = forced < 1 ? 1 : (forced > p.num_k_blocks ? p.num_k_blocks : forced);
+        if (forced == 0) {
+            split = num_sms() / total_tiles;
+            if (split > 4) split = 4;
+            if (split > p.num_k_blocks / 2) split = p.num_k_blocks / 2;     // at least two K blocks per CTA
+        } else {
+            split = forced > p.num_k_blocks ? p.num_k_blocks : forced;
+        }
         if (split < 1) split = 1;
     }
     if (split > 1) {

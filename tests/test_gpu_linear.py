@@ -385,10 +385,13 @@ def test_layer_proj_host_chunked_equals_device(ops):
 
 @pytest.mark.parametrize("M,N,K,epi", [(256, 2048, 6144, "residual"), (256, 3072, 2048, "store"), (200, 512, 2048, "silu"),
                                        (77, 640, 1024, "store"), (256, 2048, 2048, "residual")])
-def test_split_k_small_m_w4a4(ops, M, N, K, epi):
-    """Decode-sized W4A4 GEMMs have too few tiles for 148 SMs and run split along K: partials summed in a
-    fixed order by the CTA that finishes last.  Same bar as the unsplit kernel against O2, and repeated
-    launches must give identical bits (no dependence on which CTA arrives last)."""
+def test_small_m_w4a4_shapes(ops, M, N, K, epi):
+    """Decode-sized W4A4 GEMMs (few tiles for 148 SMs) against O2; repeated launches must give identical bits.
+    test_split_k_in_subprocess runs the same cases with the K loop split across CTAs."""
+    run_small_m_case(ops, M, N, K, epi)
+
+
+def run_small_m_case(ops, M, N, K, epi):
     x = o.seeded_activation(M, K, 40 + M)
     isc = o.default_input_scale(x)
     xd = to_dev_bf16(x)
@@ -414,3 +417,19 @@ def test_split_k_small_m_w4a4(ops, M, N, K, epi):
     for _ in range(20):
         assert torch.equal(f(), first)
     assert ops.status() == 0
+
+
+def test_split_k_in_subprocess():
+    """The split-K variant (GLMASR_SPLIT_K, read once per process): partials summed in split order by the CTA
+    that finishes last -- same bar against O2, and bit-identical results across repeated launches."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]\n"
+            "import test_gpu_linear as t\nfrom glm_asr_stack_b200 import ops\n"
+            "for c in [(256, 2048, 6144, 'residual'), (256, 3072, 2048, 'store'), (200, 512, 2048, 'silu'), (77, 640, 1024, 'store')]:\n"
+            "    t.run_small_m_case(ops, *c)\nprint('SPLIT OK')"
+            % (root, os.path.join(root, "oracle"), os.path.join(root, "tests")))
+    for factor in ("0", "3"):
+        r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, GLMASR_SPLIT_K=factor), capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0 and "SPLIT OK" in r.stdout, r.stdout + r.stderr
