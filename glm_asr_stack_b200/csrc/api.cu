@@ -481,6 +481,10 @@ static int run_fused(const FusedArgs &a) {
     p.dbg_cycles = (p.debug & 64) ? (unsigned long long *)workspace_slot(WS_DBG, 148 * 16 * 8 * 4) : nullptr;
     p.num_m_tiles = (a.M + 127) / 128;
     p.n_out = total_out_cols(a);
+    // W4A4 weights and their re-tiled scales are read-only for every kernel that signals its dependents early:
+    // the only writer, the one-time scale re-tiling, is launched as an ordinary kernel and therefore completes
+    // before anything behind it starts.  So the producer may fetch them ahead of the dependency wait.
+    p.early_weights = (a.mode == GEMM_W4A4 && pdl_enabled()) ? 1 : 0;
 
     // operand A
     const __nv_bfloat16 *x = a.x;

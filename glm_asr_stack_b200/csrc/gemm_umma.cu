@@ -136,7 +136,12 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                 // set-up above touched no global memory; everything below may
+    // Set-up above touched no global memory.  Everything below may, so every warp waits for the preceding
+    // kernels here -- except the producer, which first starts the WEIGHT loads of its first stages (weights
+    // and their re-tiled scales are written by no kernel of a chain; p.early_weights is cleared by the host
+    // when that is not true) and waits before its first activation load.
+    const bool early_b = MODE != GEMM_W4A16 && p.early_weights != 0;
+    if (warp != 0 || !early_b) pdl_wait();
     const long long t_setup = ((p.debug & 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
 
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
@@ -153,6 +158,48 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
         const bool leader = elect_one();
         uint32_t it = 0, raw_it = 0;
         bool ok = true;
+        // weight tiles (and their scales) of stage `s` for K block kb of a tile
+        auto load_weights = [&](int s, int kb, const SubTile (&st)[NB], const uint8_t *const (&sfb_src)[NB]) {
+            const uint32_t sb = stage_base(s);
+            const int kx = MODE == GEMM_W4A4 ? kb * 128 : kb * 64;
+#pragma unroll
+            for (int h = 0; h < NB; ++h)
+                tma_load_2d(sb + C::A_BYTES + h * C::SUB_BYTES, &p.tm_b[st[h].seg], full_bar(s), kx, st[h].row0);
+            if (MODE == GEMM_W4A4 && !(p.debug & 2)) {
+                const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
+#pragma unroll
+                for (int h = 0; h < NB; ++h)
+                    bulk_load_1d(sf + (1 + h) * C::SF_TILE, sfb_src[h] + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
+            }
+        };
+        int preloaded = 0;          // stages of the first work item whose weight loads were issued before the wait
+        if (early_b) {
+            if ((int)blockIdx.x < total_work) {
+                const int tile = (int)blockIdx.x / S, split = (int)blockIdx.x - tile * S;
+                const int kb0 = split * nkb / S, kb1 = (split + 1) * nkb / S;
+                const int n_tile = tile / p.num_m_tiles;
+                SubTile st[NB];
+                const uint8_t *sfb_src[NB];
+#pragma unroll
+                for (int h = 0; h < NB; ++h) {
+                    st[h] = resolve_subtile(p, n_tile, h, NB);
+                    sfb_src[h] = nullptr;
+                    if constexpr (MODE == GEMM_W4A4) {
+                        const int rt = st[h].ncols > 0 ? (st[h].row0 >> 7) : 0;
+                        sfb_src[h] = p.sfb[st[h].seg] + (size_t)rt * p.sf_k_chunks * C::SF_CHUNK;
+                    }
+                }
+                preloaded = kb1 - kb0 < C::STAGES ? kb1 - kb0 : C::STAGES;
+                if (p.debug & 8) preloaded = 0;
+                for (int i = 0; i < preloaded; ++i) {
+                    if (leader) {
+                        mbar_expect_tx(full_bar(i), (p.debug & 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
+                        load_weights(i, kb0 + i, st, sfb_src);
+                    }
+                }
+            }
+            pdl_wait();
+        }
         for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
             const int tile = work / S, split = work - tile * S;
             const int kb0 = split * nkb / S, kb1 = (split + 1) * nkb / S;
@@ -204,20 +251,17 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                 const uint32_t sb = stage_base(s);
                 // innermost coordinate in elements of the tensor map: bytes for packed e2m1, bf16 otherwise
                 const int kx = MODE == GEMM_W4A4 ? kb * 128 : kb * 64;
+                // the first stages of the first work item already have their byte count announced and their
+                // weights on the way
+                const bool have_weights = work == (int)blockIdx.x && kb - kb0 < preloaded;
                 if (leader) {
-                    mbar_expect_tx(full_bar(s), (p.debug & 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
+                    if (!have_weights)
+                        mbar_expect_tx(full_bar(s), (p.debug & 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
                     tma_load_2d(sb, &p.tm_a, full_bar(s), kx, m_tile * 128);
+                    if (MODE == GEMM_W4A4 && !(p.debug & 2))
+                        bulk_load_1d(sb + C::A_BYTES + C::B_BYTES, sfa_src + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
                     if constexpr (MODE != GEMM_W4A16) {
-#pragma unroll
-                        for (int h = 0; h < NB; ++h)
-                            tma_load_2d(sb + C::A_BYTES + h * C::SUB_BYTES, &p.tm_b[st[h].seg], full_bar(s), kx, st[h].row0);
-                    }
-                    if (MODE == GEMM_W4A4 && !(p.debug & 2)) {
-                        const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
-                        bulk_load_1d(sf, sfa_src + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
-#pragma unroll
-                        for (int h = 0; h < NB; ++h)
-                            bulk_load_1d(sf + (1 + h) * C::SF_TILE, sfb_src[h] + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
+                        if (!have_weights) load_weights(s, kb, st, sfb_src);
                     }
                 }
                 ++it;

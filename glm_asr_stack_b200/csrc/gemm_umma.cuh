@@ -56,6 +56,9 @@ struct alignas(64) GemmParams {
     // Each writes its raw fp32 partial to `partial`; the CTA that finishes last (per-tile counter) adds
     // the partials in split order and runs the epilogue, so the result does not depend on arrival order
     // and no CTA ever waits for another.  split_k <= 1: off.
+    // 1: weights and their scales are not written by any kernel still running when this one starts, so the
+    // producer may load them before it waits for the preceding kernels (programmatic dependent launch)
+    int early_weights;
     int split_k;
     float *partial;                     // [tiles][split_k][128 x BN] fp32, column-quad major
     int *tile_counters;                 // [tiles], zero between launches (the last CTA resets its tile's)
