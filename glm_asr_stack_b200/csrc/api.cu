@@ -607,7 +607,14 @@ static int run_fused(const FusedArgs &a) {
         }
     }
 
-    if (a.q_out != nullptr) return -1;      // the quantising epilogue exists in the pair kernel only
+    if (a.q_out != nullptr) {               // quantising SiLU-gate epilogue of the single-CTA kernel (two sub-tiles per tile)
+        if (a.epi != EPI_SILU_GATE || (p.seg_rows[0] % 64) != 0 || !(a.q_out_input_scale > 0.0f)) return -1;
+        p.q_packed = a.q_out;
+        p.q_sf = a.q_out_sf;
+        p.q_inv_in = 1.0f / a.q_out_input_scale;
+        p.q_ld = p.seg_rows[0] / 2;
+        p.q_sf_chunks = p.seg_rows[0] / 64;
+    }
 
     // tile shape: two weight sub-tiles per CTA tile when that still fills the machine
     int nb;
@@ -673,8 +680,10 @@ size_t tiled_scale_bytes(int rows, int K) { return tiled_sf_bytes(rows, K); }
 // a producer kernel of this library.  Tensor-core path only; -1 when the shape cannot take it.
 int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
                                  const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
-                                 const uint16_t *residual, int M, int K) {
-    if (out == nullptr || xq == nullptr || xq_sf == nullptr || weights == nullptr || !(input_scale > 0.0f)) return -1;
+                                 const uint16_t *residual, int M, int K, uint8_t *q_out, uint8_t *q_out_sf,
+                                 float q_out_input_scale) {
+    if ((out == nullptr && q_out == nullptr) || xq == nullptr || xq_sf == nullptr || weights == nullptr || !(input_scale > 0.0f))
+        return -1;
     for (int i = 0; i < num_weights && i < kMaxSegments; ++i)
         if (weights[i].w_scales == nullptr) return -1;
     FusedArgs a;
@@ -692,6 +701,9 @@ int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, cons
     a.residual = (const __nv_bfloat16 *)residual;
     a.M = M;
     a.K = K;
+    a.q_out = q_out;
+    a.q_out_sf = q_out_sf;
+    a.q_out_input_scale = q_out_input_scale;
     if (ldo < total_out_cols(a)) return -1;
     return run_fused(a);
 }

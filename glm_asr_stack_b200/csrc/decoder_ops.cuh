@@ -33,11 +33,14 @@ bool launch_paged_decode_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloa
                                    int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
                                    cudaStream_t st);
 // Flash-decoding variant (paged_attention.cu): cp.async-staged tiles + warp-level tensor-core MMA.
+// With q_packed / q_sf the result is written as the quantised operand of the next W4A4 GEMM (e2m1 bytes
+// [num_seqs, hidden / 2] + 128x4-tiled scales, quantiser input scale q_input_scale) instead of bf16 to out.
 bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *query, int ldq,
                                        const __nv_bfloat16 *key_cache, const __nv_bfloat16 *value_cache,
                                        const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
                                        int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
-                                       cudaStream_t st);
+                                       cudaStream_t st, uint8_t *q_packed = nullptr, uint8_t *q_sf = nullptr,
+                                       float q_input_scale = 0.0f);
 // Variable-length GQA self-attention of a prefill batch (prefill_attention.cu): sequence s owns rows
 // [seq_offsets[s], +seq_lens[s]) of q / k / v / out (device arrays; seq_lens == NULL: seq_offsets is a
 // cumulative table of num_seqs + 1 entries); head_dim 128.

@@ -31,7 +31,8 @@
 namespace glmasr {
 int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
                                  const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
-                                 const uint16_t *residual, int M, int K);   // api.cu
+                                 const uint16_t *residual, int M, int K, uint8_t *q_out = nullptr,
+                                 uint8_t *q_out_sf = nullptr, float q_out_input_scale = 0.0f);   // api.cu
 
 struct ProjRef {
     int dtype = -1;                     // GLMASR_DTYPE_UINT8 (FP4) or GLMASR_DTYPE_BF16
@@ -205,7 +206,8 @@ static bool fused_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, const
 // norm and the projections separately.
 static bool norm_then_fused_proj_w4a4(uint16_t *out, int ldo, const uint16_t *x, const uint16_t *norm_w, float eps,
                                       const ProjRef *const *ps, int n, int epi, int M, int H, uint8_t *xq, uint8_t *xsf,
-                                      cudaStream_t st) {
+                                      cudaStream_t st, uint8_t *q_out = nullptr, uint8_t *q_out_sf = nullptr,
+                                      float q_out_scale = 0.0f) {
     if (!prefer_w4a4() || (H % 256) != 0) return false;
     glmasr_fp4_weight w[3];
     for (int i = 0; i < n; ++i) {
@@ -219,9 +221,33 @@ static bool norm_then_fused_proj_w4a4(uint16_t *out, int ldo, const uint16_t *x,
                               M, H, st))
         return false;
     note_launches(1);
-    const int rc = fp4_linear_w4a4_prequantized(out, ldo, xq, xsf, w, n, ps[0]->input_scale, epi, nullptr, M, H);
+    const int rc = fp4_linear_w4a4_prequantized(out, ldo, xq, xsf, w, n, ps[0]->input_scale, epi, nullptr, M, H, q_out,
+                                                q_out_sf, q_out_scale);
     GLMASR_CHECK(rc == 0, "decoder projection on a quantised norm output failed (M=%d H=%d)", M, H);
     return true;
+}
+
+static bool attn_scalar_forced() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_ATTN_SCALAR");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+// A projection that can take an activation quantised by its producer kernel (W4A4, plain FP4 weight).
+static bool takes_quantised_input(const ProjRef &p) {
+    return prefer_w4a4() && p.dtype == GLMASR_DTYPE_UINT8 && p.pre == nullptr && p.scales != nullptr && p.input_scale > 0.0f &&
+           (p.K % 256) == 0;
+}
+
+static void single_proj_prequantized(uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xsf, const ProjRef &p, int M,
+                                     const uint16_t *residual) {
+    const glmasr_fp4_weight w = as_weight(p);
+    const int rc = fp4_linear_w4a4_prequantized(out, ldo, xq, xsf, &w, 1, p.input_scale,
+                                                residual ? GLMASR_EPI_RESIDUAL : GLMASR_EPI_STORE, residual, M, p.K);
+    GLMASR_CHECK(rc == 0, "decoder projection on a quantised input failed (N=%d K=%d M=%d)", p.N, p.K, M);
 }
 
 }  // namespace glmasr
@@ -232,6 +258,9 @@ enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
     WS_D_HID = 13, WS_D_NORM = 14, WS_D_QKV = 15, WS_D_ATTN = 16, WS_D_ACT = 17, WS_D_SLOT = 18, WS_D_LENS = 19,
     WS_D_BT = 20, WS_D_ROWS = 21, WS_D_PTRS = 22, WS_D_SCRATCH = 23, WS_D_XQ = 26, WS_D_XSF = 27,
     WS_D_POS = 28, WS_D_OFFS = 29,
+    // 30, 31: api.cu (split-K).  Quantised hand-overs of the decode step share the layer path's slots 24, 25
+    // (both are temporaries of one call).
+    WS_D_AQ = 24, WS_D_ASF = 25,
 };
 
 // ============================================================================================
@@ -362,6 +391,10 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     uint16_t *scratch = (uint16_t *)workspace_slot(WS_D_SCRATCH, (size_t)M * (F > H ? F : H) * 2);
     uint8_t *nq = (uint8_t *)workspace_slot(WS_D_XQ, (size_t)M * H / 2);
     uint8_t *nsf = (uint8_t *)workspace_slot(WS_D_XSF, tiled_scale_bytes(M, H));
+    // quantised attention output (K = H) and SiLU-gate output (K = F) handed to the o / down projections
+    const int KQ = F > H ? F : H;
+    uint8_t *aq = (uint8_t *)workspace_slot(WS_D_AQ, (size_t)M * KQ / 2);
+    uint8_t *asf = (uint8_t *)workspace_slot(WS_D_ASF, tiled_scale_bytes(M, KQ));
 
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_total, h_total.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
@@ -404,16 +437,32 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
                                      (const __nv_bfloat16 *)qkv + H + KV, NQKV, d_slot, M, KVH, HD, pool->block_size, st);
             glue += 3;
         }
-        const bool ok = launch_paged_decode_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV, k_base,
-                                                      v_base, d_bt, d_total, M, QH, KVH, HD, pool->block_size,
-                                                      pool->max_blocks_per_seq, st);
-        GLMASR_CHECK(ok, "decoder_decode_step_batched: unsupported attention shape");
-
-        // o + residual -> hid (residual is the pre-norm hidden state)
-        single_proj(hid, H, att, H, R.o, M, hid, scratch);
+        // attention writes the o projection's quantised operand itself when that projection runs in W4A4
+        const bool o_q = takes_quantised_input(R.o) && R.o.K == H && !attn_scalar_forced();
+        bool ok = false;
+        if (o_q)
+            ok = launch_paged_decode_attention_mma((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV, k_base, v_base, d_bt,
+                                                   d_total, M, QH, KVH, HD, pool->block_size, pool->max_blocks_per_seq, st, aq,
+                                                   asf, R.o.input_scale);
+        if (ok) {
+            single_proj_prequantized(hid, H, aq, asf, R.o, M, hid);
+        } else {
+            ok = launch_paged_decode_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV, k_base, v_base, d_bt,
+                                               d_total, M, QH, KVH, HD, pool->block_size, pool->max_blocks_per_seq, st);
+            GLMASR_CHECK(ok, "decoder_decode_step_batched: unsupported attention shape");
+            // o + residual -> hid (residual is the pre-norm hidden state)
+            single_proj(hid, H, att, H, R.o, M, hid, scratch);
+        }
 
         const ProjRef *gu_p[2] = {&R.gate, &R.up};
-        if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
+        // gate|up's SiLU-gate epilogue quantises for the down projection when that one runs in W4A4
+        const bool down_q = takes_quantised_input(R.down) && R.down.K == F && (F % 64) == 0;
+        bool down_done = false;
+        if (down_q && norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st, aq,
+                                                asf, R.down.input_scale)) {
+            single_proj_prequantized(hid, H, aq, asf, R.down, M, hid);
+            down_done = true;
+        } else if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
             // done
         } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st),
                    ++glue, !fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
@@ -421,7 +470,7 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
             single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
             silu_elementwise_mul(act, act + (size_t)M * F, M * F);
         }
-        single_proj(hid, H, act, F, R.down, M, hid, scratch);
+        if (!down_done) single_proj(hid, H, act, F, R.down, M, hid, scratch);
         note_launches(glue + 1);   // norms, RoPE / cache write, attention (the projections count themselves)
     }
 

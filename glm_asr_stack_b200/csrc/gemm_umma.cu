@@ -439,6 +439,25 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                         }
                         const int c0 = half * GC + ch * 32;
                         const int nvalid = sg.ncols - c0;
+                        if (p.q_packed != nullptr) {
+                            // the next GEMM's operand: quantise the bf16-rounded products in 16-column blocks
+                            uint32_t q[4], sf = 0;
+#pragma unroll
+                            for (int b = 0; b < 2; ++b) {
+                                float blk[16];
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) blk[j] = bf16_round(v[16 * b + j]);
+                                sf |= quantize_block16(blk, p.q_inv_in, q[2 * b], q[2 * b + 1]) << (8 * b);
+                            }
+                            if (row_ok && nvalid >= 32) {
+                                const int col = sg.col0 + c0;
+                                *reinterpret_cast<uint4 *>(p.q_packed + (size_t)row * p.q_ld + (col >> 1)) = make_uint4(q[0], q[1], q[2], q[3]);
+                                uint8_t *sfp = p.q_sf + ((size_t)m_tile * p.q_sf_chunks + (col >> 6)) * 512 + lane * 16 + quad * 4 +
+                                               ((col >> 4) & 3);
+                                *reinterpret_cast<uint16_t *>(sfp) = (uint16_t)sf;
+                            }
+                            return;
+                        }
                         if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
                     };
                     if (from_partials) {

@@ -20,6 +20,7 @@
 #include <stdint.h>
 
 #include "decoder_ops.cuh"
+#include "fp4_format.cuh"
 #include "runtime.cuh"
 
 namespace glmasr {
@@ -70,7 +71,8 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
     __nv_bfloat16 *__restrict__ out, int ldo, const __nv_bfloat16 *__restrict__ query, int ldq,
     const __nv_bfloat16 *__restrict__ key_cache, const __nv_bfloat16 *__restrict__ value_cache,
     const int *__restrict__ block_tables, const int *__restrict__ seq_lens, int num_kv_heads, int group,
-    int block_size, int max_blocks_per_seq, float scale) {
+    int block_size, int max_blocks_per_seq, float scale, uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf,
+    int q_sf_chunks, float q_inv_in) {
     extern __shared__ __align__(1024) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -84,6 +86,16 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
     const int q_head0 = kv_head * group;
 
     if (seq_len <= 0) {                 // reference: zeros
+        if (q_packed != nullptr) {      // zeros quantise to zero codes and zero scales
+            const int hidden = num_kv_heads * group * 128;
+            for (int i = threadIdx.x; i < group * 64; i += blockDim.x)
+                q_packed[(size_t)seq * (hidden / 2) + (size_t)q_head0 * 64 + i] = 0;
+            for (int b = threadIdx.x; b < group * 8; b += blockDim.x) {
+                const int kb = q_head0 * 8 + b, rem = seq & 127;
+                q_sf[((((size_t)(seq >> 7) * q_sf_chunks + (kb >> 2)) * 32 + (rem & 31)) * 4 + (rem >> 5)) * 4 + (kb & 3)] = 0;
+            }
+            return;
+        }
         for (int i = threadIdx.x; i < group * 128; i += blockDim.x)
             out[(size_t)seq * ldo + (size_t)q_head0 * 128 + i] = __float2bfloat16(0.0f);
         return;
@@ -238,6 +250,39 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
         }
     }
     __syncthreads();
+    if (q_packed != nullptr) {
+        // the o projection's operand directly: 16-element blocks of the bf16-rounded result through the
+        // activation quantiser (same bytes as the bf16 output followed by the stand-alone quantiser)
+        const int hidden = num_kv_heads * group * 128;
+        for (int task = threadIdx.x; task < group * 8; task += blockDim.x) {
+            const int h = task >> 3, b = task & 7;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) m = fmaxf(m, part[((size_t)w * 8 + h) * kPart]);
+            float e[kWarps], den = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float *pw = part + ((size_t)w * 8 + h) * kPart;
+                e[w] = (pw[0] == -INFINITY) ? 0.0f : __expf(pw[0] - m);
+                den += e[w] * pw[1];
+            }
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                float num = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) num += e[w] * part[((size_t)w * 8 + h) * kPart + 2 + b * 16 + j];
+                v[j] = __bfloat162float(__float2bfloat16(num / (den + 1e-9f)));
+            }
+            uint32_t lo, hi;
+            const uint32_t sf = quantize_block16(v, q_inv_in, lo, hi);
+            const int col = (q_head0 + h) * 128 + b * 16;
+            *reinterpret_cast<uint2 *>(q_packed + (size_t)seq * (hidden / 2) + (col >> 1)) = make_uint2(lo, hi);
+            const int kb = col >> 4, rem = seq & 127;
+            q_sf[((((size_t)(seq >> 7) * q_sf_chunks + (kb >> 2)) * 32 + (rem & 31)) * 4 + (rem >> 5)) * 4 + (kb & 3)] = (uint8_t)sf;
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < group * 128; idx += blockDim.x) {
         const int h = idx >> 7, d = idx & 127;
         float m = -INFINITY;
@@ -259,12 +304,15 @@ bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_b
                                        const __nv_bfloat16 *key_cache, const __nv_bfloat16 *value_cache,
                                        const int *block_tables, const int *seq_lens, int num_seqs, int num_q_heads,
                                        int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
-                                       cudaStream_t st) {
+                                       cudaStream_t st, uint8_t *q_packed, uint8_t *q_sf, float q_input_scale) {
     if (head_dim != 128 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return false;
     const int group = num_q_heads / num_kv_heads;
     if (group > 8 || (ldq % 2) != 0) return false;
     if ((((uintptr_t)key_cache | (uintptr_t)value_cache) & 15) != 0 || (((uintptr_t)query) & 3) != 0) return false;
     if (num_seqs <= 0) return true;
+    if (q_packed != nullptr && (q_sf == nullptr || !(q_input_scale > 0.0f) || (((uintptr_t)q_packed) & 7) != 0)) return false;
+    const int q_sf_chunks = num_q_heads * head_dim / 64;
+    const float q_inv_in = q_packed != nullptr ? 1.0f / q_input_scale : 0.0f;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(paged_decode_attention_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -281,11 +329,11 @@ bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_b
     if (block_size % kTile == 0)
         launch_chained(paged_decode_attention_mma_kernel<true>, grid, dim3(kWarps * 32), (size_t)kAttnSmem, st, out, ldo, query,
                        ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
-                       max_blocks_per_seq, scale);
+                       max_blocks_per_seq, scale, q_packed, q_sf, q_sf_chunks, q_inv_in);
     else
         launch_chained(paged_decode_attention_mma_kernel<false>, grid, dim3(kWarps * 32), (size_t)kAttnSmem, st, out, ldo, query,
                        ldq, key_cache, value_cache, block_tables, seq_lens, num_kv_heads, group, block_size,
-                       max_blocks_per_seq, scale);
+                       max_blocks_per_seq, scale, q_packed, q_sf, q_sf_chunks, q_inv_in);
     return true;
 }
 
