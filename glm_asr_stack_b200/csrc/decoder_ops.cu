@@ -122,6 +122,16 @@ void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int
 // so every value is bit-equal to the three separate kernels.  The rotated k is also written back
 // in place, as the separate kernels leave it.
 // --------------------------------------------------------------------------------------------
+// 1 / 10000^(2 d / head_dim) for d < head_dim / 2, computed once per head_dim on the device with the
+// reference's own float expression (so that every later use has the same bits as computing it in place)
+static __device__ float g_inv_freq[512];
+static int g_inv_freq_dim = 0;
+
+__global__ void rope_inv_freq_kernel(int head_dim) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d < head_dim / 2) g_inv_freq[d] = 1.0f / powf(10000.0f, (2.0f * d) / head_dim);
+}
+
 __global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *__restrict__ positions,
                                      const int64_t *__restrict__ slot_mapping, __nv_bfloat16 *__restrict__ key_cache,
                                      __nv_bfloat16 *__restrict__ value_cache, int q_heads, int kv_heads, int head_dim) {
@@ -132,8 +142,7 @@ __global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int 
     const int half_dim = head_dim / 2;
     const int pos = positions[seq];
     for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
-        const float inv_freq = 1.0f / powf(10000.0f, (2.0f * d) / head_dim);
-        const float theta = pos * inv_freq;
+        const float theta = pos * g_inv_freq[d];
         cs[d] = cosf(theta);
         cs[half_dim + d] = sinf(theta);
     }
@@ -143,22 +152,43 @@ __global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int 
     const size_t row_elems = (size_t)kv_heads * head_dim;
     __nv_bfloat16 *kdst = key_cache + (size_t)slot * row_elems;
     __nv_bfloat16 *vdst = value_cache + (size_t)slot * row_elems;
-    const int q_pairs = q_heads * half_dim, k_pairs = kv_heads * half_dim;
-    for (int i = threadIdx.x; i < q_pairs + k_pairs; i += blockDim.x) {
-        const bool is_k = i >= q_pairs;
-        const int j = is_k ? i - q_pairs : i;
-        const int head = j / half_dim, d = j % half_dim;
+    // one task = 8 consecutive dims d of one head and their partners d + half_dim: two 16-byte loads,
+    // eight rotations, two 16-byte stores (and two more into the cache for a k head)
+    const int cpt = half_dim / 8;
+    const int tasks = (q_heads + kv_heads) * cpt;
+    for (int t = threadIdx.x; t < tasks; t += blockDim.x) {
+        const int head_all = t / cpt, c = t - head_all * cpt;
+        const bool is_k = head_all >= q_heads;
+        const int head = is_k ? head_all - q_heads : head_all;
         __nv_bfloat16 *base = row + (is_k ? k_col : 0) + head * head_dim;
-        const float v0 = __bfloat162float(base[d]);
-        const float v1 = __bfloat162float(base[d + half_dim]);
-        const float cos_t = cs[d], sin_t = cs[half_dim + d];
-        const __nv_bfloat16 r0 = __float2bfloat16(v0 * cos_t - v1 * sin_t);
-        const __nv_bfloat16 r1 = __float2bfloat16(v0 * sin_t + v1 * cos_t);
-        base[d] = r0;
-        base[d + half_dim] = r1;
+        const uint4 lo4 = *reinterpret_cast<const uint4 *>(base + 8 * c);
+        const uint4 hi4 = *reinterpret_cast<const uint4 *>(base + half_dim + 8 * c);
+        const uint32_t lo[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+        uint32_t o_lo[4], o_hi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float r0[2], r1[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int d = 8 * c + 2 * j + e;
+                const float v0 = __uint_as_float(e ? (lo[j] & 0xFFFF0000u) : (lo[j] << 16));
+                const float v1 = __uint_as_float(e ? (hi[j] & 0xFFFF0000u) : (hi[j] << 16));
+                const float cos_t = cs[d], sin_t = cs[half_dim + d];
+                r0[e] = v0 * cos_t - v1 * sin_t;
+                r1[e] = v0 * sin_t + v1 * cos_t;
+            }
+            const __nv_bfloat162 a = __floats2bfloat162_rn(r0[0], r0[1]);
+            const __nv_bfloat162 b = __floats2bfloat162_rn(r1[0], r1[1]);
+            o_lo[j] = *reinterpret_cast<const uint32_t *>(&a);
+            o_hi[j] = *reinterpret_cast<const uint32_t *>(&b);
+        }
+        const uint4 out_lo = make_uint4(o_lo[0], o_lo[1], o_lo[2], o_lo[3]);
+        const uint4 out_hi = make_uint4(o_hi[0], o_hi[1], o_hi[2], o_hi[3]);
+        *reinterpret_cast<uint4 *>(base + 8 * c) = out_lo;
+        *reinterpret_cast<uint4 *>(base + half_dim + 8 * c) = out_hi;
         if (is_k) {
-            kdst[head * head_dim + d] = r0;
-            kdst[head * head_dim + d + half_dim] = r1;
+            *reinterpret_cast<uint4 *>(kdst + head * head_dim + 8 * c) = out_lo;
+            *reinterpret_cast<uint4 *>(kdst + head * head_dim + half_dim + 8 * c) = out_hi;
         }
     }
     // V row: 16 bytes per thread (the launcher checks the alignment)
@@ -172,9 +202,14 @@ bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, cons
                           int q_heads, int kv_heads, int head_dim, cudaStream_t st) {
     const int row_elems = kv_heads * head_dim;
     if (num_seqs <= 0) return true;
-    if ((head_dim % 2) != 0 || (row_elems % 8) != 0 || (ld % 8) != 0 || (v_col % 8) != 0 ||
-        (((uintptr_t)qkv | (uintptr_t)value_cache) & 15) != 0)
+    if ((head_dim % 16) != 0 || head_dim > 1024 || (row_elems % 8) != 0 || (ld % 8) != 0 || (v_col % 8) != 0 || (k_col % 8) != 0 ||
+        (((uintptr_t)qkv | (uintptr_t)value_cache | (uintptr_t)key_cache) & 15) != 0)
         return false;
+    if (g_inv_freq_dim != head_dim) {
+        // ordinary launch: it completes before the kernels behind it start
+        rope_inv_freq_kernel<<<(head_dim / 2 + 127) / 128, 128, 0, st>>>(head_dim);
+        g_inv_freq_dim = head_dim;
+    }
     GLMASR_PREFER_MAX_SMEM(rope_qk_cache_kernel);
     launch_chained(rope_qk_cache_kernel, dim3(num_seqs), dim3(256), (size_t)head_dim * sizeof(float), st, qkv, ld, k_col, v_col, positions, slot_mapping,
                                                                              key_cache, value_cache, q_heads, kv_heads,

@@ -154,16 +154,19 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 const uint32_t sb = stage_base(s);
                 const uint32_t fb = full0 + 8u * (uint32_t)s;
                 const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
+                const bool no_sf = (p.debug & 2) != 0;      // timing experiment: no scale-factor traffic (wrong results)
                 if (leader_lane) {
                     if (do_a) {
-                        if (rank == 0) mbar_expect_tx(full_bar(s), C::TX_BYTES_PAIR);
+                        if (rank == 0) mbar_expect_tx(full_bar(s), no_sf ? 2u * (C::A_BYTES + C::B_BYTES) : C::TX_BYTES_PAIR);
                         tma_load_2d_pair(sb, &p.tm_a, fb, kb * 128, m_tile * 128);
-                        tma_load_2d_pair(sf, &p.tm_sfa, fb, 0, sfa_row + kb * 4);
+                        if (!no_sf) tma_load_2d_pair(sf, &p.tm_sfa, fb, 0, sfa_row + kb * 4);
                     }
                     if (do_b) {
                         tma_load_2d_pair(sb + C::A_BYTES, &p.tm_b[mine.seg], fb, kb * 128, mine.row0);
-                        tma_load_2d_pair(sf + C::SF_TILE, &p.tm_sfb[st0.seg], fb, 0, sfb_row0 + kb * 4);
-                        tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
+                        if (!no_sf) {
+                            tma_load_2d_pair(sf + C::SF_TILE, &p.tm_sfb[st0.seg], fb, 0, sfb_row0 + kb * 4);
+                            tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
+                        }
                     }
                 }
                 ++it;
