@@ -28,6 +28,7 @@ static int *g_status = nullptr;
 static long long g_launches = 0;
 static int g_num_sms = 0;
 static bool g_umma_ready = false;
+static bool g_pair16_ready = false;
 static bool g_pair_ready = false;
 
 // optional per-launch timing of the GEMM kernel (CUDA events on the launching stream)
@@ -191,6 +192,16 @@ static int split_k_override() {
     return v;
 }
 
+// GLMASR_PAIR16=0: SiLU-gate epilogues stay on the eight-epilogue-warp pair kernel (comparison runs)
+static bool use_pair16_kernel() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_PAIR16");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 static bool force_simt() {
     static int v = -1;
     if (v < 0) {
@@ -246,10 +257,11 @@ static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
 static void clear_tmap_cache() { g_tmaps.clear(); }
 
 static bool make_tmap(CUtensorMap *tm, const void *base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner,
-                      uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+                      uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128,
+                      bool swizzle64 = false) {
     if (((uintptr_t)base & 15) != 0 || (pitch_bytes & 15) != 0) return false;
     (void)elem_bytes;
-    const TmapKey key = {base, inner, rows, pitch_bytes, box_inner, box_rows, (int)dt, swizzle128 ? 1 : 0};
+    const TmapKey key = {base, inner, rows, pitch_bytes, box_inner, box_rows, (int)dt, swizzle128 ? 1 : (swizzle64 ? 2 : 0)};
     auto it = g_tmaps.find(key);
     if (it != g_tmaps.end()) {
         *tm = it->second;
@@ -261,7 +273,8 @@ static bool make_tmap(CUtensorMap *tm, const void *base, CUtensorMapDataType dt,
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode_fn()(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                              : (swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return false;
     if (g_tmaps.size() > 16384) g_tmaps.clear();
@@ -573,9 +586,13 @@ static int run_fused(const FusedArgs &a) {
             bool tma_ok = aligned16(a.out) && (a.ldo % 8) == 0 && !no_tma_store();
             for (int i = 0; i < p.num_segs && a.epi != EPI_SILU_GATE; ++i)
                 if (i + 1 < p.num_segs && (p.seg_rows[i] % 8) != 0) tma_ok = false;   // segment column offsets stay 16-byte aligned
-            if (tma_ok)
-                tma_ok = make_tmap(&p.tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.n_out, (uint64_t)a.M,
-                                   (uint64_t)a.ldo * 2, 64, 32, true);
+            // SiLU-gate epilogues run on the sixteen-epilogue-warp variant (32 x 32 output boxes)
+            const bool wide = a.epi == EPI_SILU_GATE && use_pair16_kernel();
+            if (tma_ok && a.q_out == nullptr)
+                tma_ok = wide ? make_tmap(&p.tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.n_out, (uint64_t)a.M,
+                                          (uint64_t)a.ldo * 2, 32, 32, false, true)
+                              : make_tmap(&p.tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.n_out, (uint64_t)a.M,
+                                          (uint64_t)a.ldo * 2, 64, 32, true);
             p.tma_store = tma_ok ? 1 : 0;
             if (a.q_out != nullptr) {
                 if (a.epi != EPI_SILU_GATE || (p.seg_rows[0] % 64) != 0 || !(a.q_out_input_scale > 0.0f)) return -1;
@@ -597,7 +614,15 @@ static int run_fused(const FusedArgs &a) {
                 if (a.q_out != nullptr) tl.bytes -= (2.0 - 0.5625) * a.M * p.n_out;   // e2m1 + scales instead of bf16
                 cudaEventRecord(tl.start, g_stream);
             }
-            if (launch_umma_gemm_pair(p, pairs, g_stream) != cudaSuccess) return -1;
+            if (wide) {
+                if (!g_pair16_ready) {
+                    GLMASR_CUDA_CHECK(umma_gemm_pair16_init());
+                    g_pair16_ready = true;
+                }
+                if (launch_umma_gemm_pair16(p, pairs, g_stream) != cudaSuccess) return -1;
+            } else if (launch_umma_gemm_pair(p, pairs, g_stream) != cudaSuccess) {
+                return -1;
+            }
             ++g_launches;
             if (g_profile) {
                 cudaEventRecord(tl.stop, g_stream);
