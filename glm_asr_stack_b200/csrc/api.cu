@@ -601,6 +601,12 @@ static int run_fused(const FusedArgs &a) {
                 p.q_inv_in = 1.0f / a.q_out_input_scale;
                 p.q_ld = p.seg_rows[0] / 2;
                 p.q_sf_chunks = p.seg_rows[0] / 64;
+                // the sixteen-warp variant stores the codes through TMA: [M, q_ld] bytes, 32-row x 16-byte boxes
+                p.tma_store = (wide && !no_tma_store() && aligned16(a.q_out) && (p.q_ld % 16) == 0 &&
+                               make_tmap(&p.tm_out, a.q_out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.q_ld, (uint64_t)a.M,
+                                         (uint64_t)p.q_ld, 16, 32, false))
+                                  ? 1
+                                  : 0;
             }
             TimedLaunch tl;
             if (g_profile) {

@@ -53,4 +53,36 @@ __device__ __forceinline__ uint32_t quantize_block16(const float (&v)[16], float
     return (uint32_t)s8.__x;
 }
 
+// Same block quantiser with the second division looked up: os = inv_in / float(s8) takes one of 127 values
+// per launch, so a kernel can fill os_table[s8] once (fill_os_table, IEEE divisions) and index it afterwards.
+// Same bytes as quantize_block16.
+__device__ __forceinline__ void fill_os_table(float *os_table, float inv_in, int tid, int nthreads) {
+    for (int b = tid; b < 128; b += nthreads) {
+        __nv_fp8_e4m3 s8;
+        s8.__x = (__nv_fp8_storage_t)b;
+        const float sr = (float)s8;
+        os_table[b] = (b != 0 && b != 0x7F && sr > 0.0f) ? __fdiv_rn(inv_in, sr) : 0.0f;
+    }
+}
+
+__device__ __forceinline__ uint32_t quantize_block16_lut(const float (&v)[16], float inv_in, const float *os_table, uint32_t &lo,
+                                                         uint32_t &hi) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const float scale = amax > 0.0f ? __fdiv_rn(inv_in * amax, 6.0f) : 0.0f;
+    const __nv_fp8_e4m3 s8(scale);
+    const uint32_t code = scale > 0.0f ? (uint32_t)s8.__x : 0u;      // scale == 0 -> os = 0 whatever the byte
+    const float os = os_table[code & 0x7Fu];
+    lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t q = __nv_cvt_float2_to_fp4x2(make_float2(v[2 * j] * os, v[2 * j + 1] * os), __NV_E2M1,
+                                                    cudaRoundNearest) & 0xFFu;
+        if (j < 4) lo |= q << (8 * j);
+        else hi |= q << (8 * (j - 4));
+    }
+    return (uint32_t)s8.__x;
+}
+
 }  // namespace glmasr

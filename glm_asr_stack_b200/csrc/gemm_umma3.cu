@@ -44,7 +44,7 @@ struct Pair16Cfg {
     static constexpr int SFA_COL = 448;
     static constexpr int SFB_COL = SFA_COL + 16;          // 464 .. 495
     static constexpr int TMEM_COLS = 512;
-    static constexpr int BAR_BYTES = 1024;
+    static constexpr int BAR_BYTES = 2048;                // barriers and flags (first KB), quantiser look-up table (second KB)
     static constexpr int OUT_STAGE_BYTES = 32 * 64;       // per epilogue warp: 32 rows x 32 bf16, 64B-swizzled
     static constexpr int SMEM_BYTES = 1024 + BAR_BYTES + STAGES * STAGE_BYTES + EPI_WARPS * OUT_STAGE_BYTES;
     static constexpr uint32_t TX_BYTES_PAIR = 2 * STAGE_BYTES;
@@ -101,6 +101,8 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
         tmem_alloc_pair(smem_u32((const void *)tmem_slot), C::TMEM_COLS);
         tmem_relinquish_pair();
     }
+    float *os_table = reinterpret_cast<float *>(smem_gen + 1024);
+    if (p.q_packed != nullptr) fill_os_table(os_table, p.q_inv_in, (int)threadIdx.x, (int)blockDim.x);
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();                                // both CTAs' barriers exist before any remote signal
@@ -278,10 +280,15 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
             }
             const int nvalid_w = sg.ncols - slice * 32;           // valid outputs of this warp
             const bool box_tma = p.tma_store && p.q_packed == nullptr && nvalid_w >= 32;
-            if (box_tma) {                       // the previous store of this warp must have finished reading the buffer
+            // quantised output: the warp's 32 rows x 16 bytes of codes also leave through a bulk tensor store (tm_out
+            // then describes the code matrix), because 32 scattered 16-byte stores per instruction cost more
+            // load/store-unit time than the whole quantiser
+            const bool q_tma = p.tma_store && p.q_packed != nullptr && nvalid_w >= 32;
+            if (box_tma || q_tma) {              // the previous store of this warp must have finished reading the buffer
                 if (store_leader) bulk_wait_read_all();
                 __syncwarp();
             }
+            uint32_t q_first_lo = 0, q_first_hi = 0, sf_first = 0;       // quantised first half, stored with the second
 #pragma unroll 1
             for (int it = 0; it < 2; ++it) {     // 16 outputs per pass
                 float g[16], u[16];
@@ -328,12 +335,31 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
                     // the next GEMM's operand: quantise the bf16-rounded products of this 16-column block
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = bf16_round(v[i]);
-                    uint32_t qlo, qhi;
-                    const uint32_t sf = quantize_block16(v, p.q_inv_in, qlo, qhi);
-                    if (row_ok && nvalid >= 16) {
-                        *reinterpret_cast<uint2 *>(p.q_packed + (size_t)row * p.q_ld + (col >> 1)) = make_uint2(qlo, qhi);
+                    uint32_t qlo, qhi, sf;
+                    if (p.debug & 8) {           // timing experiment: no quantiser arithmetic (wrong results)
+                        qlo = __float_as_uint(v[0]), qhi = __float_as_uint(v[9]), sf = __float_as_uint(v[3]) & 0x7Fu;
+                    } else {
+                        sf = quantize_block16_lut(v, p.q_inv_in, os_table, qlo, qhi);
+                    }
+                    if (it == 0) {
+                        q_first_lo = qlo, q_first_hi = qhi, sf_first = sf;
+                    } else if (q_tma) {
+                        sts128(out_stage + (uint32_t)lane * 16, make_uint4(q_first_lo, q_first_hi, qlo, qhi));
+                        if (row_ok && !(p.debug & (4 | 16))) {
+                            const int col0 = col - 16;
+                            uint8_t *sfp = p.q_sf + ((size_t)m_tile * p.q_sf_chunks + (col0 >> 6)) * 512 + lane * 16 + quad * 4 +
+                                           ((col0 >> 4) & 3);
+                            *reinterpret_cast<uint16_t *>(sfp) = (uint16_t)(sf_first | (sf << 8));
+                        }
+                    } else if (row_ok && nvalid >= 16 && !(p.debug & 4)) {
+                        // both halves at once: 16 bytes of codes and the two scale bytes of this warp's 32 outputs
+                        const int col0 = col - 16;
+                        *reinterpret_cast<uint4 *>(p.q_packed + (size_t)row * p.q_ld + (col0 >> 1)) =
+                            make_uint4(q_first_lo, q_first_hi, qlo, qhi);
                         // tiled scale layout: chunk (row tile, col / 64), byte (row % 32) * 16 + (row / 32 % 4) * 4 + block
-                        p.q_sf[((size_t)m_tile * p.q_sf_chunks + (col >> 6)) * 512 + lane * 16 + quad * 4 + ((col >> 4) & 3)] = (uint8_t)sf;
+                        uint8_t *sfp = p.q_sf + ((size_t)m_tile * p.q_sf_chunks + (col0 >> 6)) * 512 + lane * 16 + quad * 4 +
+                                       ((col0 >> 4) & 3);
+                        *reinterpret_cast<uint16_t *>(sfp) = (uint16_t)(sf_first | (sf << 8));
                     }
                     continue;
                 }
@@ -361,11 +387,13 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
                     }
                 }
             }
-            if (box_tma && !(p.debug & 4)) {
+            if ((box_tma || q_tma) && !(p.debug & 4)) {
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (store_leader) {
-                    tma_store_2d(&p.tm_out, out_stage, sg.col0 + slice * 32, m_tile * 128 + quad * 32);
+                    // bf16 output: x in elements of the [M, n_out] view; codes: x in bytes of the [M, q_ld] view
+                    const int x = q_tma ? ((sg.col0 + slice * 32) >> 1) : (sg.col0 + slice * 32);
+                    tma_store_2d(&p.tm_out, out_stage, x, m_tile * 128 + quad * 32);
                     bulk_commit_group();
                 }
             }
