@@ -52,6 +52,7 @@ struct LayerRef {
 struct ModelRefs {
     const glmasr_WeightStore *ws = nullptr;
     int count = -1;
+    uint64_t fingerprint = 0;
     std::vector<LayerRef> layers;
     const uint16_t *final_norm = nullptr;
 };
@@ -105,11 +106,26 @@ static ProjRef resolve_proj(const glmasr_WeightStore *ws, int layer, const char 
     return r;
 }
 
+// The table is cached per weight store.  The store's address alone is not an identity (a freed store's
+// address is reused by the next one), so the key also folds in every tensor's data pointer and size:
+// ~300 loads per call, nothing against a step's 200 launches.
+static uint64_t store_fingerprint(const glmasr_WeightStore *ws) {
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < ws->count; ++i) {
+        h = (h ^ (uint64_t)(uintptr_t)ws->tensors[i].data) * 1099511628211ull;
+        h = (h ^ (uint64_t)ws->tensors[i].nbytes) * 1099511628211ull;
+    }
+    return h;
+}
+
 static const ModelRefs &model_refs(const glmasr_WeightStore *ws, int num_layers) {
-    if (g_refs.ws == ws && g_refs.count == ws->count && (int)g_refs.layers.size() == num_layers) return g_refs;
+    const uint64_t fp = store_fingerprint(ws);
+    if (g_refs.ws == ws && g_refs.count == ws->count && g_refs.fingerprint == fp && (int)g_refs.layers.size() == num_layers)
+        return g_refs;
     g_refs = ModelRefs();
     g_refs.ws = ws;
     g_refs.count = ws->count;
+    g_refs.fingerprint = fp;
     g_refs.layers.resize(num_layers);
     char name[256];
     for (int l = 0; l < num_layers; ++l) {

@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from . import _lib
+from . import _lib, ops
 from .weights import DTYPE_BF16, DTYPE_FP32, DTYPE_FP8, DTYPE_UINT8
 
 MAX_DIMS = 4
@@ -60,8 +60,19 @@ class WeightStore:
         self.c = CWeightStore()
         self.c.count = 0
         self.keep: Dict[str, torch.Tensor] = {}
+        self._forget_cached_table()
+
+    @staticmethod
+    def _forget_cached_table():
+        # The library keeps a per-store table of pointers and of the scalar tensors' VALUES
+        # (weight_scale_2, input_scale: read once, as the reference's decoder_scalar_read_cached does).
+        # A new store can reuse a freed store's address, and its tensors the old tensors' addresses, with
+        # different contents, so the table is dropped whenever a store is created or changed
+        # (the C host calls glmasr_decoder_forget_weights from safetensors_free).
+        _lib.load().glmasr_decoder_forget_weights()
 
     def add(self, name: str, t: torch.Tensor, dtype: Optional[int] = None):
+        self._forget_cached_table()
         i = self.c.count
         assert i < MAX_WEIGHTS
         self.keep[name] = t
@@ -78,6 +89,9 @@ class WeightStore:
     def add_fp4(self, prefix: str, w, input_scale: Optional[float] = None):
         """The five tensors of one FP4 projection under the checkpoint's names."""
         dev = w.w_packed.device
+        # the library caches re-tiled scales by device pointer: drop the entry when this tensor goes away
+        # (what the C host does from safetensors_free), or a later weight at the same address would inherit it
+        ops._track_scales(w.w_scales)
         self.add(f"{prefix}.weight", w.w_packed)
         self.add(f"{prefix}.weight_scale", w.w_scales, DTYPE_FP8)
         self.add(f"{prefix}.weight_scale_2", torch.tensor([w.w_global_scale], dtype=torch.float32, device=dev))

@@ -368,6 +368,10 @@ def run_prefill_case(w4a4: bool):
         mask = np.ones(num_blocks * bs, bool)
         mask[slots] = False
         assert not kd[mask].any()                       # rows of no token stay untouched
+        if o.rel_err(kd[slots], kc[l][slots]) > kv_tol:    # name the rows before failing
+            bad = [i for i in range(T) if o.rel_err(kd[slots[i]][None], kc[l][slots[i]][None]) > 5e-2]
+            zero = [i for i in bad if not kd[slots[i]].any()]
+            print(f"K cache layer {l}: bad token rows {bad} all-zero {zero}")
         assert o.rel_err(kd[slots], kc[l][slots]) <= kv_tol
         assert o.rel_err(bits_of(pool.v[l].reshape(num_blocks * bs, -1))[slots], vc[l][slots]) <= kv_tol
     # one decode step on top of that cache: compare with the oracle continuing from the device's cache
