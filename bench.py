@@ -404,10 +404,10 @@ def main():
     else:
         peak, peak_src = 1590.0, "fallback bf16 burst"
     # DRAM bytes of one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one
-    # `ncu --set full` capture of this workload's gate|up launch at M = 10000, W4A4: 25.96 MB read + 1.01 MB
+    # `ncu --set full` capture of this workload's gate|up launch at M = 10000, W4A4: 25.78 MB read + 0.58 MB
     # written; the quantised output stays in L2).  Not captured for other modes or row counts.
-    traffic = 26.97e6 if (args.mode == "w4a4" and M == M_TOKENS) else None
-    kname = ("umma_gemm_pair_kernel (gate|up, SiLU-gate + quantising epilogue)" if args.mode == "w4a4"
+    traffic = 26.36e6 if (args.mode == "w4a4" and M == M_TOKENS) else None
+    kname = ("umma_gemm_pair16_kernel (gate|up, SiLU-gate + quantising epilogue)" if args.mode == "w4a4"
              else "umma_gemm_kernel (gate|up, SiLU-gate epilogue)")
     roofline = {"bound": "tensor", "kernel": kname, "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
