@@ -8,7 +8,7 @@
 //     context and keeps its own online-softmax state; the four partial results are merged through
 //     shared memory at the end;
 //   * each tile's K and V rows (16 x 256 B each) are brought to shared memory with 16-byte cp.async
-//     into a 3-deep per-warp ring (rows past the sequence or in masked pages are zero-filled), with
+//     into a 2-deep per-warp ring (64 KB per CTA, so three CTAs share an SM: measured faster than a deeper ring with two) (rows past the sequence or in masked pages are zero-filled), with
 //     the 16-byte chunks XOR-swizzled by row so that ldmatrix is bank-conflict free;
 //   * S = Q K^T and O += P V run on mma.sync m16n8k16 (bf16 in, fp32 accumulate): the G <= 8 query
 //     heads of the group are rows 0..G-1 of the 16-row A operand.  Four query rows are far below the
@@ -28,10 +28,10 @@ namespace glmasr {
 static constexpr int kTile = 16;                       // tokens per tile
 static constexpr int kRowBytes = 256;                  // one K or V row of one kv head (128 bf16)
 static constexpr int kTileBytes = kTile * kRowBytes;   // 4 KB
-static constexpr int kStages = 3;
+static constexpr int kStages = 2;
 static constexpr int kWarps = 4;
-static constexpr int kWarpSmem = kStages * 2 * kTileBytes;          // K and V rings of one warp: 24 KB
-static constexpr int kAttnSmem = kWarps * kWarpSmem;                // 96 KB
+static constexpr int kWarpSmem = kStages * 2 * kTileBytes;          // K and V rings of one warp: 16 KB
+static constexpr int kAttnSmem = kWarps * kWarpSmem;                // 64 KB
 
 __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool valid) {
     const int n = valid ? 16 : 0;
@@ -109,21 +109,6 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
     const int num_tiles = (seq_len + kTile - 1) / kTile;
     const int my_tiles = num_tiles > warp ? (num_tiles - warp + kWarps - 1) / kWarps : 0;
 
-    // ---- Q fragments: rows = query heads of the group (lanes with g >= group hold zeros) ----
-    uint32_t qa[8][2];
-    {
-        const __nv_bfloat16 *qp = query + (size_t)seq * ldq + (size_t)(q_head0 + g) * 128;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            qa[ks][0] = 0u;
-            qa[ks][1] = 0u;
-            if (g < group) {
-                qa[ks][0] = *reinterpret_cast<const uint32_t *>(qp + ks * 16 + tq * 2);
-                qa[ks][1] = *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8 + tq * 2);
-            }
-        }
-    }
-
     // ---- producer: this warp's tile i (global tile index warp + 4 i) into ring slot i % kStages ----
     auto load_tile = [&](int i) {
         const int tile = warp + kWarps * i;
@@ -172,6 +157,22 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_attention_mma_kernel
         if (i < my_tiles) load_tile(i);
         cp_async_commit();
     }
+
+    // ---- Q fragments (loaded while the first K / V tiles are on their way): rows = query heads of the group (lanes with g >= group hold zeros) ----
+    uint32_t qa[8][2];
+    {
+        const __nv_bfloat16 *qp = query + (size_t)seq * ldq + (size_t)(q_head0 + g) * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qa[ks][0] = 0u;
+            qa[ks][1] = 0u;
+            if (g < group) {
+                qa[ks][0] = *reinterpret_cast<const uint32_t *>(qp + ks * 16 + tq * 2);
+                qa[ks][1] = *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8 + tq * 2);
+            }
+        }
+    }
+
 
     for (int i = 0; i < my_tiles; ++i) {
         if (i + kStages - 1 < my_tiles) load_tile(i + kStages - 1);
