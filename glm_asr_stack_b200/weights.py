@@ -151,3 +151,53 @@ def linear_proj_pair_same_input(ws: WeightStore, x: torch.Tensor, prefix0: str, 
     if prefer_nvfp4_cutlass() and a.input_scale == b.input_scale:
         mode = ops.MODE_W4A4
     return ops.fp4_linear_fused(mode, x[:M], [a, b], epilogue=epilogue, input_scale=a.input_scale)
+
+
+def linear_proj_triple_same_input_bf16(ws: WeightStore, x: torch.Tensor, w0_name: str, w1_name: str, w2_name: str,
+                                       M: int, N0: int, N1: int, K: int) -> Optional[torch.Tensor]:
+    """reference: linear_proj_triple_same_input_bf16, Infer-engine/cuda/decoder.cu:980-1013: the bf16-only
+    q|k|v fusion, one GEMM writing [M, N0 + 2 N1] from the three weights laid end to end.  Returns None
+    ("0" in the reference) unless all three weights are bf16 -- FP4 weights are fused by
+    ops.fp4_linear_fused instead."""
+    tws = [ws.require(n) for n in (w0_name, w1_name, w2_name)]
+    if any(t.dtype != DTYPE_BF16 for t in tws):
+        return None
+    w = torch.cat([tws[0].data[:N0, :K], tws[1].data[:N1, :K], tws[2].data[:N1, :K]], dim=0).contiguous()
+    return ops.bf16_linear(x[:M], w)
+
+
+_compare_done = False
+
+
+def should_compare_nvfp4_once() -> bool:
+    """reference: should_compare_nvfp4_once, Infer-engine/cuda/decoder.cu:196-204 (GLMASR_NVFP4_COMPARE_ONCE=1)."""
+    return os.environ.get("GLMASR_NVFP4_COMPARE_ONCE", "")[:1] == "1"
+
+
+def compare_nvfp4_once(x: torch.Tensor, w_packed: torch.Tensor, w_scales: torch.Tensor, input_scale: float,
+                       global_scale: float, pre_quant_scale: Optional[torch.Tensor], M: int, N: int, K: int,
+                       tag: str, out: Optional[torch.Tensor] = None, force: bool = False):
+    """reference: compare_nvfp4_once, Infer-engine/cuda/decoder.cu:206-275 -- the engine's only in-tree numerical
+    check: run one projection through nvfp4_linear (native) and fp4_linear (fallback), report the largest and
+    the mean absolute difference on stderr in the reference's format, and leave the native result in ``out``.
+    Runs once per process and only when GLMASR_NVFP4_COMPARE_ONCE=1 (``force`` skips both conditions).
+    Returns the statistics as a dict, or None when it did not run or the native path refused the shape."""
+    global _compare_done
+    if not force and (_compare_done or not should_compare_nvfp4_once()):
+        return None
+    _compare_done = True
+    native = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if ops.nvfp4_linear(native, x[:M], w_packed, w_scales, input_scale, global_scale, pre_quant_scale, None, M, N, K) != 0:
+        sys.stderr.write(f"NVFP4_COMPARE {tag} native_status=fail\n")
+        return None
+    fallback = ops.fp4_linear(x[:M], w_packed, w_scales, global_scale, pre_quant_scale, None)
+    a, b = native.float().flatten(), fallback.float().flatten()
+    d = (a - b).abs()
+    idx = int(torch.argmax(d).item())
+    stats = {"max_abs": float(d[idx].item()), "mean_abs": float(d.double().mean().item()), "idx": idx,
+             "native": float(a[idx].item()), "fallback": float(b[idx].item())}
+    sys.stderr.write("NVFP4_COMPARE %s M=%d N=%d K=%d max_abs=%.6f mean_abs=%.6f idx=%d native=%.6f fallback=%.6f\n"
+                     % (tag, M, N, K, stats["max_abs"], stats["mean_abs"], idx, stats["native"], stats["fallback"]))
+    if out is not None:
+        out[:M, :N].copy_(native)
+    return stats

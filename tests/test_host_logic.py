@@ -111,6 +111,44 @@ def test_pair_fusion_rules(monkeypatch):
     assert calls == [ops.MODE_W4A4]
 
 
+def test_triple_bf16_fusion_rules(monkeypatch):
+    """reference decoder.cu:980-1013: only three bf16 weights fuse; the weights are laid end to end."""
+    seen = {}
+    monkeypatch.setattr(ops, "bf16_linear", lambda x, w, *a, **k: seen.setdefault("w", w) is None or "fused")
+    x = torch.zeros((2, 32), dtype=torch.bfloat16)
+    st = weights.WeightStore()
+    for i, (n, rows) in enumerate((("q", 8), ("k", 4), ("v", 4))):
+        st.add(f"{n}.weight", torch.full((rows, 32), float(i), dtype=torch.bfloat16))
+    assert weights.linear_proj_triple_same_input_bf16(st, x, "q.weight", "k.weight", "v.weight", 2, 8, 4, 32) == "fused"
+    assert seen["w"].shape == (16, 32) and seen["w"][8, 0] == 1 and seen["w"][12, 0] == 2
+    # any FP4 member: no fusion here (the FP4 fusion is fp4_linear_fused)
+    mixed = weights.WeightStore()
+    mixed.add("q.weight", torch.zeros((8, 16), dtype=torch.uint8))
+    mixed.add("k.weight", torch.zeros((4, 32), dtype=torch.bfloat16))
+    mixed.add("v.weight", torch.zeros((4, 32), dtype=torch.bfloat16))
+    assert weights.linear_proj_triple_same_input_bf16(mixed, x, "q.weight", "k.weight", "v.weight", 2, 8, 4, 32) is None
+
+
+def test_compare_nvfp4_once_runs_once_and_reports(monkeypatch, capsys):
+    """reference decoder.cu:196-275: gated by GLMASR_NVFP4_COMPARE_ONCE=1, once per process, reference's line format."""
+    native = torch.tensor([[1.0, 2.0], [3.0, 4.5]], dtype=torch.bfloat16)
+    fallback = torch.tensor([[1.0, 2.0], [3.0, 4.0]], dtype=torch.bfloat16)
+    monkeypatch.setattr(ops, "nvfp4_linear", lambda out, *a, **k: out.copy_(native) is None or 0)
+    monkeypatch.setattr(ops, "fp4_linear", lambda *a, **k: fallback)
+    monkeypatch.setattr(weights, "_compare_done", False)
+    x = torch.zeros((2, 16), dtype=torch.bfloat16)
+    args = (x, None, None, 1.0, 1.0, None, 2, 2, 16, "layer0.q")
+    monkeypatch.delenv("GLMASR_NVFP4_COMPARE_ONCE", raising=False)
+    assert weights.compare_nvfp4_once(*args) is None                      # not asked for
+    monkeypatch.setenv("GLMASR_NVFP4_COMPARE_ONCE", "1")
+    out = torch.zeros((2, 2), dtype=torch.bfloat16)
+    st = weights.compare_nvfp4_once(*args, out=out)
+    assert st["max_abs"] == 0.5 and st["idx"] == 3 and st["native"] == 4.5 and st["fallback"] == 4.0
+    assert abs(st["mean_abs"] - 0.125) < 1e-9 and torch.equal(out, native)
+    assert "NVFP4_COMPARE layer0.q M=2 N=2 K=16 max_abs=0.500000 mean_abs=0.125000 idx=3" in capsys.readouterr().err
+    assert weights.compare_nvfp4_once(*args) is None                      # only once per process
+
+
 def test_ops_reject_cpu_tensors():
     with pytest.raises(ValueError):
         ops.fp4_dequant_to_bf16(torch.zeros((2, 8), dtype=torch.uint8), None, 1.0)
