@@ -415,6 +415,36 @@ def main():
                 "achieved_gbs": top[0][2] / (top_ms * 1e-3) / 1e9,
                 "frac_of_measured_bf16": (achieved / peaks["bf16_tflops"]) if peaks else None}
 
+    # ---- what the tensor pipe delivers to this kernel when nothing else is in the way ----------------
+    # MEASURED_PEAKS.json has no FP4 figure, so measure one here: the dominant GEMM (same kernel, same
+    # shape) with its operands left resident in shared memory after the first round of the ring and its
+    # stores switched off, i.e. the k-loop at the rate of the MMA issue and the tensor pipe alone.
+    mma_loop_tflops = None
+    if args.mode == "w4a4":
+        import ctypes
+        from glm_asr_stack_b200 import _lib
+        lib = _lib.load()
+        w0 = keep[0]
+        lib.glmasr_debug_set_flags(ctypes.c_int(4 | 8))
+        try:
+            for _ in range(3):
+                ops.fp4_linear_fused(mode, xs[0], [w0["gate"], w0["up"]], epilogue=ops.EPI_SILU_GATE, input_scale=isc_h)
+            ops.profile_enable(True)
+            for _ in range(5):
+                ops.fp4_linear_fused(mode, xs[0], [w0["gate"], w0["up"]], epilogue=ops.EPI_SILU_GATE, input_scale=isc_h)
+            pk = [ms for ms, f, _ in ops.profile_read() if f == top_flops]
+            ops.profile_enable(False)
+            if pk:
+                mma_loop_tflops = top_flops / (statistics.median(pk) * 1e-3) / 1e12
+        finally:
+            lib.glmasr_debug_set_flags(ctypes.c_int(-1))
+        torch.cuda.synchronize()
+        ops.status()
+        roofline["mma_loop_tflops"] = mma_loop_tflops
+        roofline["frac_of_mma_loop"] = (achieved / mma_loop_tflops) if mma_loop_tflops else None
+        roofline["mma_loop_how"] = ("same kernel and shape with operands resident in shared memory (no loads after the "
+                                    "first ring round) and stores off: the rate of MMA issue + tensor pipe alone")
+
     # ---- end to end: host buffers in, host buffers out, through the C-ABI host entry point ----
     for i in range(2):
         ops.layer_proj_host(mode, hin[i % 2], hout, layers[i % n_sets])

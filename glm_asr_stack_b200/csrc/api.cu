@@ -143,13 +143,14 @@ static int w4a16_dequant_once_rows() {
     return v;
 }
 
+static int g_debug_override = -1;           // glmasr_debug_set_flags: timing experiments from the host language
 static int debug_flags() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("GLMASR_DEBUG_FLAGS");
         v = (e && e[0]) ? atoi(e) : 0;
     }
-    return v;
+    return g_debug_override >= 0 ? g_debug_override : v;
 }
 
 // GLMASR_PAIR_KERNEL=0 keeps W4A4 on the single-CTA kernel (comparison runs)
@@ -1218,6 +1219,9 @@ extern "C" int glmasr_fp4_status(void) {
 }
 
 extern "C" long long glmasr_launch_count(void) { return g_launches; }
+
+// timing experiments: switch the kernels' experiment flags (wrong results by design; -1 = back to the environment's)
+extern "C" void glmasr_debug_set_flags(int flags) { g_debug_override = flags; }
 
 // timing experiments: copy the per-CTA cycle counters of the last instrumented GEMM launch
 extern "C" int glmasr_debug_cycles(unsigned long long *host_out, int max_ctas) {

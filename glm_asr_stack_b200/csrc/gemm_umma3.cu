@@ -146,6 +146,13 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
                 const uint32_t fb = full0 + 8u * (uint32_t)s;
                 const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
                 const bool no_sf = (p.debug & 2) != 0;      // timing experiment: no scale-factor traffic (wrong results)
+                if ((p.debug & 8) && it >= (uint32_t)C::STAGES) {
+                    // timing experiment: operands stay resident in shared memory after the first round of the
+                    // ring, so the k-loop runs at the rate the tensor pipe (and the MMA issue) allows
+                    if (leader_lane && do_a && rank == 0) mbar_arrive(full_bar(s));
+                    ++it;
+                    continue;
+                }
                 if (leader_lane) {
                     if (do_a) {
                         if (rank == 0) mbar_expect_tx(full_bar(s), no_sf ? 2u * (C::A_BYTES + C::B_BYTES) : C::TX_BYTES_PAIR);
