@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Benchmark of the FP4 linear path: the four FP4 projections of one GLM-ASR decoder layer at
-prefill (M = 10000 tokens, hidden 2048, q/k/v 2048/512/512, ffn 6144) -- BASELINE config 1.
+prefill (M = 10000 tokens, hidden 2048, q/k/v 2048/512/512, ffn 6144) -- benchmark configuration 1.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode w4a4|w4a16]
 
@@ -118,7 +118,7 @@ def run_reference(args, rank):
 
 
 def run_decode(args, rank, local_rank, world):
-    """BASELINE config 2: one batched decode step of the 28-layer decoder + FP4 lm_head + arg-max for
+    """Benchmark configuration 2: one batched decode step of the 28-layer decoder + FP4 lm_head + arg-max for
     256 sequences with paged bf16 KV (16-token pages, context 200-450).  tok/s = sequences / step time."""
     os.environ["GLMASR_USE_CUTLASS_NVFP4"] = "1" if args.mode == "w4a4" else "0"
     import torch
@@ -296,7 +296,7 @@ def main():
     ap.add_argument("--rows", type=int, default=M_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="layer", choices=["layer", "decode", "prefill"],
-                    help="layer = BASELINE config 1 (default, the headline); decode = BASELINE config 2; "
+                    help="layer = benchmark configuration 1 (default, the headline); decode = configuration 2; "
                          "prefill = the whole 28-layer batched prefill the config-1 projections belong to")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--layers", type=int, default=28)

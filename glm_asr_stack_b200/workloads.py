@@ -1,5 +1,5 @@
 """Synthetic instances of the benchmark configurations: a random-init FP4 decoder with the
-checkpoint's tensor names, and a paged-KV decode state (BASELINE config 2: 256 sequences, context
+checkpoint's tensor names, and a paged-KV decode state (benchmark configuration 2: 256 sequences, context
 lengths uniform in 200-450, 16-token pages handed out from a random permutation of the pool).
 """
 from __future__ import annotations

@@ -175,7 +175,7 @@ def test_fused_residual_epilogue(ops, mode):
 
 
 def test_config0_full_size_both_paths(ops):
-    """BASELINE config 0: x [256, 2048] ~ N(0,1) seed 1, W [6144, 2048] ~ N(0, 0.02) seed 0."""
+    """Benchmark configuration 0: x [256, 2048] ~ N(0,1) seed 1, W [6144, 2048] ~ N(0, 0.02) seed 0."""
     M, N, K = 256, 6144, 2048
     pw, sw, g = o.seeded_weight(N, K, 0)
     x = o.seeded_activation(M, K, 1)
@@ -196,7 +196,7 @@ def test_config0_full_size_both_paths(ops):
 
 
 def test_full_size_prefill_properties(ops):
-    """M = 10000 (BASELINE config 1 rows) is too large for the numpy oracle to finish in seconds
+    """M = 10000 (the rows of benchmark configuration 1) is too large for the numpy oracle to finish in seconds
     for every projection; use size-independent properties: row independence (the first rows of
     the big launch equal a small launch that the oracle did check), the M tail (10000 = 78*128+16)
     and exact agreement of the fused q|k|v GEMM with three single GEMMs."""
