@@ -40,7 +40,8 @@ struct TimedLaunch {
 };
 static std::vector<TimedLaunch> g_timed;
 
-static constexpr int kSlots = 32;   // 0..12, 24..25, 30..31 used here, 13..23 and 26..29 by the decode step (decoder_step.cu)
+static constexpr int kSlots = 40;   // 0..12, 24..25, 30..31 used here, 13..23 and 26..29 by the decode step (decoder_step.cu),
+                                    // 32 by the prefill attention (prefill_attention_umma.cu)
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
 
@@ -281,6 +282,11 @@ static bool make_tmap(CUtensorMap *tm, const void *base, CUtensorMapDataType dt,
     if (g_tmaps.size() > 16384) g_tmaps.clear();
     g_tmaps.emplace(key, *tm);
     return true;
+}
+
+bool make_bf16_tmap_sw128(CUtensorMap *tm, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                          uint32_t box_inner, uint32_t box_rows) {
+    return make_tmap(tm, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, inner, rows, pitch_bytes, box_inner, box_rows, true);
 }
 
 // ------------------------------------------------------------------------------------------

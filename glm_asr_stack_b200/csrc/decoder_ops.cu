@@ -269,11 +269,73 @@ __global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__
     }
 }
 
+// Same results, one WARP per row, for batches of thousands of rows (prefill), where the CTA-per-row
+// kernel above is a chain of load -> one-warp reduction -> quantise with little to overlap it.  Lane i
+// adds x[i], x[i + 32], ... in that order -- the summation order of the kernel above and of the
+// reference's rmsnorm -- from 2-byte loads (a warp reads 64 contiguous bytes per load, 16 loads in
+// flight per lane); the shuffle tree and the arithmetic after it are the same expressions.  The second
+// pass re-reads the row (first-level cache hits) 16 bytes at a time: a lane quantises four consecutive
+// 16-element blocks, i.e. 32 contiguous output bytes and one 4-byte group of scales.  dim % 2048 == 0.
+__global__ void __launch_bounds__(256) rmsnorm_quant_warp_kernel(uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf,
+                                                                int sf_chunks, const __nv_bfloat16 *__restrict__ x,
+                                                                const __nv_bfloat16 *__restrict__ weight, float eps,
+                                                                float inv_in, int rows, int dim) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const __nv_bfloat16 *xr = x + (size_t)row * dim;
+    float sum_sq = 0.0f;
+    for (int i0 = lane; i0 < dim; i0 += 512) {
+        float v[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) v[t] = __bfloat162float(xr[i0 + 32 * t]);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) sum_sq += v[t] * v[t];
+    }
+    for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
+    const float rms = __shfl_sync(0xFFFFFFFFu, sqrtf(sum_sq / dim + eps), 0);
+    const int rem = row & 127;
+    for (int b0 = 4 * lane; b0 < dim / 16; b0 += 128) {
+        uint32_t packed[8], sfw = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int b = b0 + k;
+            float v[16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 xv = reinterpret_cast<const uint4 *>(xr)[2 * b + h];
+                const uint4 wv = reinterpret_cast<const uint4 *>(weight)[2 * b + h];
+                const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float a0 = __fdiv_rn(__uint_as_float(xs[j] << 16), rms) * __uint_as_float(ws[j] << 16);
+                    const float a1 = __fdiv_rn(__uint_as_float(xs[j] & 0xFFFF0000u), rms) * __uint_as_float(ws[j] & 0xFFFF0000u);
+                    v[8 * h + 2 * j] = __bfloat162float(__float2bfloat16(a0));
+                    v[8 * h + 2 * j + 1] = __bfloat162float(__float2bfloat16(a1));
+                }
+            }
+            const uint32_t sf = quantize_block16(v, inv_in, packed[2 * k], packed[2 * k + 1]);
+            sfw |= (sf & 0xFFu) << (8 * k);
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(q_packed + (size_t)row * (dim / 2) + (size_t)b0 * 8);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        *reinterpret_cast<uint32_t *>(q_sf + ((((size_t)(row >> 7) * sf_chunks + (b0 >> 2)) * 32 + (rem & 31)) * 4 + (rem >> 5)) * 4) = sfw;
+    }
+}
+
 bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps,
                           float input_scale, int rows, int dim, cudaStream_t st) {
     if (rows <= 0) return true;
     if ((dim % 64) != 0 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)q_packed) & 15) != 0 || !(input_scale > 0.0f))
         return false;
+    if (rows >= 2048 && (dim % 2048) == 0) {
+        launch_chained(rmsnorm_quant_warp_kernel, dim3((rows + 7) / 8), dim3(256), (size_t)0, st, q_packed, q_sf, dim / 64, x, weight,
+                       eps, 1.0f / input_scale, rows, dim);
+        return true;
+    }
     GLMASR_PREFER_MAX_SMEM(rmsnorm_quant_kernel);
     launch_chained(rmsnorm_quant_kernel, dim3(rows), dim3(128), (size_t)dim * sizeof(__nv_bfloat16), st, q_packed, q_sf, dim / 64, x, weight, eps,
                                                                             1.0f / input_scale, rows, dim);

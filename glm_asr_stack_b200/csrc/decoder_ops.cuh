@@ -43,11 +43,22 @@ bool launch_paged_decode_attention_mma(__nv_bfloat16 *out, int ldo, const __nv_b
                                        float q_input_scale = 0.0f);
 // Variable-length GQA self-attention of a prefill batch (prefill_attention.cu): sequence s owns rows
 // [seq_offsets[s], +seq_lens[s]) of q / k / v / out (device arrays; seq_lens == NULL: seq_offsets is a
-// cumulative table of num_seqs + 1 entries); head_dim 128.
+// cumulative table of num_seqs + 1 entries); head_dim 128.  total_tokens = rows of q / k / v (the sequences
+// lie inside them and do not overlap).  The caller accounts for one launch; a second one (the V transposition
+// of the tcgen05 path) is noted by the launcher itself.  With q_packed / q_sf the result is written as the
+// next projection's quantised operand (packed e2m1 [rows, q_heads * 64] + 128x4-tiled scales) instead of bf16;
+// false if that form is not available for the shape.
 bool launch_prefill_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *q, int ldq, const __nv_bfloat16 *k,
                               int ldk, const __nv_bfloat16 *v, int ldv, const int *seq_offsets, const int *seq_lens,
-                              int num_seqs, int max_seq_len, int num_q_heads, int num_kv_heads, int head_dim, bool causal,
-                              cudaStream_t st);
+                              int num_seqs, int max_seq_len, int total_tokens, int num_q_heads, int num_kv_heads,
+                              int head_dim, bool causal, cudaStream_t st, uint8_t *q_packed = nullptr,
+                              uint8_t *q_sf = nullptr, float q_input_scale = 0.0f);
+// The tcgen05 kernel behind it (prefill_attention_umma.cu); false = shape or alignment not covered.
+bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *q, int ldq, const __nv_bfloat16 *k,
+                                   int ldk, const __nv_bfloat16 *v, int ldv, const int *seq_offsets, const int *seq_lens,
+                                   int num_seqs, int max_seq_len, int total_tokens, int num_q_heads, int num_kv_heads,
+                                   int head_dim, bool causal, cudaStream_t st, uint8_t *q_packed = nullptr,
+                                   uint8_t *q_sf = nullptr, float q_input_scale = 0.0f);
 void launch_embedding_lookup(__nv_bfloat16 *out, const __nv_bfloat16 *table, const int *ids, int n, int dim,
                              cudaStream_t st);
 // out[i, :] = src_rows[i][:]  /  dst_rows[i][:] = in[i, :]   (device arrays of row pointers)

@@ -514,7 +514,8 @@ extern "C" int flash_fwd_vllm_gqa_launch(void *q, void *k, void *v, void *out, i
     if (total_seqlen <= 0 || num_seqs <= 0) return 1;
     if (!launch_prefill_attention((__nv_bfloat16 *)out, q_heads * head_dim, (const __nv_bfloat16 *)q, q_row_stride,
                                   (const __nv_bfloat16 *)k, k_row_stride, (const __nv_bfloat16 *)v, v_row_stride,
-                                  d_cu_seqlens, nullptr, num_seqs, max_seqlen, q_heads, kv_heads, head_dim, is_causal != 0,
+                                  d_cu_seqlens, nullptr, num_seqs, max_seqlen, total_seqlen, q_heads, kv_heads, head_dim,
+                                  is_causal != 0,
                                   current_stream()))
         return 0;
     note_launches(1);
@@ -580,6 +581,10 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
     uint16_t *scratch = (uint16_t *)workspace_slot(WS_D_SCRATCH, (size_t)M * (F > H ? F : H) * 2);
     uint8_t *nq = (uint8_t *)workspace_slot(WS_D_XQ, (size_t)M * H / 2);
     uint8_t *nsf = (uint8_t *)workspace_slot(WS_D_XSF, tiled_scale_bytes(M, H));
+    // quantised SiLU-gate output (K = F) handed to the down projection
+    const int KQ = F > H ? F : H;
+    uint8_t *aq = (uint8_t *)workspace_slot(WS_D_AQ, (size_t)M * KQ / 2);
+    uint8_t *asf = (uint8_t *)workspace_slot(WS_D_ASF, tiled_scale_bytes(M, KQ));
     int64_t *d_slot = (int64_t *)workspace_slot(WS_D_SLOT, (size_t)M * sizeof(int64_t));
     int *d_pos = (int *)workspace_slot(WS_D_POS, (size_t)M * sizeof(int));
     int *d_meta = (int *)workspace_slot(WS_D_OFFS, (size_t)2 * num_seqs * sizeof(int));
@@ -616,16 +621,32 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
                                      (const __nv_bfloat16 *)qkv + H + KV, NQKV, d_slot, M, KVH, HD, pool->block_size, st);
             glue += 3;
         }
-        const bool ok = launch_prefill_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV,
-                                                 (const __nv_bfloat16 *)qkv + H, NQKV, (const __nv_bfloat16 *)qkv + H + KV,
-                                                 NQKV, d_meta, d_meta + num_seqs, num_seqs, max_len, QH, KVH, HD, true, st);
-        GLMASR_CHECK(ok, "decoder_prefill_paged_batched: unsupported attention shape");
+        // attention; where the o projection takes a quantised operand the kernel writes that instead of bf16
+        const bool o_q = takes_quantised_input(R.o) && R.o.K == H && QH * HD == H;
+        if (o_q && launch_prefill_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV,
+                                            (const __nv_bfloat16 *)qkv + H, NQKV, (const __nv_bfloat16 *)qkv + H + KV, NQKV,
+                                            d_meta, d_meta + num_seqs, num_seqs, max_len, M, QH, KVH, HD, true, st, aq, asf,
+                                            R.o.input_scale)) {
+            single_proj_prequantized(hid, H, aq, asf, R.o, M, hid);
+        } else {
+            const bool ok = launch_prefill_attention((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV,
+                                                     (const __nv_bfloat16 *)qkv + H, NQKV,
+                                                     (const __nv_bfloat16 *)qkv + H + KV, NQKV, d_meta, d_meta + num_seqs,
+                                                     num_seqs, max_len, M, QH, KVH, HD, true, st);
+            GLMASR_CHECK(ok, "decoder_prefill_paged_batched: unsupported attention shape");
+            single_proj(hid, H, att, H, R.o, M, hid, scratch);
+        }
         glue += 1;
 
-        single_proj(hid, H, att, H, R.o, M, hid, scratch);
-
         const ProjRef *gu_p[2] = {&R.gate, &R.up};
-        if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
+        const bool down_q = takes_quantised_input(R.down) && R.down.K == F && (F % 64) == 0;
+        bool down_done = false;
+        if (down_q && norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st, aq,
+                                                asf, R.down.input_scale)) {
+            // the SiLU-gate epilogue wrote the down projection's quantised operand
+            single_proj_prequantized(hid, H, aq, asf, R.down, M, hid);
+            down_done = true;
+        } else if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
             // done
         } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st),
                    ++glue, !fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
@@ -633,7 +654,7 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
             single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
             silu_elementwise_mul(act, act + (size_t)M * F, M * F);
         }
-        single_proj(hid, H, act, F, R.down, M, hid, scratch);
+        if (!down_done) single_proj(hid, H, act, F, R.down, M, hid, scratch);
         note_launches(glue);
     }
     launch_rmsnorm((__nv_bfloat16 *)hid, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)refs.final_norm, 1e-5f, M, H, st);

@@ -9,8 +9,8 @@
 //     XOR-swizzled by row so that ldmatrix is bank-conflict free;
 //   * S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 in, fp32 accumulate), online softmax in
 //     fp32 registers, P rounded to bf16 for the second product.
-// The work is ~16 GFLOP per layer at 10000 tokens against ~965 GFLOP in the layer's projections,
-// so a warp-level MMA kernel is enough; it is not on the FP4 path's critical kernel list.
+// This warp-level kernel serves the shapes and alignments the tcgen05 kernel
+// (prefill_attention_umma.cu) does not take; launch_prefill_attention tries that one first.
 #include <cuda_bf16.h>
 #include <math.h>
 #include <stdint.h>
@@ -235,8 +235,15 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
 
 bool launch_prefill_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *q, int ldq, const __nv_bfloat16 *k,
                               int ldk, const __nv_bfloat16 *v, int ldv, const int *seq_offsets, const int *seq_lens,
-                              int num_seqs, int max_seq_len, int num_q_heads, int num_kv_heads, int head_dim, bool causal,
-                              cudaStream_t st) {
+                              int num_seqs, int max_seq_len, int total_tokens, int num_q_heads, int num_kv_heads,
+                              int head_dim, bool causal, cudaStream_t st, uint8_t *q_packed, uint8_t *q_sf,
+                              float q_input_scale) {
+    if (num_seqs > 0 && max_seq_len > 0 &&
+        launch_prefill_attention_umma(out, ldo, q, ldq, k, ldk, v, ldv, seq_offsets, seq_lens, num_seqs, max_seq_len,
+                                      total_tokens, num_q_heads, num_kv_heads, head_dim, causal, st, q_packed, q_sf,
+                                      q_input_scale))
+        return true;
+    if (q_packed != nullptr) return false;      // only the tcgen05 kernel quantises its output
     if (head_dim != 128 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return false;
     if ((ldq % 2) != 0 || (ldo % 2) != 0 || (ldk % 8) != 0 || (ldv % 8) != 0) return false;
     if ((((uintptr_t)k | (uintptr_t)v) & 15) != 0 || (((uintptr_t)q | (uintptr_t)out) & 3) != 0) return false;

@@ -17,6 +17,8 @@ enum : int {
     ST_TIMEOUT_EPILOGUE = 3,   // epilogue waited too long for a finished accumulator
     ST_TIMEOUT_DEQUANT = 4,    // dequant warps waited too long for raw weights / a free tile
     ST_TIMEOUT_SPLITK = 5,     // split-K reduction waited too long for partial results
+    ST_TIMEOUT_ATTENTION = 6,  // a role of the prefill attention kernel waited too long
+    ST_BAD_LAYOUT = 7,         // shared-memory base or workspace extent not as the kernel needs it
 };
 
 // ~1.5 s at 1.3-1.9 GHz: far beyond any legitimate wait, short enough not to look like a hang.
@@ -189,6 +191,15 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Store 32 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- CTA pairs (cta_group::2): two CTAs of a cluster drive one 256-row MMA ---------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {

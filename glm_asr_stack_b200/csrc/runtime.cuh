@@ -4,7 +4,9 @@
 // reference's conventions (Infer-engine/include/types.h:182-199: print and exit(1) for the
 // void entry points; nvfp4_linear instead returns -1, Infer-engine/cuda/nvfp4_cutlass.cu:262-269).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
+#include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -17,7 +19,11 @@ void *workspace(size_t bytes);      // grow-only private device workspace (slot 
 void *workspace_slot(int slot, size_t bytes);
 void free_all_private_state();
 void note_launches(int n);          // launch accounting for kernels started outside api.cu
-size_t tiled_scale_bytes(int rows, int K);   // bytes of the 128x4-tiled scale layout for [rows, K]
+size_t tiled_scale_bytes(int rows, int K);
+// Cached TMA descriptor of a row-major bf16 matrix [rows, inner] (row pitch in bytes, a multiple of 16; base
+// 16-byte aligned) cut into box_rows x box_inner boxes with the 128-byte swizzle.  False if it cannot be encoded.
+bool make_bf16_tmap_sw128(CUtensorMap *tm, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                          uint32_t box_inner, uint32_t box_rows);   // bytes of the 128x4-tiled scale layout for [rows, K]
 
 // Ask once for the largest shared-memory carve-out for `kernel`.  The GEMM kernels need almost all
 // of an SM's shared memory; a small kernel launched between two of them with the default

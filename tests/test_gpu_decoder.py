@@ -157,7 +157,7 @@ def test_rope_qk_cache_equals_three_launches(ops):
     assert ulp_diff(bits_of(buf[:, :H].contiguous()), want_q).max() <= 1 or o.rel_err(bits_of(buf[:, :H].contiguous()), want_q) < 2e-3
 
 
-@pytest.mark.parametrize("rows,dim", [(1, 2048), (130, 256), (256, 2048)])
+@pytest.mark.parametrize("rows,dim", [(1, 2048), (130, 256), (256, 2048), (2500, 2048), (2051, 4096)])
 def test_rmsnorm_quant_equals_norm_then_quantiser(ops, rows, dim):
     """rmsnorm + quantiser in one launch = rmsnorm, then the stand-alone quantiser, then the scale re-tiling."""
     rng = np.random.default_rng(rows + dim)
@@ -301,12 +301,60 @@ def test_prefill_attention_vs_oracle(qh, kvh, causal):
                                            max(lens), qh, kvh, hd, causal))
     want = do.prefill_attention(qkv[:, :H], qkv[:, H:H + KV], qkv[:, H + KV:], offs[:-1], lens, qh, kvh, hd, causal)
     assert o.rel_err(got, want) <= REL_TOL_TIGHT
+    from glm_asr_stack_b200 import ops as _ops
+    assert _ops.status() == 0
     # row by row: every query row within bf16 tolerance, the first row of a causal sequence is its own V row
     for off, ln in zip(offs[:-1], lens):
         assert o.rel_err(got[off:off + ln], want[off:off + ln]) <= REL_TOL_TIGHT
         if causal:
             v0 = qkv[off, H + KV:].reshape(kvh, hd)
             assert np.array_equal(got[off].reshape(qh, hd), np.repeat(v0, qh // kvh, axis=0))
+
+
+@pytest.mark.parametrize("lens,causal,q_scale", [
+    ([1000, 129, 700, 128, 2], True, 1.0),        # many key steps per query tile
+    ([513, 64, 300], False, 1.0),
+    ([448, 394, 200], True, 6.0),                 # wide score range: the running maximum keeps jumping
+    ([300, 257], False, 6.0),
+])
+def test_prefill_attention_long_and_wide_range(ops, lens, causal, q_scale):
+    """Longer sequences (up to 16 key steps per query tile) and scores whose range forces the accumulator
+    of the tensor-core kernel to be rescaled between key steps; the status word must stay clear."""
+    from glm_asr_stack_b200 import engine
+    rng = np.random.default_rng(len(lens) * 100 + int(q_scale))
+    qh, kvh, hd = 8, 2, 128
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T, H, KV = int(offs[-1]), qh * hd, kvh * hd
+    qkv = rnd_bits(rng, (T, H + 2 * KV))
+    qkv[:, :H] = rnd_bits(rng, (T, H), q_scale)
+    buf = to_dev_bf16(qkv)
+    got = bits_of(engine.prefill_attention(buf[:, :H], buf[:, H:H + KV], buf[:, H + KV:], torch.from_numpy(offs).cuda(),
+                                           max(lens), qh, kvh, hd, causal))
+    assert ops.status() == 0
+    want = do.prefill_attention(qkv[:, :H], qkv[:, H:H + KV], qkv[:, H + KV:], offs[:-1], lens, qh, kvh, hd, causal)
+    for off, ln in zip(offs[:-1], lens):
+        assert o.rel_err(got[off:off + ln], want[off:off + ln]) <= REL_TOL_TIGHT
+
+
+def test_prefill_attention_sequences_with_gaps(ops):
+    """Sequences given by offsets + lengths semantics of the plug-in (cumulative table) whose rows are separated
+    by rows of other data: rows outside every sequence must be left untouched, rows inside must not see them."""
+    from glm_asr_stack_b200 import engine
+    rng = np.random.default_rng(77)
+    qh, kvh, hd = 4, 2, 128
+    lens = [70, 130, 5]
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T, H, KV = int(offs[-1]), qh * hd, kvh * hd
+    qkv = rnd_bits(rng, (T, H + 2 * KV))
+    buf = to_dev_bf16(qkv)
+    whole = bits_of(engine.prefill_attention(buf[:, :H], buf[:, H:H + KV], buf[:, H + KV:], torch.from_numpy(offs).cuda(),
+                                             max(lens), qh, kvh, hd, True))
+    # the middle sequence alone, addressed through a table that starts at its first row
+    sub = buf[lens[0]:lens[0] + lens[1]]
+    alone = bits_of(engine.prefill_attention(sub[:, :H], sub[:, H:H + KV], sub[:, H + KV:],
+                                             torch.tensor([0, lens[1]], dtype=torch.int32).cuda(), lens[1], qh, kvh, hd, True))
+    assert ops.status() == 0
+    assert np.array_equal(whole[lens[0]:lens[0] + lens[1]], alone)
 
 
 def run_prefill_case(w4a4: bool):
