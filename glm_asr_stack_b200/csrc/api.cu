@@ -41,7 +41,7 @@ struct TimedLaunch {
 static std::vector<TimedLaunch> g_timed;
 
 static constexpr int kSlots = 40;   // 0..12, 24..25, 30..31 used here, 13..23 and 26..29 by the decode step (decoder_step.cu),
-                                    // 32 by the prefill attention (prefill_attention_umma.cu)
+                                    // 32..33 by the prefill attention (prefill_attention_umma.cu)
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
 

@@ -269,49 +269,98 @@ __global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__
     }
 }
 
+// x / d for many x and one divisor d, each quotient rounded exactly as the IEEE division the reference's
+// rmsnorm performs (x[i] / rms).  The correctly rounded reciprocal is taken once per divisor, kept as
+// r_hi + r_lo, and every quotient then costs four multiply-adds: q0 = x * (r_hi + r_lo) lies within one
+// unit in the last place of x / d, the residual e = x - q0 * d is exact in a fused multiply-add, and
+// q0 + e * r_hi rounds to the correctly rounded quotient (Markstein's theorem; it needs r_hi = RN(1 / d)
+// and a divisor whose significand is not all ones).  Operands outside the range where every intermediate
+// is a normal number, zeros, infinities and NaNs take the ordinary division.
+struct ExactRowDivider {
+    float d, r_hi, r_lo, fast_min;
+    __device__ __forceinline__ explicit ExactRowDivider(float divisor) : d(divisor) {
+        r_hi = __frcp_rn(d);
+        r_lo = fmaf(-d, r_hi, 1.0f) * r_hi;
+        const bool ok = d > 9.094947e-13f && d < 1.0995116e12f &&                  // 2^-40 < d < 2^40
+                        (__float_as_uint(d) & 0x007FFFFFu) != 0x007FFFFFu;
+        fast_min = ok ? 8.6736174e-19f : __int_as_float(0x7FC00000);               // 2^-60, or NaN: never fast
+    }
+    __device__ __forceinline__ float operator()(float x) const {
+        if (fabsf(x) >= fast_min) {
+            const float q0 = fmaf(x, r_hi, x * r_lo);
+            const float e = fmaf(-q0, d, x);
+            return fmaf(e, r_hi, q0);
+        }
+        return __fdiv_rn(x, d);
+    }
+};
+
 // Same results, one WARP per row, for batches of thousands of rows (prefill), where the CTA-per-row
-// kernel above is a chain of load -> one-warp reduction -> quantise with little to overlap it.  Lane i
-// adds x[i], x[i + 32], ... in that order -- the summation order of the kernel above and of the
-// reference's rmsnorm -- from 2-byte loads (a warp reads 64 contiguous bytes per load, 16 loads in
-// flight per lane); the shuffle tree and the arithmetic after it are the same expressions.  The second
-// pass re-reads the row (first-level cache hits) 16 bytes at a time: a lane quantises four consecutive
-// 16-element blocks, i.e. 32 contiguous output bytes and one 4-byte group of scales.  dim % 2048 == 0.
+// kernel above is a chain of load -> one-warp reduction -> quantise with little to overlap it.  A warp
+// reads its row once, coalesced, into a private strip of shared memory (128-byte lines 144 bytes apart,
+// so that every access pattern below is free of avoidable bank conflicts).  Lane i then adds x[i],
+// x[i + 32], ... in that order -- the summation order of the kernel above and of the reference's rmsnorm
+// -- and the shuffle tree and the arithmetic after it give the same values (the division by the row's
+// rms through ExactRowDivider).  For the quantiser a lane takes line `lane` of the strip: four
+// consecutive 16-element blocks, i.e. 32 contiguous output bytes and one 4-byte group of scales.
+// dim = 2048 * P.
+constexpr int kNormStrip = 32 * 144;      // bytes of shared memory per 2048 elements
+template <int P>
 __global__ void __launch_bounds__(256) rmsnorm_quant_warp_kernel(uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf,
                                                                 int sf_chunks, const __nv_bfloat16 *__restrict__ x,
                                                                 const __nv_bfloat16 *__restrict__ weight, float eps,
-                                                                float inv_in, int rows, int dim) {
+                                                                float inv_in, int rows) {
+    extern __shared__ __align__(16) uint8_t strips[];
+    constexpr int dim = 2048 * P;
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int row = blockIdx.x * 8 + wib;
     if (row >= rows) return;
-    const __nv_bfloat16 *xr = x + (size_t)row * dim;
+    uint8_t *rs = strips + wib * (P * kNormStrip);
+    {
+        const uint4 *xr4 = reinterpret_cast<const uint4 *>(x + (size_t)row * dim);
+        uint4 v[8 * P];
+#pragma unroll
+        for (int k = 0; k < 8 * P; ++k) v[k] = xr4[k * 32 + lane];
+#pragma unroll
+        for (int k = 0; k < 8 * P; ++k) {
+            const int byte = 512 * k + 16 * lane;
+            *reinterpret_cast<uint4 *>(rs + byte + (byte >> 7) * 16) = v[k];
+        }
+    }
+    __syncwarp();
     float sum_sq = 0.0f;
-    for (int i0 = lane; i0 < dim; i0 += 512) {
-        float v[16];
+    {
+        const uint8_t *ri = rs + 2 * lane;
 #pragma unroll
-        for (int t = 0; t < 16; ++t) v[t] = __bfloat162float(xr[i0 + 32 * t]);
-#pragma unroll
-        for (int t = 0; t < 16; ++t) sum_sq += v[t] * v[t];
+        for (int t = 0; t < 64 * P; ++t) {
+            const uint32_t h = *reinterpret_cast<const uint16_t *>(ri + 64 * t + 16 * (t >> 1));
+            const float v = __uint_as_float(h << 16);
+            sum_sq += v * v;
+        }
     }
     for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
     const float rms = __shfl_sync(0xFFFFFFFFu, sqrtf(sum_sq / dim + eps), 0);
+    const ExactRowDivider by_rms(rms);
     const int rem = row & 127;
-    for (int b0 = 4 * lane; b0 < dim / 16; b0 += 128) {
+#pragma unroll
+    for (int pass = 0; pass < P; ++pass) {
+        const int b0 = pass * 128 + 4 * lane;            // first of this lane's four blocks
+        const uint8_t *line = rs + pass * kNormStrip + lane * 144;
         uint32_t packed[8], sfw = 0;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const int b = b0 + k;
             float v[16];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint4 xv = reinterpret_cast<const uint4 *>(xr)[2 * b + h];
-                const uint4 wv = reinterpret_cast<const uint4 *>(weight)[2 * b + h];
+                const uint4 xv = *reinterpret_cast<const uint4 *>(line + (2 * k + h) * 16);
+                const uint4 wv = reinterpret_cast<const uint4 *>(weight)[2 * (b0 + k) + h];
                 const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float a0 = __fdiv_rn(__uint_as_float(xs[j] << 16), rms) * __uint_as_float(ws[j] << 16);
-                    const float a1 = __fdiv_rn(__uint_as_float(xs[j] & 0xFFFF0000u), rms) * __uint_as_float(ws[j] & 0xFFFF0000u);
+                    const float a0 = by_rms(__uint_as_float(xs[j] << 16)) * __uint_as_float(ws[j] << 16);
+                    const float a1 = by_rms(__uint_as_float(xs[j] & 0xFFFF0000u)) * __uint_as_float(ws[j] & 0xFFFF0000u);
                     v[8 * h + 2 * j] = __bfloat162float(__float2bfloat16(a0));
                     v[8 * h + 2 * j + 1] = __bfloat162float(__float2bfloat16(a1));
                 }
@@ -331,9 +380,20 @@ bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 
     if (rows <= 0) return true;
     if ((dim % 64) != 0 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)q_packed) & 15) != 0 || !(input_scale > 0.0f))
         return false;
-    if (rows >= 2048 && (dim % 2048) == 0) {
-        launch_chained(rmsnorm_quant_warp_kernel, dim3((rows + 7) / 8), dim3(256), (size_t)0, st, q_packed, q_sf, dim / 64, x, weight,
-                       eps, 1.0f / input_scale, rows, dim);
+    if (rows >= 2048 && (dim == 2048 || dim == 4096)) {
+        const dim3 grid((rows + 7) / 8);
+        if (dim == 2048) {
+            launch_chained(rmsnorm_quant_warp_kernel<1>, grid, dim3(256), (size_t)(8 * kNormStrip), st, q_packed, q_sf, dim / 64, x,
+                           weight, eps, 1.0f / input_scale, rows);
+        } else {
+            static bool configured = false;
+            if (!configured) {
+                cudaFuncSetAttribute(rmsnorm_quant_warp_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * kNormStrip);
+                configured = true;
+            }
+            launch_chained(rmsnorm_quant_warp_kernel<2>, grid, dim3(256), (size_t)(16 * kNormStrip), st, q_packed, q_sf, dim / 64, x,
+                           weight, eps, 1.0f / input_scale, rows);
+        }
         return true;
     }
     GLMASR_PREFER_MAX_SMEM(rmsnorm_quant_kernel);

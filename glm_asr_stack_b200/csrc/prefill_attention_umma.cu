@@ -3,8 +3,9 @@
 // Infer-engine/cuda/decoder.cu:1401-1441, and the plug-in entry flash_fwd_vllm_gqa_launch,
 // Infer-engine/cuda/flash_fwd_vllm.h:21-30): per sequence softmax(Q K^T / sqrt(d) [+ causal mask]) V.
 //
-// One CTA = 128 queries of one (sequence, q head); keys are walked in steps of 64:
-//   warp 0      TMA producer: Q once (two 128-row x 64-dim boxes), then per step the K tile (two 64-row
+// Persistent CTAs (two per SM) take work items = 128 queries of one (sequence, q head), longest first; the
+// keys of an item are walked in steps of 64:
+//   warp 0      TMA producer: Q once per item (two 128-row x 64-dim boxes), then per step the K tile (two 64-row
 //               boxes) and the V^T tile (128 dims x 64 keys) into two-stage rings, 128-byte swizzle;
 //   warp 1      MMA issuer: S_j = Q K_j^T (M 128, N 64, K 128) into one of two TMEM score buffers, and
 //               O += P_j V_j (M 128, N 128, K 64) into the TMEM output accumulator; S_{j+1} is issued
@@ -25,6 +26,8 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
+
+#include <vector>
 
 #include "decoder_ops.cuh"
 #include "fp4_format.cuh"
@@ -52,7 +55,7 @@ constexpr int THREADS = 192;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units
 
 enum : int { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SFREE = 11, B_PFULL = 13,
-             B_PVDONE = 14 };
+             B_PVDONE = 14, B_QEMPTY = 15, B_OFREE = 16 };
 
 struct AttnParams {
     CUtensorMap tm_q, tm_k, tm_vt;
@@ -60,7 +63,10 @@ struct AttnParams {
     const int *seq_offsets;
     const int *seq_lens;          // NULL: seq_offsets is cumulative (num_seqs + 1 entries)
     int *status;
-    int ldo, num_q_heads, group, q_tiles, causal;
+    const int *vt_col;            // first V^T column of every sequence (written by transpose_v_kernel)
+    unsigned long long *dbg;      // timing experiments: 8 cycle sums per CTA (soft-max warp 2), else NULL
+    int dbg_no_store;             // timing experiments: leave the result stores out
+    int ldo, num_q_heads, num_seqs, group, q_tiles, total_items, causal;
     float scale_log2;             // log2(e) / sqrt(head_dim)
     // optional: the result quantised for the next projection (activation quantiser on the bf16 values)
     uint8_t *q_packed;            // [rows, q_ld] e2m1 pairs; NULL = bf16 output to `out`
@@ -95,7 +101,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restrict__ vt, int vt_cols,
                                                          const __nv_bfloat16 *__restrict__ v, int ldv,
                                                          const int *__restrict__ seq_offsets,
-                                                         const int *__restrict__ seq_lens, int *status) {
+                                                         const int *__restrict__ seq_lens, int *__restrict__ vt_col,
+                                                         int *status) {
     __shared__ uint32_t tile[64][65];          // [token][dim pair], odd pitch
     __shared__ int s_col;
     pdl_launch_dependents();
@@ -106,7 +113,10 @@ __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restr
     if (t0 >= len) return;
     if (threadIdx.x < 32) {
         const int col = padded_column_of(seq_offsets, seq_lens, seq, threadIdx.x);
-        if (threadIdx.x == 0) s_col = col;
+        if (threadIdx.x == 0) {
+            s_col = col;
+            if (blockIdx.x == 0 && blockIdx.y == 0) vt_col[seq] = col;
+        }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -141,30 +151,43 @@ __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restr
     }
 }
 
+// Work item = (128-query tile, sequence, q head).  Items are numbered with the last (longest, when causal)
+// query tiles first; CTA c takes items c, c + gridDim.x, ...  Every role walks the same item list and keeps
+// running counters for its ring stages and barrier phases, so the producer and the MMA issuer run ahead into
+// the next item while the soft-max warps still write the current one's result.
+struct ItemInfo {
+    int head, seq, q0, off, len, n;
+};
+__device__ __forceinline__ bool decode_item(const AttnParams &p, int item, ItemInfo &it) {
+    const int per_tile = p.num_q_heads * p.num_seqs;
+    const int x = item % per_tile;
+    it.q0 = (p.q_tiles - 1 - item / per_tile) * QT;
+    it.head = x % p.num_q_heads;
+    it.seq = x / p.num_q_heads;
+    it.off = p.seq_offsets[it.seq];
+    it.len = seq_len_of(p.seq_offsets, p.seq_lens, it.seq);
+    if (it.q0 >= it.len) return false;
+    const int kv_end = p.causal ? min(it.len, it.q0 + QT) : it.len;
+    it.n = (kv_end + KT - 1) / KT;              // key steps of this tile (>= 1)
+    return true;
+}
+
 __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.x % p.num_q_heads, seq = blockIdx.x / p.num_q_heads;
-    const int q0 = (p.q_tiles - 1 - (int)blockIdx.y) * QT;      // longest tiles are scheduled first
-    pdl_wait();
-    const int off = p.seq_offsets[seq];
-    const int len = seq_len_of(p.seq_offsets, p.seq_lens, seq);
-    if (q0 >= len) return;
     if ((sbase & 1023u) != 0) {                 // the swizzled tiles need a 1024-byte aligned base
         if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, ST_BAD_LAYOUT);
         return;
     }
-    const int kv_end = p.causal ? min(len, q0 + QT) : len;
-    const int n = (kv_end + KT - 1) / KT;       // key steps of this tile (>= 1)
-
     auto bar = [&](int i) { return sbase + OFF_BAR + 8u * (uint32_t)i; };
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + OFF_BAR + 128);
-    volatile int *abort_word = reinterpret_cast<volatile int *>(smem + OFF_BAR + 136);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + OFF_BAR + 192);
+    volatile int *abort_word = reinterpret_cast<volatile int *>(smem + OFF_BAR + 200);
 
     if (threadIdx.x == 0) {
         mbar_init(bar(B_QFULL), 1);
+        mbar_init(bar(B_QEMPTY), 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(B_KFULL + s), 1);
             mbar_init(bar(B_KEMPTY + s), 1);
@@ -175,6 +198,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
         }
         mbar_init(bar(B_PFULL), 128);
         mbar_init(bar(B_PVDONE), 1);
+        mbar_init(bar(B_OFREE), 128);
         *abort_word = 0;
         fence_mbar_init();
         tma_prefetch_desc(&p.tm_q);
@@ -189,31 +213,40 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                                 // nothing above touched global memory
 
     if (warp == 0) {
         // ================================ TMA producer ================================
-        const int kv_head = head / p.group;
-        const int col = padded_column_of(p.seq_offsets, p.seq_lens, seq, lane);
         const bool leader = elect_one();
-        if (leader) {
-            mbar_expect_tx(bar(B_QFULL), Q_BYTES);
-            tma_load_2d(sbase + OFF_Q, &p.tm_q, bar(B_QFULL), head * 128, off + q0);
-            tma_load_2d(sbase + OFF_Q + Q_BYTES / 2, &p.tm_q, bar(B_QFULL), head * 128 + 64, off + q0);
-        }
-        for (int j = 0; j < n; ++j) {
-            const int s = j & 1;
-            const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-            if (!mbar_wait_warp(bar(B_KEMPTY + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) break;
+        uint32_t kv = 0, qi = 0;                // key steps loaded, items started
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+            ItemInfo it;
+            if (!decode_item(p, item, it)) continue;
+            const int kv_head = it.head / p.group;
+            const int col = p.vt_col[it.seq];
+            if (!mbar_wait_warp(bar(B_QEMPTY), (qi & 1u) ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) break;
             if (leader) {
-                const uint32_t dst = sbase + OFF_K + (uint32_t)s * K_BYTES;
-                mbar_expect_tx(bar(B_KFULL + s), K_BYTES);
-                tma_load_2d(dst, &p.tm_k, bar(B_KFULL + s), kv_head * 128, off + j * KT);
-                tma_load_2d(dst + K_BYTES / 2, &p.tm_k, bar(B_KFULL + s), kv_head * 128 + 64, off + j * KT);
+                mbar_expect_tx(bar(B_QFULL), Q_BYTES);
+                tma_load_2d(sbase + OFF_Q, &p.tm_q, bar(B_QFULL), it.head * 128, it.off + it.q0);
+                tma_load_2d(sbase + OFF_Q + Q_BYTES / 2, &p.tm_q, bar(B_QFULL), it.head * 128 + 64, it.off + it.q0);
             }
-            if (!mbar_wait_warp(bar(B_VEMPTY + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) break;
-            if (leader) {
-                mbar_expect_tx(bar(B_VFULL + s), V_BYTES);
-                tma_load_2d(sbase + OFF_V + (uint32_t)s * V_BYTES, &p.tm_vt, bar(B_VFULL + s), col + j * KT, kv_head * 128);
+            ++qi;
+            for (int j = 0; j < it.n; ++j, ++kv) {
+                const int s = (int)(kv & 1u);
+                const uint32_t ph = (kv >> 1) & 1u;
+                if (!mbar_wait_warp(bar(B_KEMPTY + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                if (leader) {
+                    const uint32_t dst = sbase + OFF_K + (uint32_t)s * K_BYTES;
+                    mbar_expect_tx(bar(B_KFULL + s), K_BYTES);
+                    tma_load_2d(dst, &p.tm_k, bar(B_KFULL + s), kv_head * 128, it.off + j * KT);
+                    tma_load_2d(dst + K_BYTES / 2, &p.tm_k, bar(B_KFULL + s), kv_head * 128 + 64, it.off + j * KT);
+                }
+                if (!mbar_wait_warp(bar(B_VEMPTY + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                if (leader) {
+                    mbar_expect_tx(bar(B_VFULL + s), V_BYTES);
+                    tma_load_2d(sbase + OFF_V + (uint32_t)s * V_BYTES, &p.tm_vt, bar(B_VFULL + s), col + j * KT, kv_head * 128);
+                }
             }
         }
     } else if (warp == 1) {
@@ -222,124 +255,159 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
         constexpr uint32_t idesc_s = idesc_bf16(128, KT);
         constexpr uint32_t idesc_o = idesc_bf16(128, 128);
         const uint32_t t_o = tmem_base + 128;
-        bool ok = mbar_wait_warp(bar(B_QFULL), 0u, abort_word, ST_TIMEOUT_ATTENTION);
-        for (int j = 0; ok && j <= n; ++j) {
-            if (j < n) {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                if (!mbar_wait_warp(bar(B_KFULL + s), ph, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
-                if (j >= 2 && !mbar_wait_warp(bar(B_SFREE + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
-                tc_fence_after();
-                if (leader) {
-                    const uint32_t kaddr = sbase + OFF_K + (uint32_t)s * K_BYTES;
+        uint32_t ks = 0, kp = 0, qi = 0;        // S products issued, P V products issued, items started
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+            ItemInfo it;
+            if (!decode_item(p, item, it)) continue;
+            if (!mbar_wait_warp(bar(B_QFULL), qi & 1u, abort_word, ST_TIMEOUT_ATTENTION)) break;
+            for (int j = 0; j <= it.n; ++j) {
+                if (j < it.n) {
+                    const int s = (int)(ks & 1u);
+                    const uint32_t ph = (ks >> 1) & 1u;
+                    if (!mbar_wait_warp(bar(B_KFULL + s), ph, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                    // the score buffer is free once the soft-max of the step two before has loaded it
+                    if (!mbar_wait_warp(bar(B_SFREE + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                    tc_fence_after();
+                    if (leader) {
+                        const uint32_t kaddr = sbase + OFF_K + (uint32_t)s * K_BYTES;
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const uint64_t adesc = smem_desc_sw128(sbase + OFF_Q + (uint32_t)(k >> 2) * (Q_BYTES / 2)) + (uint64_t)(((k & 3) * 32) >> 4);
-                        const uint64_t bdesc = smem_desc_sw128(kaddr + (uint32_t)(k >> 2) * (K_BYTES / 2)) + (uint64_t)(((k & 3) * 32) >> 4);
-                        umma_bf16(tmem_base + (uint32_t)s * KT, adesc, bdesc, idesc_s, k > 0 ? 1u : 0u);
+                        for (int k = 0; k < 8; ++k) {
+                            const uint64_t adesc = smem_desc_sw128(sbase + OFF_Q + (uint32_t)(k >> 2) * (Q_BYTES / 2)) + (uint64_t)(((k & 3) * 32) >> 4);
+                            const uint64_t bdesc = smem_desc_sw128(kaddr + (uint32_t)(k >> 2) * (K_BYTES / 2)) + (uint64_t)(((k & 3) * 32) >> 4);
+                            umma_bf16(tmem_base + (uint32_t)s * KT, adesc, bdesc, idesc_s, k > 0 ? 1u : 0u);
+                        }
+                        umma_commit(bar(B_KEMPTY + s));
+                        umma_commit(bar(B_SFULL + s));
+                        if (j == it.n - 1) umma_commit(bar(B_QEMPTY));      // last product that reads this Q tile
                     }
-                    umma_commit(bar(B_KEMPTY + s));
-                    umma_commit(bar(B_SFULL + s));
+                    ++ks;
                 }
-            }
-            if (j >= 1) {
-                const int i = j - 1, s = i & 1;
-                const uint32_t ph = (uint32_t)(i >> 1) & 1u;
-                if (!mbar_wait_warp(bar(B_VFULL + s), ph, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
-                if (!mbar_wait_warp(bar(B_PFULL), (uint32_t)i & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
-                tc_fence_after();
-                if (leader) {
-                    const uint64_t adesc0 = smem_desc_sw128(sbase + OFF_P);
-                    const uint64_t bdesc0 = smem_desc_sw128(sbase + OFF_V + (uint32_t)s * V_BYTES);
+                if (j >= 1) {
+                    const int s = (int)(kp & 1u);
+                    const uint32_t ph = (kp >> 1) & 1u;
+                    if (!mbar_wait_warp(bar(B_VFULL + s), ph, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar(B_PFULL), kp & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                    // the first product of an item overwrites the accumulator the previous item's result is read from
+                    if (j == 1 && !mbar_wait_warp(bar(B_OFREE), (qi & 1u) ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                    tc_fence_after();
+                    if (leader) {
+                        const uint64_t adesc0 = smem_desc_sw128(sbase + OFF_P);
+                        const uint64_t bdesc0 = smem_desc_sw128(sbase + OFF_V + (uint32_t)s * V_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(t_o, adesc0 + (uint64_t)((k * 32) >> 4), bdesc0 + (uint64_t)((k * 32) >> 4), idesc_o,
-                                  (i > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(bar(B_VEMPTY + s));
-                    umma_commit(bar(B_PVDONE));
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(t_o, adesc0 + (uint64_t)((k * 32) >> 4), bdesc0 + (uint64_t)((k * 32) >> 4), idesc_o,
+                                      (j > 1 || k > 0) ? 1u : 0u);
+                        umma_commit(bar(B_VEMPTY + s));
+                        umma_commit(bar(B_PVDONE));
+                    }
+                    ++kp;
                 }
             }
+            ++qi;
         }
     } else {
         // ================================ soft-max ====================================
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;               // query row of the tile = TMEM lane
-        const int row_g = q0 + row;                     // position within the sequence
         const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const int visible = p.causal ? min(len, row_g + 1) : len;     // keys [0, visible) count for this row
         const uint32_t p_row = sbase + OFF_P + (uint32_t)row * 128u;
         const float scale = p.scale_log2;
-        float m = -INFINITY, l = 0.0f;
+        uint32_t sc = 0, pv = 0;                        // key steps consumed, P V products of earlier items
         bool ok = true;
-        for (int j = 0; j < n; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait_warp(bar(B_SFULL + b), (uint32_t)(j >> 1) & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
-            tc_fence_after();
-            uint32_t sr[2][32];
-            tmem_ld_x32(t_row + (uint32_t)b * KT, sr[0]);
-            tmem_ld_x32(t_row + (uint32_t)b * KT + 32, sr[1]);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(bar(B_SFREE + b));
-            const int lim = visible - j * KT;           // columns [0, lim) of this step are visible
-            if (lim < KT) {
-#pragma unroll
-                for (int c = 0; c < KT; ++c)
-                    if (c >= lim) sr[c >> 5][c & 31] = 0xFF800000u;      // -inf
-            }
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < KT; ++c) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
-            const float m_new = fmaxf(m, mx * scale);
-            float alpha = 1.0f;
-            if (j == 0) {
-                m = m_new;
-            } else if (m_new - m > kRescaleThreshold) {
-                alpha = ex2(m - m_new);
-                m = m_new;
-            }
-            const bool rescale = __any_sync(0xFFFFFFFFu, alpha != 1.0f);
-            const float neg_m = -m;
-            float sum = 0.0f;
-            uint32_t pk[32];
-#pragma unroll
-            for (int c = 0; c < KT; c += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale, neg_m));
-                const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale, neg_m));
-                sum += p0 + p1;
-                pk[c >> 1] = pack2(p0, p1);
-            }
-            l = l * alpha + sum;
-            if (j >= 1) {
-                // P V of the previous step has to be complete before P is overwritten or O rescaled
-                if (!mbar_wait_warp(bar(B_PVDONE), (uint32_t)(j - 1) & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+        const bool dbg = p.dbg != nullptr && warp == 2 && lane == 0;
+        unsigned long long dsum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long tl = dbg ? clock64() : 0;
+        const long long t_begin = tl;
+#define ATT_DBG(i)                                   \
+    if (dbg) {                                       \
+        const long long t_ = clock64();              \
+        dsum[i] += (unsigned long long)(t_ - tl);    \
+        tl = t_;                                     \
+    }
+        for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+            ItemInfo it;
+            if (!decode_item(p, item, it)) continue;
+            ATT_DBG(7);
+            const int n = it.n, len = it.len, head = it.head, off = it.off;
+            const int row_g = it.q0 + row;                  // position within the sequence
+            const int visible = p.causal ? min(len, row_g + 1) : len;     // keys [0, visible) count for this row
+            float m = -INFINITY, l = 0.0f;
+            for (int j = 0; j < n; ++j, ++sc) {
+                const int b = (int)(sc & 1u);
+                if (!mbar_wait_warp(bar(B_SFULL + b), (sc >> 1) & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                ATT_DBG(1);
                 tc_fence_after();
-                if (rescale) {
-#pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint32_t o[32];
-                        tmem_ld_x32(t_row + 128 + (uint32_t)ch * 32, o);
-                        tmem_ld_wait();
+                uint32_t sr[2][32];
+                tmem_ld_x32(t_row + (uint32_t)b * KT, sr[0]);
+                tmem_ld_x32(t_row + (uint32_t)b * KT + 32, sr[1]);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(bar(B_SFREE + b));
+                const int lim = visible - j * KT;           // columns [0, lim) of this step are visible
+                if (lim < KT) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                        tmem_st_x32(t_row + 128 + (uint32_t)ch * 32, o);
-                    }
-                    tmem_st_wait();
+                    for (int c = 0; c < KT; ++c)
+                        if (c >= lim) sr[c >> 5][c & 31] = 0xFF800000u;      // -inf
                 }
-            }
+                float mx = -INFINITY;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                const uint32_t dst = p_row + (uint32_t)((ch ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * ch]), "r"(pk[4 * ch + 1]),
-                             "r"(pk[4 * ch + 2]), "r"(pk[4 * ch + 3])
-                             : "memory");
+                for (int c = 0; c < KT; ++c) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
+                const float m_new = fmaxf(m, mx * scale);
+                float alpha = 1.0f;
+                if (j == 0) {
+                    m = m_new;
+                } else if (m_new - m > kRescaleThreshold) {
+                    alpha = ex2(m - m_new);
+                    m = m_new;
+                }
+                const bool rescale = __any_sync(0xFFFFFFFFu, alpha != 1.0f);
+                const float neg_m = -m;
+                float sum = 0.0f;
+                uint32_t pk[32];
+#pragma unroll
+                for (int c = 0; c < KT; c += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale, neg_m));
+                    sum += p0 + p1;
+                    pk[c >> 1] = pack2(p0, p1);
+                }
+                l = l * alpha + sum;
+                ATT_DBG(2);
+                if (j >= 1) {
+                    // P V of the previous step has to be complete before P is overwritten or O rescaled
+                    if (!mbar_wait_warp(bar(B_PVDONE), (pv + (uint32_t)j - 1u) & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+                    tc_fence_after();
+                    if (rescale) {
+#pragma unroll 1
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t o[32];
+                            tmem_ld_x32(t_row + 128 + (uint32_t)ch * 32, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                            tmem_st_x32(t_row + 128 + (uint32_t)ch * 32, o);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                ATT_DBG(3);
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t dst = p_row + (uint32_t)((ch ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * ch]), "r"(pk[4 * ch + 1]),
+                                 "r"(pk[4 * ch + 2]), "r"(pk[4 * ch + 3])
+                                 : "memory");
+                }
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(bar(B_PFULL));
+                ATT_DBG(4);
             }
-            fence_proxy_async_smem();
-            tc_fence_before();
-            mbar_arrive(bar(B_PFULL));
-        }
-        if (ok) ok = mbar_wait_warp(bar(B_PVDONE), (uint32_t)(n - 1) & 1u, abort_word, ST_TIMEOUT_ATTENTION);
-        if (ok) {
+            if (!ok) break;
+            if (!mbar_wait_warp(bar(B_PVDONE), (pv + (uint32_t)n - 1u) & 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
+            ATT_DBG(5);
+            pv += (uint32_t)n;
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const size_t grow = (size_t)(off + row_g);                 // row of the token in q / k / v / out
@@ -350,7 +418,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                     uint32_t o[32];
                     tmem_ld_x32(t_row + 128 + (uint32_t)ch * 32, o);
                     tmem_ld_wait();
-                    if (row_g < len) {
+                    if (ch == 3) {                              // the accumulator may be overwritten by the next item
+                        tc_fence_before();
+                        mbar_arrive(bar(B_OFREE));
+                    }
+                    if (row_g < len && !p.dbg_no_store) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             uint4 w;
@@ -371,6 +443,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                     uint32_t o[32];
                     tmem_ld_x32(t_row + 128 + (uint32_t)ch * 32, o);
                     tmem_ld_wait();
+                    if (ch == 3) {
+                        tc_fence_before();
+                        mbar_arrive(bar(B_OFREE));
+                    }
                     uint32_t pk[4];
 #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {
@@ -392,6 +468,12 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                     *reinterpret_cast<uint32_t *>(sf0 + 512) = sf_hi;           // next 64-column chunk
                 }
             }
+            ATT_DBG(6);
+        }
+#undef ATT_DBG
+        if (dbg) {
+            dsum[0] = (unsigned long long)(clock64() - t_begin);
+            for (int i = 0; i < 8; ++i) p.dbg[(size_t)blockIdx.x * 8 + i] = dsum[i];
         }
     }
 
@@ -458,6 +540,10 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     p.num_q_heads = num_q_heads;
     p.group = num_q_heads / num_kv_heads;
     p.q_tiles = (max_seq_len + QT - 1) / QT;
+    p.num_seqs = num_seqs;
+    p.total_items = p.q_tiles * num_q_heads * num_seqs;
+    int *vt_col = (int *)workspace_slot(33, (size_t)num_seqs * sizeof(int));
+    p.vt_col = vt_col;
     p.causal = causal ? 1 : 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)head_dim);
     p.q_packed = q_packed;
@@ -467,10 +553,38 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     p.q_inv_in = q_packed != nullptr ? 1.0f / q_input_scale : 0.0f;
 
     const dim3 tgrid((max_seq_len + 63) / 64, num_kv_heads, num_seqs);
-    launch_chained(transpose_v_kernel, tgrid, dim3(256), (size_t)0, st, vt, vt_cols, v, ldv, seq_offsets, seq_lens, p.status);
+    launch_chained(transpose_v_kernel, tgrid, dim3(256), (size_t)0, st, vt, vt_cols, v, ldv, seq_offsets, seq_lens, vt_col, p.status);
     note_launches(1);
-    const dim3 grid(num_q_heads * num_seqs, p.q_tiles, 1);
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+    }
+    const dim3 grid(p.total_items < 2 * num_sms ? p.total_items : 2 * num_sms, 1, 1);
+    static int debug = -1;
+    if (debug < 0) {
+        const char *e = getenv("GLMASR_ATTN_DEBUG");
+        debug = (e != nullptr && e[0] >= '1' && e[0] <= '2') ? e[0] - '0' : 0;
+    }
+    p.dbg_no_store = debug == 2 ? 1 : 0;
+    if (debug) {
+        p.dbg = (unsigned long long *)workspace_slot(34, (size_t)grid.x * 8 * sizeof(unsigned long long));
+        cudaMemsetAsync(p.dbg, 0, (size_t)grid.x * 8 * sizeof(unsigned long long), st);
+    }
     launch_chained(prefill_attention_umma_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, st, p);
+    if (debug) {
+        // timing experiment: where the soft-max warps of every CTA spent their cycles (averages over the CTAs)
+        std::vector<unsigned long long> h((size_t)grid.x * 8);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h.data(), p.dbg, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+        double avg[8] = {0};
+        for (unsigned c = 0; c < grid.x; ++c)
+            for (int i = 0; i < 8; ++i) avg[i] += (double)h[(size_t)c * 8 + i] / grid.x;
+        fprintf(stderr, "attention cycles per CTA: loop %.0f | wait S %.0f, soft-max %.0f, wait PV+rescale %.0f, write P %.0f, "
+                        "last PV %.0f, result %.0f, item set-up %.0f\n",
+                avg[0], avg[1], avg[2], avg[3], avg[4], avg[5], avg[6], avg[7]);
+    }
     return true;
 }
 

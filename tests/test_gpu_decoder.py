@@ -162,6 +162,13 @@ def test_rmsnorm_quant_equals_norm_then_quantiser(ops, rows, dim):
     """rmsnorm + quantiser in one launch = rmsnorm, then the stand-alone quantiser, then the scale re-tiling."""
     rng = np.random.default_rng(rows + dim)
     x, w = rnd_bits(rng, (rows, dim), 3.0), rnd_bits(rng, (dim,), 1.0)
+    if rows >= 8:
+        # operands the fast exact division of the many-row kernel must hand to the ordinary one, a row of
+        # zeros (rms = sqrt(eps)), and rows whose scale makes rms tiny or huge
+        x[3, :8] = np.array([0x8000, 0x0000, 0x0001, 0x8001, 0x0080, 0x1000, 0x9000, 0x0C00], dtype=np.uint16)
+        x[4, :] = 0
+        x[5, :] = o.f32_to_bf16_bits((rng.standard_normal(dim) * 1e-14).astype(np.float32))
+        x[6, :] = o.f32_to_bf16_bits((rng.standard_normal(dim) * 1e13).astype(np.float32))
     isc = 0.003
     normed = ops.rmsnorm(to_dev_bf16(x), to_dev_bf16(w))
     pk, sc = ops.quantize_bf16_to_fp4(normed, isc)
