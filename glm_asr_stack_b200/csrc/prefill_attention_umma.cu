@@ -411,32 +411,50 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const size_t grow = (size_t)(off + row_g);                 // row of the token in q / k / v / out
+            // The result leaves through the warp's own 32 rows of the P tile (free once the last P V has
+            // completed; the next item's P is written by the same warp after this), so that global stores
+            // cover whole 128-byte (bf16) or 64-byte (quantised) row segments instead of 16 bytes per row.
+            const int wrow0 = quad * 32;                               // first tile row of this warp
+            const uint32_t stage = sbase + OFF_P + (uint32_t)wrow0 * 128u;
             if (p.q_packed == nullptr) {
-                __nv_bfloat16 *orow = p.out + grow * p.ldo + (size_t)head * 128;
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t o[32];
-                    tmem_ld_x32(t_row + 128 + (uint32_t)ch * 32, o);
-                    tmem_ld_wait();
-                    if (ch == 3) {                              // the accumulator may be overwritten by the next item
-                        tc_fence_before();
-                        mbar_arrive(bar(B_OFREE));
-                    }
-                    if (row_g < len && !p.dbg_no_store) {
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        uint32_t o[32];
+                        tmem_ld_x32(t_row + 128 + (uint32_t)(half * 64 + c2 * 32), o);
+                        tmem_ld_wait();
+                        if (half == 1 && c2 == 1) {                    // the accumulator may be overwritten by the next item
+                            tc_fence_before();
+                            mbar_arrive(bar(B_OFREE));
+                        }
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            uint4 w;
-                            w.x = pack2(__uint_as_float(o[8 * e + 0]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
-                            w.y = pack2(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
-                            w.z = pack2(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
-                            w.w = pack2(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
-                            *reinterpret_cast<uint4 *>(orow + ch * 32 + e * 8) = w;
+                            const uint32_t w0 = pack2(__uint_as_float(o[8 * e + 0]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
+                            const uint32_t w1 = pack2(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
+                            const uint32_t w2 = pack2(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
+                            const uint32_t w3 = pack2(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
+                            const uint32_t dst = stage + (uint32_t)lane * 128u + (uint32_t)(((c2 * 4 + e) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
                         }
                     }
+                    __syncwarp();
+                    if (!p.dbg_no_store) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = i * 4 + (lane >> 3), c = lane & 7;       // row of the warp, 16-byte chunk
+                            uint4 w;
+                            const uint32_t src = stage + (uint32_t)r * 128u + (uint32_t)((c ^ (r & 7)) << 4);
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(src));
+                            const int rg = it.q0 + wrow0 + r;
+                            if (rg < len)
+                                *reinterpret_cast<uint4 *>(p.out + (size_t)(off + rg) * p.ldo + (size_t)head * 128 + half * 64 + c * 8) = w;
+                        }
+                    }
+                    __syncwarp();
                 }
             } else {
                 // a row of one head is eight 16-element blocks of the quantiser: 64 packed bytes, 8 scale bytes
-                uint8_t *qrow = p.q_packed + grow * p.q_ld + (size_t)head * 64;
                 uint32_t sf_lo = 0u, sf_hi = 0u;
 #pragma unroll 1
                 for (int ch = 0; ch < 4; ++ch) {
@@ -459,8 +477,21 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                         if (ch < 2) sf_lo |= byte;
                         else sf_hi |= byte;
                     }
-                    if (row_g < len) *reinterpret_cast<uint4 *>(qrow + ch * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    // 64 staged bytes per row; the chunk position is swizzled by the row pair
+                    const uint32_t dst = stage + (uint32_t)lane * 64u + (uint32_t)((ch ^ ((lane >> 1) & 3)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
                 }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = i * 8 + (lane >> 2), c = lane & 3;
+                    uint4 w;
+                    const uint32_t src = stage + (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) << 4);
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(src));
+                    const int rg = it.q0 + wrow0 + r;
+                    if (rg < len) *reinterpret_cast<uint4 *>(p.q_packed + (size_t)(off + rg) * p.q_ld + (size_t)head * 64 + c * 16) = w;
+                }
+                __syncwarp();
                 if (row_g < len) {
                     const int rem = (int)(grow & 127);
                     uint8_t *sf0 = p.q_sf + ((((grow >> 7) * p.q_sf_chunks + (size_t)(head * 2)) * 32 + (rem & 31)) * 4 + (rem >> 5)) * 4;
