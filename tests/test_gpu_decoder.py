@@ -323,6 +323,8 @@ def test_prefill_attention_vs_oracle(qh, kvh, causal):
     ([513, 64, 300], False, 1.0),
     ([448, 394, 200], True, 6.0),                 # wide score range: the running maximum keeps jumping
     ([300, 257], False, 6.0),
+    ([5, 0, 70, 0, 129], True, 1.0),              # empty sequences inside the batch
+    ([3] * 150, True, 1.0),                       # more sequences than a CTA walks items for, one key step each
 ])
 def test_prefill_attention_long_and_wide_range(ops, lens, causal, q_scale):
     """Longer sequences (up to 16 key steps per query tile) and scores whose range forces the accumulator
