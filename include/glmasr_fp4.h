@@ -131,7 +131,10 @@ void decoder_prefill_paged_batched(void *handle, const void *ws, uint16_t *hidde
 /* The attention plug-in's entry points (Infer-engine/cuda/flash_fwd_vllm.h:21-30) served by this library:
  * variable-length GQA self-attention, head_dim 128, q / k / v rows of sequence s at
  * [d_cu_seqlens[s], d_cu_seqlens[s+1]) with the given row strides (elements), out dense
- * [total_seqlen, q_heads*head_dim].  Returns 1 on success, 0 otherwise, like the plug-in. */
+ * [total_seqlen, q_heads*head_dim].  Returns 1 on success, 0 otherwise, like the plug-in.  With 16-byte aligned
+ * pointers and row strides that are multiples of 8 elements it runs on the tcgen05 tensor cores (TMA-staged tiles,
+ * accumulators in tensor memory; total_seqlen must cover every row the table points at); other layouts run on a
+ * warp-level MMA kernel with the same results up to rounding. */
 int flash_fwd_vllm_gqa_available(void);
 int flash_fwd_vllm_gqa_launch(void *q, void *k, void *v, void *out, int total_seqlen, int max_seqlen, int q_heads,
                               int kv_heads, int head_dim, int q_row_stride, int k_row_stride, int v_row_stride,
