@@ -557,7 +557,7 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
         configured = true;
     }
     const int vt_cols = (total_tokens + 64 * num_seqs + 63) & ~63;
-    __nv_bfloat16 *vt = (__nv_bfloat16 *)workspace_slot(32, (size_t)num_kv_heads * 128 * (size_t)vt_cols * 2);
+    __nv_bfloat16 *vt = (__nv_bfloat16 *)workspace_slot(WS_ATTN_VT, (size_t)num_kv_heads * 128 * (size_t)vt_cols * 2);
     AttnParams p;
     memset(&p, 0, sizeof(p));
     if (!make_bf16_tmap_sw128(&p.tm_q, q, (uint64_t)num_q_heads * 128, (uint64_t)total_tokens, (uint64_t)ldq * 2, 64, 128)) return false;
@@ -573,7 +573,7 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     p.q_tiles = (max_seq_len + QT - 1) / QT;
     p.num_seqs = num_seqs;
     p.total_items = p.q_tiles * num_q_heads * num_seqs;
-    int *vt_col = (int *)workspace_slot(33, (size_t)num_seqs * sizeof(int));
+    int *vt_col = (int *)workspace_slot(WS_ATTN_VT_COL, (size_t)num_seqs * sizeof(int));
     p.vt_col = vt_col;
     p.causal = causal ? 1 : 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)head_dim);
@@ -600,7 +600,7 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     }
     p.dbg_no_store = debug == 2 ? 1 : 0;
     if (debug) {
-        p.dbg = (unsigned long long *)workspace_slot(34, (size_t)grid.x * 8 * sizeof(unsigned long long));
+        p.dbg = (unsigned long long *)workspace_slot(WS_ATTN_DEBUG, (size_t)grid.x * 8 * sizeof(unsigned long long));
         cudaMemsetAsync(p.dbg, 0, (size_t)grid.x * 8 * sizeof(unsigned long long), st);
     }
     launch_chained(prefill_attention_umma_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, st, p);

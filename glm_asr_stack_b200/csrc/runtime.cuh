@@ -17,6 +17,8 @@ cudaStream_t current_stream();
 int *device_status_word();          // device pointer, 4 ints, zero-initialised; allocated on first use
 void *workspace(size_t bytes);      // grow-only private device workspace (slot 0)
 void *workspace_slot(int slot, size_t bytes);
+// Slots owned outside api.cu / decoder_step.cu (those two number their own, 0..31).
+enum : int { WS_ATTN_VT = 32, WS_ATTN_VT_COL = 33, WS_ATTN_DEBUG = 34 };
 void free_all_private_state();
 void note_launches(int n);          // launch accounting for kernels started outside api.cu
 size_t tiled_scale_bytes(int rows, int K);

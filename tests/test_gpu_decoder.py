@@ -345,6 +345,31 @@ def test_prefill_attention_long_and_wide_range(ops, lens, causal, q_scale):
         assert o.rel_err(got[off:off + ln], want[off:off + ln]) <= REL_TOL_TIGHT
 
 
+def test_prefill_attention_unaligned_q_takes_the_warp_level_kernel(ops):
+    """A q matrix that starts 4 bytes into a 16-byte unit (and has an odd-multiple-of-2 row stride) cannot be read
+    through a TMA descriptor; the call must still succeed (on the warp-level kernel) and agree with the oracle
+    and, to rounding, with the aligned call."""
+    from glm_asr_stack_b200 import engine
+    rng = np.random.default_rng(91)
+    qh, kvh, hd = 8, 2, 128
+    lens = [130, 64, 7]
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T, H, KV = int(offs[-1]), qh * hd, kvh * hd
+    qkv = rnd_bits(rng, (T, H + 2 * KV))
+    dev = to_dev_bf16(qkv)
+    wide = torch.zeros((T, H + 6), dtype=torch.bfloat16, device="cuda")     # row stride H + 6: not a multiple of 8
+    wide[:, 2:2 + H] = dev[:, :H]
+    q_shifted = wide[:, 2:2 + H]
+    assert q_shifted.data_ptr() % 16 == 4
+    cu = torch.from_numpy(offs).cuda()
+    got = bits_of(engine.prefill_attention(q_shifted, dev[:, H:H + KV], dev[:, H + KV:], cu, max(lens), qh, kvh, hd, True))
+    assert ops.status() == 0
+    want = do.prefill_attention(qkv[:, :H], qkv[:, H:H + KV], qkv[:, H + KV:], offs[:-1], lens, qh, kvh, hd, True)
+    assert o.rel_err(got, want) <= REL_TOL_TIGHT
+    ref = bits_of(engine.prefill_attention(dev[:, :H], dev[:, H:H + KV], dev[:, H + KV:], cu, max(lens), qh, kvh, hd, True))
+    assert o.rel_err(got, ref) <= REL_TOL_TIGHT
+
+
 def test_prefill_attention_sequences_with_gaps(ops):
     """Sequences given by offsets + lengths semantics of the plug-in (cumulative table) whose rows are separated
     by rows of other data: rows outside every sequence must be left untouched, rows inside must not see them."""
