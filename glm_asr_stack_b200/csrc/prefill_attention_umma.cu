@@ -49,7 +49,8 @@ constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + 2 * K_BYTES;
 constexpr int OFF_P = OFF_V + 2 * V_BYTES;
 constexpr int OFF_BAR = OFF_P + P_BYTES;      // 112 KB of tiles, then barriers
-constexpr int SMEM_BYTES = OFF_BAR + 256;
+constexpr int OFF_OS_TABLE = OFF_BAR + 256;  // 128 floats: the quantiser's second division, one entry per scale byte
+constexpr int SMEM_BYTES = OFF_OS_TABLE + 512;
 constexpr int TMEM_COLS = 256;                // S0 [0,64), S1 [64,128), O [128,256)
 constexpr int THREADS = 192;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units
@@ -209,6 +210,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
         tmem_alloc(smem_u32((const void *)tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
+    float *os_table = reinterpret_cast<float *>(smem + OFF_OS_TABLE);
+    if (p.q_packed != nullptr) fill_os_table(os_table, p.q_inv_in, (int)threadIdx.x, (int)blockDim.x);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -472,7 +475,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
 #pragma unroll
                         for (int e = 0; e < 16; ++e)
                             v[e] = __bfloat162float(__float2bfloat16(__uint_as_float(o[16 * hb + e]) * inv));
-                        const uint32_t sf = quantize_block16(v, p.q_inv_in, pk[2 * hb], pk[2 * hb + 1]);
+                        const uint32_t sf = quantize_block16_lut(v, p.q_inv_in, os_table, pk[2 * hb], pk[2 * hb + 1]);
                         const uint32_t byte = (sf & 0xFFu) << (8 * (2 * (ch & 1) + hb));
                         if (ch < 2) sf_lo |= byte;
                         else sf_hi |= byte;
