@@ -8,6 +8,7 @@
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "elementwise.cuh"
 #include "fp4_format.cuh"
@@ -140,11 +141,81 @@ __global__ void quantize_act_kernel(uint8_t *__restrict__ packed_out, uint8_t *_
     if (scale_swizzled) scale_swizzled[swizzled_sf_index(r, b, (blocks_per_row + 3) >> 2)] = (uint8_t)s8;
 }
 
+// The same quantiser for the common prefill case (no pre-scale, K a multiple of 2048, thousands of rows): a warp
+// takes 2048 consecutive elements of a row, reads them once with coalesced 16-byte loads into a private strip of
+// shared memory (128-byte lines 144 bytes apart: conflict-free both ways), and every lane then quantises line
+// `lane`, i.e. four consecutive blocks: 32 contiguous output bytes and one aligned 4-byte group of scales per lane
+// instead of four 8-byte and four 1-byte stores.  Same bytes as quantize_act_kernel.
+constexpr int kQuantStrip = 32 * 144;
+__global__ void __launch_bounds__(256) quantize_act_strip_kernel(uint8_t *__restrict__ packed_out, uint8_t *__restrict__ scale_rowmajor,
+                                                                uint8_t *__restrict__ scale_swizzled,
+                                                                const __nv_bfloat16 *__restrict__ x, float inv_in, int M, int K,
+                                                                int ldx) {
+    __shared__ __align__(16) uint8_t strips[8 * kQuantStrip];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int segs = K >> 11;                                   // 2048-element segments per row
+    const long long unit = (long long)blockIdx.x * 8 + wib;
+    if (unit >= (long long)M * segs) return;
+    const int r = (int)(unit / segs), seg = (int)(unit % segs);
+    uint8_t *rs = strips + wib * kQuantStrip;
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)r * ldx + (size_t)seg * 2048);
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = src[k * 32 + lane];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int byte = 512 * k + 16 * lane;
+            *reinterpret_cast<uint4 *>(rs + byte + (byte >> 7) * 16) = v[k];
+        }
+    }
+    __syncwarp();
+    const int blocks_per_row = K >> 4;
+    const int b0 = seg * 128 + 4 * lane;                        // first of this lane's four blocks
+    const uint8_t *line = rs + lane * 144;
+    uint32_t packed[8], sfw = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float v[16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 xv = *reinterpret_cast<const uint4 *>(line + (2 * k + h) * 16);
+            const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[8 * h + 2 * j] = __uint_as_float(xs[j] << 16);
+                v[8 * h + 2 * j + 1] = __uint_as_float(xs[j] & 0xFFFF0000u);
+            }
+        }
+        const uint32_t s8 = quantize_block16(v, inv_in, packed[2 * k], packed[2 * k + 1]);
+        sfw |= (s8 & 0xFFu) << (8 * k);
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(packed_out + (size_t)r * (K >> 1) + (size_t)b0 * 8);
+    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    if (scale_rowmajor) *reinterpret_cast<uint32_t *>(scale_rowmajor + (size_t)r * blocks_per_row + b0) = sfw;
+    if (scale_swizzled) *reinterpret_cast<uint32_t *>(scale_swizzled + swizzled_sf_index(r, b0, (blocks_per_row + 3) >> 2)) = sfw;
+}
+
 void launch_quantize_act(uint8_t *packed_out, uint8_t *scale_rowmajor, uint8_t *scale_swizzled,
                          const __nv_bfloat16 *x, const __nv_bfloat16 *pre, float input_scale, int M, int K,
                          int ldx, cudaStream_t st) {
     const long long total = (long long)M * (K / 16);
     if (total <= 0) return;
+    static int strip = -1;
+    if (strip < 0) {
+        const char *e = getenv("GLMASR_QUANT_STRIP");
+        strip = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (strip && pre == nullptr && M >= 1024 && (K % 2048) == 0 && (ldx % 8) == 0 &&
+        (((uintptr_t)x | (uintptr_t)packed_out) & 15) == 0 && (((uintptr_t)scale_rowmajor | (uintptr_t)scale_swizzled) & 3) == 0) {
+        const long long units = (long long)M * (K / 2048);
+        launch_chained(quantize_act_strip_kernel, dim3(blocks_for(units, 8)), dim3(256), 0, st, packed_out, scale_rowmajor,
+                       scale_swizzled, x, 1.0f / input_scale, M, K, ldx);
+        return;
+    }
     GLMASR_PREFER_MAX_SMEM(quantize_act_kernel);
     launch_chained(quantize_act_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, st, packed_out, scale_rowmajor, scale_swizzled, x, pre,
                                                                 1.0f / input_scale, M, K, ldx);

@@ -40,7 +40,8 @@ def test_dequant_odd_column_count(ops):
     assert np.array_equal(bits_of(out), o.f32_to_bf16_bits(want))
 
 
-@pytest.mark.parametrize("M,K,with_pre", [(1, 16, False), (17, 64, True), (129, 2048, False), (300, 512, True)])
+@pytest.mark.parametrize("M,K,with_pre", [(1, 16, False), (17, 64, True), (129, 2048, False), (300, 512, True),
+                                          (1100, 2048, False), (1030, 4096, False), (1025, 2048, True)])
 def test_activation_quantiser_bit_exact(ops, M, K, with_pre):
     x = o.seeded_activation(M, K, 5)
     xf = o.bf16_bits_to_f32(x)
