@@ -26,10 +26,20 @@ namespace glmasr {
 static cudaStream_t g_stream = nullptr;
 static int *g_status = nullptr;
 static long long g_launches = 0;
-static int g_num_sms = 0;
-static bool g_umma_ready = false;
-static bool g_pair16_ready = false;
-static bool g_pair_ready = false;
+// Per-device facts and one-time set-up (the large shared-memory opt-in is an attribute of the kernel ON a
+// device): indexed by the current device, so a process that drives several GPUs sets each one up.
+static constexpr int kMaxDevices = 64;
+static int g_num_sms[kMaxDevices] = {0};
+static bool g_umma_ready[kMaxDevices] = {false};
+static bool g_pair16_ready[kMaxDevices] = {false};
+static bool g_pair_ready[kMaxDevices] = {false};
+
+static int current_device() {
+    int dev = 0;
+    GLMASR_CUDA_CHECK(cudaGetDevice(&dev));
+    GLMASR_CHECK(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+    return dev;
+}
 
 // optional per-launch timing of the GEMM kernel (CUDA events on the launching stream)
 static bool g_profile = false;
@@ -125,12 +135,10 @@ enum Slot : int {
 };
 
 static int num_sms() {
-    if (g_num_sms == 0) {
-        int dev = 0;
-        GLMASR_CUDA_CHECK(cudaGetDevice(&dev));
-        GLMASR_CUDA_CHECK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-    }
-    return g_num_sms;
+    const int dev = current_device();
+    if (g_num_sms[dev] == 0)
+        GLMASR_CUDA_CHECK(cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+    return g_num_sms[dev];
 }
 
 // rows from which W4A16 dequantises each weight once instead of inside the GEMM
@@ -144,6 +152,7 @@ static int w4a16_dequant_once_rows() {
     return v;
 }
 
+#ifdef GLMASR_EXPERIMENTS
 static int g_debug_override = -1;           // glmasr_debug_set_flags: timing experiments from the host language
 static int debug_flags() {
     static int v = -1;
@@ -152,6 +161,19 @@ static int debug_flags() {
         v = (e && e[0]) ? atoi(e) : 0;
     }
     return g_debug_override >= 0 ? g_debug_override : v;
+}
+#else
+static int debug_flags() { return 0; }
+#endif
+
+// GLMASR_FORCE_NB=1/2: 128-row weight sub-tiles per CTA tile of the single-CTA kernel (comparison runs); 0 = per shape
+static int forced_nb() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_FORCE_NB");
+        v = (e && e[0]) ? (atoi(e) == 1 ? 1 : 2) : 0;
+    }
+    return v;
 }
 
 // GLMASR_PAIR_KERNEL=0 keeps W4A4 on the single-CTA kernel (comparison runs)
@@ -482,9 +504,10 @@ static int run_fused(const FusedArgs &a) {
         return run_fused(b);
     }
 
-    if (!g_umma_ready) {
+    const int dev = current_device();
+    if (!g_umma_ready[dev]) {
         GLMASR_CUDA_CHECK(umma_gemm_init());
-        g_umma_ready = true;
+        g_umma_ready[dev] = true;
     }
 
     GemmParams p;
@@ -498,7 +521,9 @@ static int run_fused(const FusedArgs &a) {
     p.epi = a.epi;
     p.status = device_status_word();
     p.debug = debug_flags();
+#ifdef GLMASR_EXPERIMENTS
     p.dbg_cycles = (p.debug & 64) ? (unsigned long long *)workspace_slot(WS_DBG, 148 * 16 * 8 * 4) : nullptr;
+#endif
     p.num_m_tiles = (a.M + 127) / 128;
     p.n_out = total_out_cols(a);
     // W4A4 weights and their re-tiled scales are read-only for every kernel that signals its dependents early:
@@ -584,9 +609,9 @@ static int run_fused(const FusedArgs &a) {
         const int m_pairs = (p.num_m_tiles + 1) / 2;
         const int pairs = num_sms() / 2;
         if (m_pairs * n_tiles >= pairs && a.M >= 512) {
-            if (!g_pair_ready) {
+            if (!g_pair_ready[dev]) {
                 GLMASR_CUDA_CHECK(umma_gemm_pair_init());
-                g_pair_ready = true;
+                g_pair_ready[dev] = true;
             }
             p.num_n_tiles = n_tiles;
             // epilogue through shared memory + bulk tensor stores when the output can be described to TMA
@@ -628,9 +653,9 @@ static int run_fused(const FusedArgs &a) {
                 cudaEventRecord(tl.start, g_stream);
             }
             if (wide) {
-                if (!g_pair16_ready) {
+                if (!g_pair16_ready[dev]) {
                     GLMASR_CUDA_CHECK(umma_gemm_pair16_init());
-                    g_pair16_ready = true;
+                    g_pair16_ready[dev] = true;
                 }
                 if (launch_umma_gemm_pair16(p, pairs, g_stream) != cudaSuccess) return -1;
             } else if (launch_umma_gemm_pair(p, pairs, g_stream) != cudaSuccess) {
@@ -662,7 +687,7 @@ static int run_fused(const FusedArgs &a) {
     } else {
         const int tiles2 = p.num_m_tiles * ((subtiles + 1) / 2);
         nb = (subtiles >= 2 && tiles2 >= num_sms()) ? 2 : 1;
-        if (getenv("GLMASR_FORCE_NB") != nullptr) nb = atoi(getenv("GLMASR_FORCE_NB")) == 1 ? 1 : 2;   // experiments
+        if (forced_nb() != 0) nb = forced_nb();
         p.num_n_tiles = (subtiles + nb - 1) / nb;
     }
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
@@ -743,6 +768,32 @@ int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, cons
     a.q_out_sf = q_out_sf;
     a.q_out_input_scale = q_out_input_scale;
     if (ldo < total_out_cols(a)) return -1;
+    return run_fused(a);
+}
+
+// gate|up as one W4A16 GEMM (the arithmetic of the reference's fused pair, Infer-engine/cuda/decoder.cu:923-978)
+// whose SiLU-gate epilogue writes the quantised operand of a following W4A4 GEMM (e2m1 bytes [M, N/2] + tiled
+// scales, quantiser input scale q_out_input_scale) instead of the bf16 activation: the same bytes as
+// silu_mul_split_packed followed by the activation quantiser.  Tensor-core path only; -1 when the shape cannot take it.
+int fp4_linear_w4a16_silu_quantized(uint8_t *q_out, uint8_t *q_out_sf, float q_out_input_scale, const uint16_t *x, int ldx,
+                                    const glmasr_fp4_weight *gate_up, int M, int K) {
+    if (q_out == nullptr || q_out_sf == nullptr || x == nullptr || gate_up == nullptr || !(q_out_input_scale > 0.0f)) return -1;
+    if (gate_up[0].w_scales == nullptr || gate_up[1].w_scales == nullptr || gate_up[0].N != gate_up[1].N || ldx < K) return -1;
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = GEMM_W4A16;
+    a.out = nullptr;                 // the epilogue writes q_out only
+    a.ldo = gate_up[0].N;
+    a.x = (const __nv_bfloat16 *)x;
+    a.ldx = ldx;
+    a.w = gate_up;
+    a.num_w = 2;
+    a.epi = EPI_SILU_GATE;
+    a.M = M;
+    a.K = K;
+    a.q_out = q_out;
+    a.q_out_sf = q_out_sf;
+    a.q_out_input_scale = q_out_input_scale;
     return run_fused(a);
 }
 
@@ -1123,9 +1174,12 @@ static constexpr size_t kNoAllocXq = (size_t)kNoAllocMaxM * kNoAllocMaxK / 2;   
 static constexpr size_t kNoAllocXsf = (size_t)(kNoAllocMaxM / 128) * (kNoAllocMaxK / 64) * 512;  // 256 KiB
 static constexpr size_t kNoAllocWsf = (size_t)(kNoAllocMaxWeight / 16);                          // 2 MiB
 static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocXq + kNoAllocXsf + kNoAllocWsf];
+// Status word of this entry point's kernels (a bounded wait that ran out records its code here).  It cannot
+// share the library's ordinary status word, which is allocated on first use; glmasr_fp4_status reads both.
+static __device__ int g_noalloc_status[4];
 
-static constexpr int kMaxDevices = 64;
 static uint8_t *g_noalloc_ptr[kMaxDevices] = {nullptr};
+static int *g_noalloc_status_ptr[kMaxDevices] = {nullptr};
 
 // Device address of the scratch array on the current device.  The array's name is only a
 // host-side handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
@@ -1139,13 +1193,20 @@ static uint8_t *noalloc_scratch_for_current_device() {
             fprintf(stderr, "glmasr_nvfp4_linear_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
             return nullptr;
         }
-        g_noalloc_ptr[dev] = (uint8_t *)ptr;
-        if (!g_umma_ready) {
+        void *sptr = nullptr;
+        const cudaError_t e2 = cudaGetSymbolAddress(&sptr, g_noalloc_status);
+        if (e2 != cudaSuccess) {
+            fprintf(stderr, "glmasr_nvfp4_linear_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e2));
+            return nullptr;
+        }
+        if (!g_umma_ready[dev]) {           // the kernels' shared-memory opt-in is per device
             if (umma_gemm_init() != cudaSuccess) return nullptr;
-            g_umma_ready = true;
+            g_umma_ready[dev] = true;
         }
         (void)num_sms();
         (void)encode_fn();
+        g_noalloc_status_ptr[dev] = (int *)sptr;
+        g_noalloc_ptr[dev] = (uint8_t *)ptr;
     }
     return g_noalloc_ptr[dev];
 }
@@ -1188,7 +1249,7 @@ extern "C" int glmasr_nvfp4_linear_noalloc(uint16_t *out, const uint16_t *x, con
     p.out = (__nv_bfloat16 *)out;
     p.ldo = N;
     p.epi = EPI_STORE;
-    p.status = nullptr;
+    p.status = g_noalloc_status_ptr[current_device()];
     p.num_m_tiles = (M + 127) / 128;
     p.n_out = N;
     p.num_segs = 1;
@@ -1218,18 +1279,29 @@ extern "C" int glmasr_nvfp4_linear_noalloc(uint16_t *out, const uint16_t *x, con
 extern "C" int glmasr_fp4_status(void) {
     int host[4] = {0, 0, 0, 0};
     if (cudaStreamSynchronize(g_stream) != cudaSuccess) return -1;
-    if (g_status == nullptr) return 0;
-    if (cudaMemcpy(host, g_status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (host[0] != 0) cudaMemset(g_status, 0, sizeof(host));
-    return host[0];
+    int code = 0;
+    if (g_status != nullptr) {
+        if (cudaMemcpy(host, g_status, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+        if (host[0] != 0) cudaMemset(g_status, 0, sizeof(host));
+        code = host[0];
+    }
+    // the no-allocation entry point reports through a word inside the library image
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_noalloc_status_ptr[dev] != nullptr) {
+        if (cudaMemcpy(host, g_noalloc_status_ptr[dev], sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+        if (host[0] != 0) cudaMemset(g_noalloc_status_ptr[dev], 0, sizeof(host));
+        if (code == 0) code = host[0];
+    }
+    return code;
 }
 
 extern "C" long long glmasr_launch_count(void) { return g_launches; }
 
-// timing experiments: switch the kernels' experiment flags (wrong results by design; -1 = back to the environment's)
+#ifdef GLMASR_EXPERIMENTS
+// experiment builds only: switch the kernels' experiment flags (wrong results by design; -1 = back to the environment's)
 extern "C" void glmasr_debug_set_flags(int flags) { g_debug_override = flags; }
 
-// timing experiments: copy the per-CTA cycle counters of the last instrumented GEMM launch
+// experiment builds only: copy the per-CTA cycle counters of the last instrumented GEMM launch
 extern "C" int glmasr_debug_cycles(unsigned long long *host_out, int max_ctas) {
     if (g_ws[WS_DBG] == nullptr) return 0;
     cudaStreamSynchronize(g_stream);
@@ -1237,6 +1309,7 @@ extern "C" int glmasr_debug_cycles(unsigned long long *host_out, int max_ctas) {
     if (cudaMemcpy(host_out, g_ws[WS_DBG], (size_t)n * 16 * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return n;
 }
+#endif
 
 extern "C" void glmasr_profile_enable(int on) {
     g_profile = on != 0;

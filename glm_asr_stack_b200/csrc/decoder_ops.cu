@@ -217,6 +217,18 @@ bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, cons
     return true;
 }
 
+// 16 bf16-representable floats as 32 contiguous bytes (dst 16-byte aligned)
+__device__ __forceinline__ void store_bf16x16(__nv_bfloat16 *dst, const float (&v)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t *>(&b);
+    }
+    reinterpret_cast<uint4 *>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4 *>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
 // --------------------------------------------------------------------------------------------
 // RMSNorm whose result goes straight into the next W4A4 GEMM: same normalisation as rmsnorm_kernel
 // (bit-equal bf16 values), then the activation quantiser on 16-element blocks of that bf16 row
@@ -224,7 +236,7 @@ bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, cons
 // --------------------------------------------------------------------------------------------
 __global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf, int sf_chunks,
                                      const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ weight,
-                                     float eps, float inv_in, int rows, int dim) {
+                                     float eps, float inv_in, int rows, int dim, __nv_bfloat16 *__restrict__ normed_out) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __nv_bfloat16 row_s[];
@@ -261,6 +273,7 @@ __global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__
                 v[8 * h + 2 * j + 1] = __bfloat162float(__float2bfloat16(a1));
             }
         }
+        if (normed_out != nullptr) store_bf16x16(normed_out + (size_t)row * dim + (size_t)b * 16, v);
         uint32_t lo, hi;
         const uint32_t sf = quantize_block16(v, inv_in, lo, hi);
         *reinterpret_cast<uint2 *>(q_packed + (size_t)row * (dim / 2) + (size_t)b * 8) = make_uint2(lo, hi);
@@ -309,7 +322,7 @@ template <int P>
 __global__ void __launch_bounds__(256) rmsnorm_quant_warp_kernel(uint8_t *__restrict__ q_packed, uint8_t *__restrict__ q_sf,
                                                                 int sf_chunks, const __nv_bfloat16 *__restrict__ x,
                                                                 const __nv_bfloat16 *__restrict__ weight, float eps,
-                                                                float inv_in, int rows) {
+                                                                float inv_in, int rows, __nv_bfloat16 *__restrict__ normed_out) {
     extern __shared__ __align__(16) uint8_t strips[];
     constexpr int dim = 2048 * P;
     pdl_launch_dependents();
@@ -365,6 +378,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_warp_kernel(uint8_t *__rest
                     v[8 * h + 2 * j + 1] = __bfloat162float(__float2bfloat16(a1));
                 }
             }
+            if (normed_out != nullptr) store_bf16x16(normed_out + (size_t)row * dim + (size_t)(b0 + k) * 16, v);
             const uint32_t sf = quantize_block16(v, inv_in, packed[2 * k], packed[2 * k + 1]);
             sfw |= (sf & 0xFFu) << (8 * k);
         }
@@ -376,15 +390,16 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_warp_kernel(uint8_t *__rest
 }
 
 bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps,
-                          float input_scale, int rows, int dim, cudaStream_t st) {
+                          float input_scale, int rows, int dim, cudaStream_t st, __nv_bfloat16 *normed_out) {
     if (rows <= 0) return true;
-    if ((dim % 64) != 0 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)q_packed) & 15) != 0 || !(input_scale > 0.0f))
+    if ((dim % 64) != 0 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)q_packed | (uintptr_t)normed_out) & 15) != 0 ||
+        !(input_scale > 0.0f))
         return false;
     if (rows >= 2048 && (dim == 2048 || dim == 4096)) {
         const dim3 grid((rows + 7) / 8);
         if (dim == 2048) {
             launch_chained(rmsnorm_quant_warp_kernel<1>, grid, dim3(256), (size_t)(8 * kNormStrip), st, q_packed, q_sf, dim / 64, x,
-                           weight, eps, 1.0f / input_scale, rows);
+                           weight, eps, 1.0f / input_scale, rows, normed_out);
         } else {
             static bool configured = false;
             if (!configured) {
@@ -392,13 +407,13 @@ bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 
                 configured = true;
             }
             launch_chained(rmsnorm_quant_warp_kernel<2>, grid, dim3(256), (size_t)(16 * kNormStrip), st, q_packed, q_sf, dim / 64, x,
-                           weight, eps, 1.0f / input_scale, rows);
+                           weight, eps, 1.0f / input_scale, rows, normed_out);
         }
         return true;
     }
     GLMASR_PREFER_MAX_SMEM(rmsnorm_quant_kernel);
     launch_chained(rmsnorm_quant_kernel, dim3(rows), dim3(128), (size_t)dim * sizeof(__nv_bfloat16), st, q_packed, q_sf, dim / 64, x, weight, eps,
-                                                                            1.0f / input_scale, rows, dim);
+                   1.0f / input_scale, rows, dim, normed_out);
     return true;
 }
 

@@ -21,8 +21,10 @@ bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, cons
                           const int64_t *slot_mapping, __nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, int num_seqs,
                           int q_heads, int kv_heads, int head_dim, cudaStream_t st);
 // RMSNorm + activation quantiser for the next W4A4 GEMM: e2m1 bytes [rows, dim/2] and 128x4-tiled scales.
+// normed_out (optional, dense [rows, dim], 16-byte aligned): the bf16 result of the norm as well, for consumers
+// that take bf16.
 bool launch_rmsnorm_quant(uint8_t *q_packed, uint8_t *q_sf, const __nv_bfloat16 *x, const __nv_bfloat16 *weight, float eps,
-                          float input_scale, int rows, int dim, cudaStream_t st);
+                          float input_scale, int rows, int dim, cudaStream_t st, __nv_bfloat16 *normed_out = nullptr);
 void launch_reshape_and_cache(__nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, const __nv_bfloat16 *key, int ldk,
                               const __nv_bfloat16 *value, int ldv, const int64_t *slot_mapping, int num_tokens,
                               int num_kv_heads, int head_dim, int block_size, cudaStream_t st);

@@ -33,6 +33,8 @@ int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, cons
                                  const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
                                  const uint16_t *residual, int M, int K, uint8_t *q_out = nullptr,
                                  uint8_t *q_out_sf = nullptr, float q_out_input_scale = 0.0f);   // api.cu
+int fp4_linear_w4a16_silu_quantized(uint8_t *q_out, uint8_t *q_out_sf, float q_out_input_scale, const uint16_t *x, int ldx,
+                                    const glmasr_fp4_weight *gate_up, int M, int K);             // api.cu
 
 struct ProjRef {
     int dtype = -1;                     // GLMASR_DTYPE_UINT8 (FP4) or GLMASR_DTYPE_BF16
@@ -158,6 +160,22 @@ static bool prefer_w4a4() {
     return state == 1;
 }
 
+// Which arithmetic the same-input PAIRS (k|v, gate|up) use when GLMASR_USE_CUTLASS_NVFP4 selects the native
+// path.  The reference never runs a fused pair natively: linear_proj_pair_same_input
+// (Infer-engine/cuda/decoder.cu:923-978) always dequantises both weights and runs a bf16 GEMM, so with the
+// switch on its q, o and down projections are W4A4 and its k|v and gate|up are W4A16 (pairs that carry a
+// pre_quant_scale are not fused and go through nvfp4_linear one by one, :957-963).  That mix is the default
+// here.  GLMASR_NVFP4_PAIRS=1 opts in to running the pairs in W4A4 as well (q|k|v and gate|up each one
+// block-scaled FP4 GEMM on a shared quantised input): faster, but not the reference's arithmetic.
+static bool pairs_w4a4() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("GLMASR_NVFP4_PAIRS");
+        state = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
+    }
+    return state == 1 && prefer_w4a4();
+}
+
 static glmasr_fp4_weight as_weight(const ProjRef &p) {
     glmasr_fp4_weight w;
     w.w_packed = (const uint8_t *)p.w;
@@ -199,16 +217,21 @@ static void single_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, cons
 }
 
 // Several same-input FP4 projections as one GEMM when the reference's own fusion rule allows it
-// (all FP4, none with a pre_quant_scale: Infer-engine/cuda/decoder.cu:957-963) and, for W4A4, they
-// share their input_scale.  Returns false when the caller has to run them one by one.
+// (all FP4, none with a pre_quant_scale: Infer-engine/cuda/decoder.cu:957-963): W4A16 like the reference's
+// fused pair, or W4A4 when the pairs were opted in to the native path and share their input_scale.
+// Returns false when the caller has to run them one by one.
+static bool fusable(const ProjRef *const *ps, int n) {
+    for (int i = 0; i < n; ++i)
+        if (ps[i]->dtype != GLMASR_DTYPE_UINT8 || ps[i]->pre != nullptr || ps[i]->K != ps[0]->K) return false;
+    return true;
+}
+
 static bool fused_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, const ProjRef *const *ps, int n, int epi,
                        int M) {
+    if (!fusable(ps, n)) return false;
     glmasr_fp4_weight w[3];
-    for (int i = 0; i < n; ++i) {
-        if (ps[i]->dtype != GLMASR_DTYPE_UINT8 || ps[i]->pre != nullptr || ps[i]->K != ps[0]->K) return false;
-        w[i] = as_weight(*ps[i]);
-    }
-    bool w4a4 = prefer_w4a4();
+    for (int i = 0; i < n; ++i) w[i] = as_weight(*ps[i]);
+    bool w4a4 = pairs_w4a4();
     for (int i = 0; i < n && w4a4; ++i)
         if (ps[i]->scales == nullptr || !(ps[i]->input_scale > 0.0f) || ps[i]->input_scale != ps[0]->input_scale) w4a4 = false;
     const int rc = glmasr_fp4_linear_fused(w4a4 ? GLMASR_MODE_W4A4 : GLMASR_MODE_W4A16, out, ldo, x, ldx, w, n,
@@ -224,7 +247,7 @@ static bool norm_then_fused_proj_w4a4(uint16_t *out, int ldo, const uint16_t *x,
                                       const ProjRef *const *ps, int n, int epi, int M, int H, uint8_t *xq, uint8_t *xsf,
                                       cudaStream_t st, uint8_t *q_out = nullptr, uint8_t *q_out_sf = nullptr,
                                       float q_out_scale = 0.0f) {
-    if (!prefer_w4a4() || (H % 256) != 0) return false;
+    if (!pairs_w4a4() || (H % 256) != 0) return false;
     glmasr_fp4_weight w[3];
     for (int i = 0; i < n; ++i) {
         const ProjRef &p = *ps[i];
@@ -264,6 +287,82 @@ static void single_proj_prequantized(uint16_t *out, int ldo, const uint8_t *xq, 
     const int rc = fp4_linear_w4a4_prequantized(out, ldo, xq, xsf, &w, 1, p.input_scale,
                                                 residual ? GLMASR_EPI_RESIDUAL : GLMASR_EPI_STORE, residual, M, p.K);
     GLMASR_CHECK(rc == 0, "decoder projection on a quantised input failed (N=%d K=%d M=%d)", p.N, p.K, M);
+}
+
+// Scratch of one driver call (private workspace slots), shared by the per-layer stages below.
+struct StepBuffers {
+    uint16_t *nrm;       // [M, H] bf16: normed hidden state, for consumers that take bf16
+    uint16_t *qkv;       // [M, H + 2 KV]
+    uint16_t *act;       // [M, 2 F]: SiLU-gate output (first F columns when fused) or gate | up
+    uint16_t *scratch;   // [M, max(H, F)]
+    uint8_t *nq, *nsf;   // quantised normed hidden state (K = H)
+    uint8_t *aq, *asf;   // quantised attention output (K = H) / SiLU-gate output (K = F)
+};
+
+// q | k | v of one layer from the pre-norm hidden state into B.qkv [M, H + 2 KV].  Returns the number of
+// glue launches (norms) the caller has to account for.
+static int project_qkv(const LayerRef &R, const uint16_t *hid, const StepBuffers &B, int M, int H, int KV, cudaStream_t st) {
+    const int NQKV = H + 2 * KV;
+    const ProjRef *qkv_p[3] = {&R.q, &R.k, &R.v};
+    const ProjRef *kv_p[2] = {&R.k, &R.v};
+    // (1) pairs opted in to W4A4: norm + quantiser in one launch, one q|k|v GEMM on the quantised rows
+    if (norm_then_fused_proj_w4a4(B.qkv, NQKV, hid, R.norm1, 1e-5f, qkv_p, 3, GLMASR_EPI_STORE, M, H, B.nq, B.nsf, st)) return 0;
+    // (2) the reference's mix: q through the native path, k|v as one W4A16 GEMM
+    //     (Infer-engine/cuda/decoder.cu:1995-2035); the norm writes its result in both forms
+    if (prefer_w4a4() && takes_quantised_input(R.q) && R.q.K == H && fusable(kv_p, 2) && R.k.K == H &&
+        launch_rmsnorm_quant(B.nq, B.nsf, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, R.q.input_scale, M, H,
+                             st, (__nv_bfloat16 *)B.nrm)) {
+        single_proj_prequantized(B.qkv, NQKV, B.nq, B.nsf, R.q, M, nullptr);
+        const bool ok = fused_proj(B.qkv + H, NQKV, B.nrm, H, kv_p, 2, GLMASR_EPI_STORE, M);
+        GLMASR_CHECK(ok, "decoder k|v projection failed (M=%d H=%d)", M, H);
+        return 1;
+    }
+    // (3) everything else: bf16 norm, then whatever can be fused
+    launch_rmsnorm((__nv_bfloat16 *)B.nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st);
+    // W4A16 throughout: one q|k|v GEMM gives the values of fp4_linear(q) + the fused k|v pair
+    if (!prefer_w4a4() && fused_proj(B.qkv, NQKV, B.nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) return 1;
+    single_proj(B.qkv, NQKV, B.nrm, H, R.q, M, nullptr, B.scratch);
+    if (!fused_proj(B.qkv + H, NQKV, B.nrm, H, kv_p, 2, GLMASR_EPI_STORE, M)) {
+        single_proj(B.qkv + H, NQKV, B.nrm, H, R.k, M, nullptr, B.scratch);
+        single_proj(B.qkv + H + KV, NQKV, B.nrm, H, R.v, M, nullptr, B.scratch);
+    }
+    return 1;
+}
+
+// post-attention norm -> gate|up -> SiLU-gate -> down + residual, in place on hid [M, H].  Returns the glue
+// launches the caller has to account for.
+static int project_mlp(const LayerRef &R, uint16_t *hid, const StepBuffers &B, int M, int H, int F, cudaStream_t st) {
+    const ProjRef *gu_p[2] = {&R.gate, &R.up};
+    // the producer of down's input quantises for it when down runs natively
+    const bool down_q = takes_quantised_input(R.down) && R.down.K == F && (F % 64) == 0;
+    // (1) pairs opted in to W4A4
+    if (down_q && norm_then_fused_proj_w4a4(B.act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, B.nq, B.nsf, st,
+                                            B.aq, B.asf, R.down.input_scale)) {
+        single_proj_prequantized(hid, H, B.aq, B.asf, R.down, M, hid);
+        return 0;
+    }
+    if (norm_then_fused_proj_w4a4(B.act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, B.nq, B.nsf, st)) {
+        single_proj(hid, H, B.act, F, R.down, M, hid, B.scratch);
+        return 0;
+    }
+    launch_rmsnorm((__nv_bfloat16 *)B.nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st);
+    // (2) the reference's mix: gate|up as one W4A16 GEMM (Infer-engine/cuda/decoder.cu:2107-2112) whose SiLU-gate
+    //     epilogue writes the native down projection's quantised operand
+    if (prefer_w4a4() && !pairs_w4a4() && down_q && fusable(gu_p, 2) && R.gate.K == H && R.gate.N == F && R.up.N == F) {
+        const glmasr_fp4_weight gu[2] = {as_weight(R.gate), as_weight(R.up)};
+        if (fp4_linear_w4a16_silu_quantized(B.aq, B.asf, R.down.input_scale, B.nrm, H, gu, M, H) == 0) {
+            single_proj_prequantized(hid, H, B.aq, B.asf, R.down, M, hid);
+            return 1;
+        }
+    }
+    // (3) everything else
+    if (!fused_proj(B.act, F, B.nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
+        single_proj(B.act, F, B.nrm, H, R.gate, M, nullptr, B.scratch);
+        single_proj(B.act + (size_t)M * F, F, B.nrm, H, R.up, M, nullptr, B.scratch);
+        silu_elementwise_mul(B.act, B.act + (size_t)M * F, M * F);
+    }
+    single_proj(hid, H, B.act, F, R.down, M, hid, B.scratch);
+    return 1;
 }
 
 }  // namespace glmasr
@@ -412,6 +511,8 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     uint8_t *aq = (uint8_t *)workspace_slot(WS_D_AQ, (size_t)M * KQ / 2);
     uint8_t *asf = (uint8_t *)workspace_slot(WS_D_ASF, tiled_scale_bytes(M, KQ));
 
+    const StepBuffers B = {nrm, qkv, act, scratch, nq, nsf, aq, asf};
+
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_total, h_total.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_rows, h_rows.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
@@ -430,19 +531,7 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
         __nv_bfloat16 *v_base = (__nv_bfloat16 *)pool->v_cache + (size_t)l * pool->layer_stride;
 
         // q | k | v into one [M, H + 2 KV] buffer
-        const ProjRef *qkv_p[3] = {&R.q, &R.k, &R.v};
-        int glue = 0;                       // launches of this layer outside the projections' own accounting
-        if (norm_then_fused_proj_w4a4(qkv, NQKV, hid, R.norm1, 1e-5f, qkv_p, 3, GLMASR_EPI_STORE, M, H, nq, nsf, st)) {
-            // done: norm + quantiser in one launch, GEMM on the quantised rows
-        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st),
-                   ++glue, !fused_proj(qkv, NQKV, nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) {
-            single_proj(qkv, NQKV, nrm, H, R.q, M, nullptr, scratch);
-            const ProjRef *kv_p[2] = {&R.k, &R.v};
-            if (!fused_proj(qkv + H, NQKV, nrm, H, kv_p, 2, GLMASR_EPI_STORE, M)) {
-                single_proj(qkv + H, NQKV, nrm, H, R.k, M, nullptr, scratch);
-                single_proj(qkv + H + KV, NQKV, nrm, H, R.v, M, nullptr, scratch);
-            }
-        }
+        int glue = project_qkv(R, hid, B, M, H, KV, st);
         // RoPE on q and k in place (position = cached length), KV write, attention over cached + 1 tokens
         if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_seq_lens, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
             glue += 1;
@@ -470,23 +559,7 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
             single_proj(hid, H, att, H, R.o, M, hid, scratch);
         }
 
-        const ProjRef *gu_p[2] = {&R.gate, &R.up};
-        // gate|up's SiLU-gate epilogue quantises for the down projection when that one runs in W4A4
-        const bool down_q = takes_quantised_input(R.down) && R.down.K == F && (F % 64) == 0;
-        bool down_done = false;
-        if (down_q && norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st, aq,
-                                                asf, R.down.input_scale)) {
-            single_proj_prequantized(hid, H, aq, asf, R.down, M, hid);
-            down_done = true;
-        } else if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
-            // done
-        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st),
-                   ++glue, !fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
-            single_proj(act, F, nrm, H, R.gate, M, nullptr, scratch);
-            single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
-            silu_elementwise_mul(act, act + (size_t)M * F, M * F);
-        }
-        if (!down_done) single_proj(hid, H, act, F, R.down, M, hid, scratch);
+        glue += project_mlp(R, hid, B, M, H, F, st);
         note_launches(glue + 1);   // norms, RoPE / cache write, attention (the projections count themselves)
     }
 
@@ -588,6 +661,7 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
     int64_t *d_slot = (int64_t *)workspace_slot(WS_D_SLOT, (size_t)M * sizeof(int64_t));
     int *d_pos = (int *)workspace_slot(WS_D_POS, (size_t)M * sizeof(int));
     int *d_meta = (int *)workspace_slot(WS_D_OFFS, (size_t)2 * num_seqs * sizeof(int));
+    const StepBuffers B = {nrm, qkv, act, scratch, nq, nsf, aq, asf};
     // pageable host vectors: the copies have been staged when these calls return
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_pos, h_pos.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
@@ -600,18 +674,7 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
         __nv_bfloat16 *v_base = (__nv_bfloat16 *)pool->v_cache + (size_t)l * pool->layer_stride;
         int glue = 0;
 
-        const ProjRef *qkv_p[3] = {&R.q, &R.k, &R.v};
-        if (norm_then_fused_proj_w4a4(qkv, NQKV, hid, R.norm1, 1e-5f, qkv_p, 3, GLMASR_EPI_STORE, M, H, nq, nsf, st)) {
-            // norm + quantiser in one launch, GEMM on the quantised rows
-        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm1, 1e-5f, M, H, st),
-                   ++glue, !fused_proj(qkv, NQKV, nrm, H, qkv_p, 3, GLMASR_EPI_STORE, M)) {
-            single_proj(qkv, NQKV, nrm, H, R.q, M, nullptr, scratch);
-            const ProjRef *kv_p[2] = {&R.k, &R.v};
-            if (!fused_proj(qkv + H, NQKV, nrm, H, kv_p, 2, GLMASR_EPI_STORE, M)) {
-                single_proj(qkv + H, NQKV, nrm, H, R.k, M, nullptr, scratch);
-                single_proj(qkv + H + KV, NQKV, nrm, H, R.v, M, nullptr, scratch);
-            }
-        }
+        glue += project_qkv(R, hid, B, M, H, KV, st);
         if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_pos, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
             glue += 1;
         } else {
@@ -638,23 +701,7 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
         }
         glue += 1;
 
-        const ProjRef *gu_p[2] = {&R.gate, &R.up};
-        const bool down_q = takes_quantised_input(R.down) && R.down.K == F && (F % 64) == 0;
-        bool down_done = false;
-        if (down_q && norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st, aq,
-                                                asf, R.down.input_scale)) {
-            // the SiLU-gate epilogue wrote the down projection's quantised operand
-            single_proj_prequantized(hid, H, aq, asf, R.down, M, hid);
-            down_done = true;
-        } else if (norm_then_fused_proj_w4a4(act, F, hid, R.norm2, 1e-5f, gu_p, 2, GLMASR_EPI_SILU_GATE, M, H, nq, nsf, st)) {
-            // done
-        } else if (launch_rmsnorm((__nv_bfloat16 *)nrm, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)R.norm2, 1e-5f, M, H, st),
-                   ++glue, !fused_proj(act, F, nrm, H, gu_p, 2, GLMASR_EPI_SILU_GATE, M)) {
-            single_proj(act, F, nrm, H, R.gate, M, nullptr, scratch);
-            single_proj(act + (size_t)M * F, F, nrm, H, R.up, M, nullptr, scratch);
-            silu_elementwise_mul(act, act + (size_t)M * F, M * F);
-        }
-        if (!down_done) single_proj(hid, H, act, F, R.down, M, hid, scratch);
+        glue += project_mlp(R, hid, B, M, H, F, st);
         note_launches(glue);
     }
     launch_rmsnorm((__nv_bfloat16 *)hid, (const __nv_bfloat16 *)hid, (const __nv_bfloat16 *)refs.final_norm, 1e-5f, M, H, st);

@@ -213,8 +213,13 @@ __device__ __forceinline__ float silu_gate(float g, float u) {
 }
 
 
-// cycle accounting for timing experiments (debug & 64): T0 opens an interval, ACC closes it into a counter
+// cycle accounting of experiment builds: T0 opens an interval, ACC closes it into a counter
+#ifdef GLMASR_EXPERIMENTS
 #define DBG_T0() long long _t0 = dbg ? clock64() : 0
 #define DBG_ACC(slot) do { if (dbg) { long long _t1 = clock64(); dbg_acc[slot] += (unsigned long long)(_t1 - _t0); _t0 = _t1; } } while (0)
+#else
+#define DBG_T0() do { } while (0)
+#define DBG_ACC(slot) do { } while (0)
+#endif
 
 }  // namespace glmasr

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const long long t_start = ((p.debug & 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
+    const long long t_start = (GLMASR_EXP(p, 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
     pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
@@ -142,15 +142,16 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
     // when that is not true) and waits before its first activation load.
     const bool early_b = MODE != GEMM_W4A16 && p.early_weights != 0;
     if (warp != 0 || !early_b) pdl_wait();
-    const long long t_setup = ((p.debug & 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
+    const long long t_setup = (GLMASR_EXP(p, 64) && p.dbg_cycles != nullptr) ? clock64() : 0;
 
     const int total_tiles = p.num_m_tiles * p.num_n_tiles;
     const int nkb = p.num_k_blocks;
     // split-K: work item w = tile * S + split covers K blocks [split * nkb / S, (split + 1) * nkb / S)
     const int S = (MODE == GEMM_W4A4 && p.split_k > 1) ? p.split_k : 1;
     const int total_work = total_tiles * S;
-    const bool dbg = (p.debug & 64) != 0 && p.dbg_cycles != nullptr;
+    const bool dbg = GLMASR_EXP(p, 64) && p.dbg_cycles != nullptr;
     unsigned long long dbg_acc[4] = {0, 0, 0, 0};
+    (void)dbg_acc;
 
     if (warp == 0) {
         // ================================ TMA producer ================================
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
 #pragma unroll
             for (int h = 0; h < NB; ++h)
                 tma_load_2d(sb + C::A_BYTES + h * C::SUB_BYTES, &p.tm_b[st[h].seg], full_bar(s), kx, st[h].row0);
-            if (MODE == GEMM_W4A4 && !(p.debug & 2)) {
+            if (MODE == GEMM_W4A4 && !GLMASR_EXP(p, 2)) {
                 const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
 #pragma unroll
                 for (int h = 0; h < NB; ++h)
@@ -190,10 +191,10 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                     }
                 }
                 preloaded = kb1 - kb0 < C::STAGES ? kb1 - kb0 : C::STAGES;
-                if (p.debug & 8) preloaded = 0;
+                if (GLMASR_EXP(p, 8)) preloaded = 0;
                 for (int i = 0; i < preloaded; ++i) {
                     if (leader) {
-                        mbar_expect_tx(full_bar(i), (p.debug & 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
+                        mbar_expect_tx(full_bar(i), GLMASR_EXP(p, 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
                         load_weights(i, kb0 + i, st, sfb_src);
                     }
                 }
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                 DBG_T0();
                 if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                 DBG_ACC(0);
-                if ((p.debug & 8) && it >= (uint32_t)C::STAGES) {   // experiment: no memory traffic
+                if (GLMASR_EXP(p, 8) && it >= (uint32_t)C::STAGES) {   // experiment: no memory traffic
                     if (leader) mbar_arrive(full_bar(s));
                     ++it;
                     continue;
@@ -256,9 +257,9 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                 const bool have_weights = work == (int)blockIdx.x && kb - kb0 < preloaded;
                 if (leader) {
                     if (!have_weights)
-                        mbar_expect_tx(full_bar(s), (p.debug & 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
+                        mbar_expect_tx(full_bar(s), GLMASR_EXP(p, 2) ? (uint32_t)(C::A_BYTES + C::B_BYTES) : (uint32_t)C::TX_BYTES);
                     tma_load_2d(sb, &p.tm_a, full_bar(s), kx, m_tile * 128);
-                    if (MODE == GEMM_W4A4 && !(p.debug & 2))
+                    if (MODE == GEMM_W4A4 && !GLMASR_EXP(p, 2))
                         bulk_load_1d(sb + C::A_BYTES + C::B_BYTES, sfa_src + (size_t)kb * C::SF_TILE, C::SF_TILE, full_bar(s));
                     if constexpr (MODE != GEMM_W4A16) {
                         if (!have_weights) load_weights(s, kb, st, sfb_src);
@@ -294,14 +295,14 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                 tc_fence_after();
                 const uint32_t a_addr = stage_base(s);
                 const uint32_t b_addr = a_addr + C::A_BYTES;
-                const uint32_t sf_set = ((p.debug & 32) ? 0u : (it & 1u)) * C::SF_SET_COLS;
+                const uint32_t sf_set = (GLMASR_EXP(p, 32) ? 0u : (it & 1u)) * C::SF_SET_COLS;
                 const uint32_t sfa_t = tmem_base + C::SFA_COL + sf_set;
                 const uint32_t sfb_t = tmem_base + C::SFB_COL + sf_set;
                 // descriptors differ from stage to stage only in their 14-bit start-address field
                 const uint64_t adesc0 = smem_desc_sw128(a_addr);
                 const uint64_t bdesc0 = smem_desc_sw128(b_addr);
                 if (leader) {
-                    if (MODE == GEMM_W4A4 && !((p.debug & 1) && it > 1)) {
+                    if (MODE == GEMM_W4A4 && !(GLMASR_EXP(p, 1) && it > 1)) {
                         const uint64_t sfdesc0 = smem_desc_sf_chunk(a_addr + C::A_BYTES + C::B_BYTES);
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        if ((p.debug & 16) && k > 0) break;   // experiment: a quarter of the MMAs
+                        if (GLMASR_EXP(p, 16) && k > 0) break;   // experiment: a quarter of the MMAs
                         const uint64_t adesc = adesc0 + (uint64_t)((k * 32) >> 4);
                         const uint64_t bdesc = bdesc0 + (uint64_t)((k * 32) >> 4);
                         const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
@@ -458,7 +459,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                             }
                             return;
                         }
-                        if (row_ok && nvalid > 0 && !(p.debug & 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
+                        if (row_ok && nvalid > 0 && !GLMASR_EXP(p, 4)) store_row_chunk(out_row + sg.col0 + c0, v, nvalid);
                     };
                     if (from_partials) {
 #pragma unroll 1
@@ -517,7 +518,7 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
                     }
-                    if (!(p.debug & 4)) store_row_chunk(out_row + col, v, nvalid);
+                    if (!GLMASR_EXP(p, 4)) store_row_chunk(out_row + col, v, nvalid);
                 };
                 if (from_partials) {
 #pragma unroll 1

@@ -21,6 +21,15 @@ enum EpilogueMode : int {
 
 static constexpr int kMaxSegments = 3;
 
+// Timing experiments (per-role cycle counters, branches that leave work out and therefore give wrong
+// results) exist only in a library built with -DGLMASR_EXPERIMENTS (`make EXPERIMENTS=1`).  In the
+// default build every test below is the constant false and the compiler removes the branches.
+#ifdef GLMASR_EXPERIMENTS
+#define GLMASR_EXP(p, bits) ((((p).debug) & (bits)) != 0)
+#else
+#define GLMASR_EXP(p, bits) false
+#endif
+
 // One launch computes out[M, sum N_s] = x[M, K] * concat_s(W_s[N_s, K])^T for up to three
 // weight tensors that share the input (q|k|v, gate|up), each with its own per-tensor scale.
 struct alignas(64) GemmParams {
@@ -66,7 +75,7 @@ struct alignas(64) GemmParams {
     int num_k_blocks;                   // K steps of 128 operand bytes per row (W4A4: 256 elements, else 64)
     int sf_k_chunks;                    // W4A4: 512-byte scale chunks per 128-row tile along K (= ceil(K/64))
     int *status;
-    int debug;                          // timing experiments only (GLMASR_DEBUG_FLAGS); 0 in normal use
+    int debug;                          // experiment builds only (GLMASR_DEBUG_FLAGS); ignored otherwise
     unsigned long long *dbg_cycles;     // debug & 64: per-CTA cycle counters [gridDim.x][16]
 };
 

@@ -65,8 +65,8 @@ struct AttnParams {
     const int *seq_lens;          // NULL: seq_offsets is cumulative (num_seqs + 1 entries)
     int *status;
     const int *vt_col;            // first V^T column of every sequence (written by transpose_v_kernel)
-    unsigned long long *dbg;      // timing experiments: 8 cycle sums per CTA (soft-max warp 2), else NULL
-    int dbg_no_store;             // timing experiments: leave the result stores out
+    unsigned long long *dbg;      // experiment builds (-DGLMASR_EXPERIMENTS): 8 cycle sums per CTA (soft-max warp 2), else NULL
+    int dbg_no_store;             // experiment builds: leave the result stores out
     int ldo, num_q_heads, num_seqs, group, q_tiles, total_items, causal;
     float scale_log2;             // log2(e) / sqrt(head_dim)
     // optional: the result quantised for the next projection (activation quantiser on the bf16 values)
@@ -318,6 +318,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
         const float scale = p.scale_log2;
         uint32_t sc = 0, pv = 0;                        // key steps consumed, P V products of earlier items
         bool ok = true;
+#ifdef GLMASR_EXPERIMENTS
         const bool dbg = p.dbg != nullptr && warp == 2 && lane == 0;
         unsigned long long dsum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tl = dbg ? clock64() : 0;
@@ -328,6 +329,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
         dsum[i] += (unsigned long long)(t_ - tl);    \
         tl = t_;                                     \
     }
+#define ATT_STORES_ON (!p.dbg_no_store)
+#else
+#define ATT_DBG(i) do { } while (0)
+#define ATT_STORES_ON true
+#endif
         for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
             ItemInfo it;
             if (!decode_item(p, item, it)) continue;
@@ -442,7 +448,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                         }
                     }
                     __syncwarp();
-                    if (!p.dbg_no_store) {
+                    if (ATT_STORES_ON) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int r = i * 4 + (lane >> 3), c = lane & 7;       // row of the warp, 16-byte chunk
@@ -504,11 +510,14 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
             }
             ATT_DBG(6);
         }
-#undef ATT_DBG
+#ifdef GLMASR_EXPERIMENTS
         if (dbg) {
             dsum[0] = (unsigned long long)(clock64() - t_begin);
             for (int i = 0; i < 8; ++i) p.dbg[(size_t)blockIdx.x * 8 + i] = dsum[i];
         }
+#endif
+#undef ATT_DBG
+#undef ATT_STORES_ON
     }
 
     // ================================ teardown ==========================================
@@ -596,6 +605,7 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
         if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
     }
     const dim3 grid(p.total_items < 2 * num_sms ? p.total_items : 2 * num_sms, 1, 1);
+#ifdef GLMASR_EXPERIMENTS
     static int debug = -1;
     if (debug < 0) {
         const char *e = getenv("GLMASR_ATTN_DEBUG");
@@ -606,7 +616,9 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
         p.dbg = (unsigned long long *)workspace_slot(WS_ATTN_DEBUG, (size_t)grid.x * 8 * sizeof(unsigned long long));
         cudaMemsetAsync(p.dbg, 0, (size_t)grid.x * 8 * sizeof(unsigned long long), st);
     }
+#endif
     launch_chained(prefill_attention_umma_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, st, p);
+#ifdef GLMASR_EXPERIMENTS
     if (debug) {
         // timing experiment: where the soft-max warps of every CTA spent their cycles (averages over the CTAs)
         std::vector<unsigned long long> h((size_t)grid.x * 8);
@@ -619,6 +631,7 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
                         "last PV %.0f, result %.0f, item set-up %.0f\n",
                 avg[0], avg[1], avg[2], avg[3], avg[4], avg[5], avg[6], avg[7]);
     }
+#endif
     return true;
 }
 

@@ -232,7 +232,11 @@ int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16
  * Limits: M <= 512, K <= 8192, K % 256 == 0, N % 8 == 0, ceil128(N) * K <= 32 Mi, 16-byte aligned
  * pointers; anything else returns -1 with a message on stderr (use nvfp4_linear then).
  * The first call on each device looks up the array's device address and opts the kernels in to
- * large shared memory; make that first call before any stream capture begins.
+ * large shared memory, and it may be the call that makes the CUDA runtime load the module holding the
+ * array and the kernels onto that device: make it once per device during warm-up -- before the KV pool
+ * takes the remaining memory and before any stream capture begins.
+ * A bounded wait that runs out inside these kernels is reported by glmasr_fp4_status() like any other
+ * (through a status word that also lives in the library image).
  * All calls share the one array and it keeps the previous call's contents (the part that must
  * start at zero is cleared on every call), so two calls whose GPU work overlaps -- different
  * streams, different host threads -- race; issue them in stream order. */
@@ -241,7 +245,8 @@ int glmasr_nvfp4_linear_noalloc(uint16_t *out, const uint16_t *x, const uint8_t 
                                 int M, int N, int K);
 
 /* Synchronise and return the first device-side status code recorded since the last call
- * (0 = none; 1..5 = a bounded wait inside a kernel ran out), then clear it. */
+ * (0 = none; 1..6 = a bounded wait inside a kernel ran out, 7 = a layout a kernel cannot work with),
+ * then clear it. */
 int glmasr_fp4_status(void);
 /* Number of kernels this library has launched since load (for launch accounting). */
 long long glmasr_launch_count(void);

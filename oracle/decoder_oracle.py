@@ -87,28 +87,55 @@ def paged_decode_attention(q_bits, k_cache, v_cache, block_tables, seq_lens, n_q
     return o.f32_to_bf16_bits(out.reshape(n, n_q_heads * head_dim).astype(F32))
 
 
+PROJECTIONS = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def projection_mix(w4a16, w4a4, mode):
+    """The arithmetic of each of the seven projections as a dict name -> linear(x_bits, w).
+
+    ``mode``: "w4a16"     every projection through fp4_linear (the reference without GLMASR_USE_CUTLASS_NVFP4);
+              "reference" the reference WITH the switch: q, o, down through nvfp4_linear (linear_proj,
+                          Infer-engine/cuda/decoder.cu:861-921, called with use_native_nvfp4 = true), k|v and
+                          gate|up through the fused pair, which always dequantises and runs a bf16 GEMM
+                          (linear_proj_pair_same_input, decoder.cu:923-978; call sites :2017, :2107);
+              "all_w4a4"  every projection through nvfp4_linear (what the reference does for pairs that carry a
+                          pre_quant_scale, and what this library does for all pairs with GLMASR_NVFP4_PAIRS=1)."""
+    if mode == "w4a16":
+        return {n: w4a16 for n in PROJECTIONS}
+    if mode == "all_w4a4":
+        return {n: w4a4 for n in PROJECTIONS}
+    assert mode == "reference", mode
+    return {n: (w4a4 if n in ("q", "o", "down") else w4a16) for n in PROJECTIONS}
+
+
+def _per_projection(linear):
+    return linear if isinstance(linear, dict) else {n: linear for n in PROJECTIONS}
+
+
 def decode_step(hidden_bits, layers, final_norm_bits, k_caches, v_caches, block_tables, cached_lens, slot_mapping,
                 n_q_heads, n_kv_heads, head_dim, block_size, linear):
     """Infer-engine/cuda/decoder.cu:1972-2139: the layer sequence of one batched decode step.
     `layers[l]` holds norm1, norm2 (bf16 bits) and q,k,v,o,gate,up,down weights; `linear(x_bits, w)`
-    is the projection oracle to use (fp4_oracle.linear_o1 or nvfp4_linear bound to its scales).
+    is the projection oracle to use (fp4_oracle.linear_o1 or nvfp4_linear bound to its scales), or a dict
+    with one such function per projection name (see projection_mix).
     Caches are updated in place.  Returns the final-normed hidden state (bf16 bits)."""
+    lin = _per_projection(linear)
     h = hidden_bits.copy()
     H = h.shape[1]
     kvw = n_kv_heads * head_dim
     total = (cached_lens + 1).astype(np.int32)
     for l, Lw in enumerate(layers):
         x = rmsnorm(h, Lw["norm1"])
-        q = rope_single_token(linear(x, Lw["q"]), cached_lens, n_q_heads, head_dim)
-        k = rope_single_token(linear(x, Lw["k"]), cached_lens, n_kv_heads, head_dim)
-        v = linear(x, Lw["v"])
+        q = rope_single_token(lin["q"](x, Lw["q"]), cached_lens, n_q_heads, head_dim)
+        k = rope_single_token(lin["k"](x, Lw["k"]), cached_lens, n_kv_heads, head_dim)
+        v = lin["v"](x, Lw["v"])
         reshape_and_cache(k_caches[l], v_caches[l], k, v, slot_mapping)
         a = paged_decode_attention(q, k_caches[l], v_caches[l], block_tables, total, n_q_heads, n_kv_heads, head_dim,
                                    block_size)
-        h = o.residual_add(linear(a, Lw["o"]), h)
+        h = o.residual_add(lin["o"](a, Lw["o"]), h)
         x = rmsnorm(h, Lw["norm2"])
-        act = o.silu_mul_split_packed(np.concatenate([linear(x, Lw["gate"]), linear(x, Lw["up"])], axis=1))
-        h = o.residual_add(linear(act, Lw["down"]), h)
+        act = o.silu_mul_split_packed(np.concatenate([lin["gate"](x, Lw["gate"]), lin["up"](x, Lw["up"])], axis=1))
+        h = o.residual_add(lin["down"](act, Lw["down"]), h)
         assert h.shape[1] == H and k.shape[1] == kvw
     return rmsnorm(h, final_norm_bits)
 
@@ -145,19 +172,20 @@ def prefill(hidden_bits, layers, final_norm_bits, k_caches, v_caches, seq_offset
     """Infer-engine/cuda/decoder.cu:1219-1557: the layer sequence of a batched variable-length prefill.
     Positions start at 0 in every sequence; caches are updated in place (slot_mapping per token row).
     Returns the final-normed hidden states (bf16 bits)."""
+    lin = _per_projection(linear)
     h = hidden_bits.copy()
     pos = np.zeros(h.shape[0], np.int32)
     for off, ln in zip(seq_offsets, seq_lens):
         pos[off:off + ln] = np.arange(ln)
     for l, Lw in enumerate(layers):
         x = rmsnorm(h, Lw["norm1"])
-        q = rope_single_token(linear(x, Lw["q"]), pos, n_q_heads, head_dim)
-        k = rope_single_token(linear(x, Lw["k"]), pos, n_kv_heads, head_dim)
-        v = linear(x, Lw["v"])
+        q = rope_single_token(lin["q"](x, Lw["q"]), pos, n_q_heads, head_dim)
+        k = rope_single_token(lin["k"](x, Lw["k"]), pos, n_kv_heads, head_dim)
+        v = lin["v"](x, Lw["v"])
         reshape_and_cache(k_caches[l], v_caches[l], k, v, slot_mapping)
         a = prefill_attention(q, k, v, seq_offsets, seq_lens, n_q_heads, n_kv_heads, head_dim)
-        h = o.residual_add(linear(a, Lw["o"]), h)
+        h = o.residual_add(lin["o"](a, Lw["o"]), h)
         x = rmsnorm(h, Lw["norm2"])
-        act = o.silu_mul_split_packed(np.concatenate([linear(x, Lw["gate"]), linear(x, Lw["up"])], axis=1))
-        h = o.residual_add(linear(act, Lw["down"]), h)
+        act = o.silu_mul_split_packed(np.concatenate([lin["gate"](x, Lw["gate"]), lin["up"](x, Lw["up"])], axis=1))
+        h = o.residual_add(lin["down"](act, Lw["down"]), h)
     return rmsnorm(h, final_norm_bits)

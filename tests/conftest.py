@@ -10,6 +10,13 @@ for p in (ROOT, os.path.join(ROOT, "oracle")):
         sys.path.insert(0, p)
 
 
+def reference_root():
+    """Directory of the reference project (the one that holds Infer-engine/), or None.  GLMASR_REFERENCE_ROOT names
+    it; by default it is looked for beside this repository."""
+    cand = os.environ.get("GLMASR_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "Infer-engine", "include")) else None
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 

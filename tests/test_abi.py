@@ -2,8 +2,11 @@
 import ctypes
 import os
 import re
+import subprocess
 
-from conftest import ROOT
+import pytest
+
+from conftest import ROOT, reference_root
 
 
 def declared_functions():
@@ -25,6 +28,27 @@ def test_library_exports_every_declared_symbol(product_lib):
     lib = ctypes.CDLL(product_lib)
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
+
+
+def test_library_exports_nothing_the_header_does_not_declare(product_lib):
+    """Every unmangled dynamic symbol of the default build is declared in the header: no probe or experiment
+    entry point ships (the glmasr_debug_* pair exists only in `make EXPERIMENTS=1` builds)."""
+    out = subprocess.run(["nm", "-D", "--defined-only", product_lib], check=True, capture_output=True, text=True).stdout
+    exported = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
+    c_symbols = {s for s in exported if not s.startswith("_")}
+    assert c_symbols == set(declared_functions()), sorted(c_symbols ^ set(declared_functions()))
+
+
+def test_engine_struct_layouts_match_the_reference_headers():
+    """include/glmasr_engine_types.h against Infer-engine/include/{types,kv_pool}.h: sizeof of every struct and
+    offsetof of every field, as _Static_asserts compiled by gcc (tests/abi/struct_layout_check.c)."""
+    ref = reference_root()
+    if ref is None:
+        pytest.skip("reference tree not present (the layout check needs its headers)")
+    r = subprocess.run(["gcc", "-std=c11", "-fsyntax-only", "-I", os.path.join(ref, "Infer-engine", "include"),
+                        "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "abi", "struct_layout_check.c")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
 
 
 def test_python_binding_covers_the_header(product_lib):

@@ -1,0 +1,145 @@
+"""Benchmark configuration 2 at its real shape under the oracle: hidden 2048, 16 q / 4 kv heads x 128, ffn 6144,
+256 sequences with contexts uniform in 200..450 on 16-token pages handed out from a permuted pool, vocabulary
+59264 -- two layers of it (the oracle is numpy) through decoder_decode_step_batched, then the FP4 lm_head and the
+row arg-max.  Bars: bf16-out relative error <= 1e-2 and logits cosine >= 0.999 against the oracle with the same
+per-projection arithmetic; arg-max tokens equal wherever the oracle's top-2 margin exceeds the tolerance.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import decoder_oracle as do
+import fp4_oracle as o
+from conftest import ROOT
+from gpu_util import REL_TOL_VS_ORACLE, bits_of
+
+pytestmark = pytest.mark.gpu
+
+SHORT = {"self_attn.q_proj": "q", "self_attn.k_proj": "k", "self_attn.v_proj": "v", "self_attn.o_proj": "o",
+         "mlp.gate_proj": "gate", "mlp.up_proj": "up", "mlp.down_proj": "down"}
+
+
+def _logits_oracle(hidden_bits, lm, input_scale, native):
+    """FP4 lm_head over the whole vocabulary in row chunks of the weight (float64 accumulation, bf16 out):
+    nvfp4_linear's arithmetic (activations quantised once) or the fp32 dequantise-then-matmul oracle."""
+    pw, sw, g = lm
+    if native:
+        xq, xs = o.quantize_bf16_to_fp4(hidden_bits, input_scale)
+        xa = o.dequant_f32(xq, xs, 1.0).astype(np.float64)
+        alpha = np.float32(input_scale) * np.float32(g)
+    else:
+        xa = o.bf16_bits_to_f32(hidden_bits).astype(np.float64)
+        alpha = np.float32(1.0)
+    out = np.empty((hidden_bits.shape[0], pw.shape[0]), np.uint16)
+    for r0 in range(0, pw.shape[0], 8192):
+        w = o.dequant_f32(pw[r0:r0 + 8192], sw[r0:r0 + 8192], 1.0 if native else g).astype(np.float64)
+        acc = (xa @ w.T).astype(np.float32)
+        out[:, r0:r0 + 8192] = o.f32_to_bf16_bits((acc * alpha).astype(np.float32))
+    return out
+
+
+def run_config2_case(mode):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import test_gpu_decoder as tgd
+    from glm_asr_stack_b200 import engine, ops, workloads
+
+    L, n = 2, 256
+    model = workloads.build_decoder(layers=L)
+    cfg = model.cfg
+    state = workloads.build_decode_state(cfg, num_seqs=n)
+    H, QH, KVH, HD = cfg.dec_hidden, cfg.dec_heads, cfg.dec_kv_heads, cfg.dec_head_dim
+    bs = state.pool.block_size
+    gen = torch.Generator(device="cpu").manual_seed(3)
+    ids = torch.randint(0, cfg.vocab_size, (n,), generator=gen, dtype=torch.int32).cuda()
+
+    # ---- numpy views of everything the oracle needs, taken BEFORE the step changes the cache ----
+    keep = model.ws.keep
+    layers = []
+    for l in range(L):
+        Lw = {}
+        for name, short in SHORT.items():
+            pre = f"language_model.model.layers.{l}.{name}"
+            Lw[short] = {"pw": keep[pre + ".weight"].cpu().numpy(), "sw": keep[pre + ".weight_scale"].cpu().numpy(),
+                         "g": float(keep[pre + ".weight_scale_2"].cpu()[0]), "isc": float(keep[pre + ".input_scale"].cpu()[0]),
+                         "pre": None, "bf16": None}
+        Lw["norm1"] = bits_of(keep[f"language_model.model.layers.{l}.input_layernorm.weight"])
+        Lw["norm2"] = bits_of(keep[f"language_model.model.layers.{l}.post_attention_layernorm.weight"])
+        layers.append(Lw)
+    fn = bits_of(keep["language_model.model.norm.weight"])
+    kc = [bits_of(state.pool.k[l].reshape(-1, KVH * HD)).copy() for l in range(L)]
+    vc = [bits_of(state.pool.v[l].reshape(-1, KVH * HD)).copy() for l in range(L)]
+    bt_np = state.pool.tables[:n].cpu().numpy()
+    cached = state.cached.copy()
+    slots = np.array([bt_np[i, cached[i] // bs] * bs + cached[i] % bs for i in range(n)], np.int64)
+
+    # ---- the step, the lm_head, the arg-max ----
+    native = mode != "w4a16"
+    hidden = ops.embedding_lookup(model.embed, ids)
+    hidden0 = bits_of(hidden).copy()
+    engine.decode_step(model.ws, cfg, state.pool, state.bts, hidden, state.d_seq_lens, state.h_seq_lens)
+    lm = model.lm_head
+    logits = torch.empty((n, cfg.vocab_size), dtype=torch.bfloat16, device="cuda")
+    if native:
+        assert ops.nvfp4_linear(logits, hidden, lm.w_packed, lm.w_scales, model.lm_head_input_scale, lm.w_global_scale) == 0
+    else:
+        ops.fp4_linear(hidden, lm.w_packed, lm.w_scales, lm.w_global_scale, out=logits)
+    tokens = ops.argmax_rows(logits).cpu().numpy()
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    got_h, got_l = bits_of(hidden), bits_of(logits)
+    assert np.array_equal(tokens, o.argmax_rows_ref(got_l))                 # the arg-max kernel at full vocabulary
+
+    # ---- oracle, same mix ----
+    lm_np = (lm.w_packed.cpu().numpy(), lm.w_scales.cpu().numpy(), lm.w_global_scale)
+    report = {}
+    want_h = {}
+    for mix in tgd.MODES:
+        k2, v2 = [c.copy() for c in kc], [c.copy() for c in vc]
+        want_h[mix] = do.decode_step(hidden0, layers, fn, k2, v2, bt_np, cached, slots, QH, KVH, HD, bs,
+                                     tgd.oracle_linears(layers, mix))
+        report[f"hidden_cos_vs_{mix}"] = o.cosine(got_h, want_h[mix])
+    own = want_h[mode]
+    err_h = o.rel_err(got_h, own)
+    want_l = _logits_oracle(own, lm_np, model.lm_head_input_scale, native)
+    err_l = o.rel_err(got_l, want_l)
+    cos_l = o.cosine(got_l, want_l)
+    gl, wl = o.bf16_bits_to_f32(got_l), o.bf16_bits_to_f32(want_l)
+    row_cos = (gl * wl).sum(1) / np.sqrt((gl * gl).sum(1) * (wl * wl).sum(1))
+    top2 = np.sort(wl, axis=1)[:, -2:]
+    margin = top2[:, 1] - top2[:, 0]
+    want_tok = wl.argmax(1)
+    clear = margin > 2e-2 * np.abs(top2[:, 1])
+    report.update(hidden_rel=err_h, logits_rel=err_l, logits_cos=cos_l, logits_row_cos_min=float(row_cos.min()),
+                  tokens_equal=float((tokens == want_tok).mean()), clear_rows=int(clear.sum()))
+    # logits of the shipped step against the OTHER mixes' oracles (reported; the reference-mix one is asserted)
+    for mix in tgd.MODES:
+        if mix != mode:
+            other = _logits_oracle(want_h[mix], lm_np, model.lm_head_input_scale, mix != "w4a16")
+            report[f"logits_cos_vs_{mix}"] = o.cosine(got_l, other)
+    print("CONFIG2", mode, report)
+    assert err_h <= REL_TOL_VS_ORACLE, err_h
+    assert err_l <= REL_TOL_VS_ORACLE, err_l
+    assert cos_l >= 0.999 and row_cos.min() >= 0.999, (cos_l, row_cos.min())
+    assert np.array_equal(tokens[clear], want_tok[clear])
+    assert (tokens == want_tok).mean() >= 0.95
+    if mode == "all_w4a4":
+        # the opt-in all-W4A4 step against the reference's own mix (q, o, down native; k|v, gate|up W4A16)
+        assert report["logits_cos_vs_reference"] >= 0.99, report
+    return report
+
+
+@pytest.mark.parametrize("mode", ["w4a16", "reference", "all_w4a4"])
+def test_config2_decode_step_real_shape(mode):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import test_gpu_decoder as tgd
+    env = dict(os.environ, **tgd.MODE_ENV[mode])
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_gpu_config2 as t; t.run_config2_case(%r)"
+            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests"), mode))
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=2400)
+    print(r.stdout[-3000:])
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    assert "CONFIG2" in r.stdout

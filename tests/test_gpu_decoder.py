@@ -197,33 +197,120 @@ def test_embedding_lookup(ops):
 # ---------------------------------------------------------------------------------------------
 # whole decode step on a small model (hidden 256 = 2 heads x 128, 1 kv head, ffn 512, 2 layers)
 # ---------------------------------------------------------------------------------------------
-def run_decode_step_case(w4a4: bool):
+MODES = ("w4a16", "reference", "all_w4a4")
+MODE_ENV = {"w4a16": {"GLMASR_USE_CUTLASS_NVFP4": "0", "GLMASR_NVFP4_PAIRS": "0"},
+            "reference": {"GLMASR_USE_CUTLASS_NVFP4": "1", "GLMASR_NVFP4_PAIRS": "0"},
+            "all_w4a4": {"GLMASR_USE_CUTLASS_NVFP4": "1", "GLMASR_NVFP4_PAIRS": "1"}}
+TOY_NAMES = [("self_attn.q_proj", "q"), ("self_attn.k_proj", "k"), ("self_attn.v_proj", "v"), ("self_attn.o_proj", "o"),
+             ("mlp.gate_proj", "gate"), ("mlp.up_proj", "up"), ("mlp.down_proj", "down")]
+
+
+def run_in_child(func, *args, mode):
+    """The arithmetic switches are read once per process (as in the reference), so every mode runs in a child."""
+    env = dict(os.environ, **MODE_ENV[mode])
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_gpu_decoder as t; print('RESULT', t.%s(*%r))"
+            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests"), func, tuple(args) + (mode,)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=1500)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    assert "RESULT" in r.stdout
+    return r.stdout
+
+
+def _bf16_linear_oracle(x_bits, w_bits):
+    """bf16_linear (Infer-engine/cuda/kernels.cu:1147-1193): fp32 accumulate, bf16 out."""
+    return o.f32_to_bf16_bits(o._matmul_f32(o.bf16_bits_to_f32(x_bits), o.bf16_bits_to_f32(w_bits)))
+
+
+def projection_oracles(Lw, mode):
+    """name -> linear(x_bits, _) for one layer, following the reference's dispatch (linear_proj,
+    Infer-engine/cuda/decoder.cu:861-921; linear_proj_pair_same_input, :923-978) on this layer's tensors:
+    bf16 weights -> bf16_linear; a same-input pair (k|v, gate|up) of plain FP4 weights -> the fused bf16 GEMM on
+    dequantised weights (W4A16), or W4A4 when the pairs are opted in and share their input_scale; everything
+    else -> nvfp4_linear with its own input_scale / pre_quant_scale when the native switch is on, fp4_linear
+    otherwise."""
+    def w4a4(w):
+        return lambda x, _=None: o.nvfp4_linear(x, w["pw"], w["sw"], w["isc"], w["g"], w["pre"])
+
+    def w4a16(w):
+        if w["pre"] is not None:
+            return lambda x, _=None: o.fp4_linear(x, w["pw"], w["sw"], w["g"], w["pre"])
+        return lambda x, _=None: o.linear_o1(x, w["pw"], w["sw"], w["g"])
+
+    def single(w):
+        if w["bf16"] is not None:
+            return lambda x, _=None: _bf16_linear_oracle(x, w["bf16"])
+        return w4a4(w) if mode != "w4a16" else w4a16(w)
+
+    out = {n: single(Lw[n]) for n in ("q", "o", "down")}
+    for a, b in (("k", "v"), ("gate", "up")):
+        wa, wb = Lw[a], Lw[b]
+        fusable = wa["bf16"] is None and wb["bf16"] is None and wa["pre"] is None and wb["pre"] is None
+        if fusable and mode == "all_w4a4" and wa["isc"] == wb["isc"]:
+            out[a], out[b] = w4a4(wa), w4a4(wb)          # one block-scaled GEMM on a shared quantised input
+        elif fusable:
+            out[a], out[b] = w4a16(wa), w4a16(wb)        # the reference's fused pair
+        else:
+            out[a], out[b] = single(wa), single(wb)      # not fused: linear_proj one by one
+    return out
+
+
+def build_toy_model(rng, seed0, variant):
+    """Random FP4 decoder (hidden 256, 2 q / 1 kv head x 128, ffn 512, 2 layers) under the checkpoint's tensor
+    names.  variant: "plain"; "pre" (AWQ-style pre_quant_scale on k, up and down of layer 0 and q of layer 1);
+    "bf16" (v and gate of layer 0 and o of layer 1 stored as bf16); "scales" (different input_scale per projection)."""
     from glm_asr_stack_b200 import engine, ops
-    rng = np.random.default_rng(11)
-    H, F, QH, KVH, HD, L, bs, n = 256, 512, 2, 1, 128, 2, 16, 5
-    cached = np.array([0, 15, 16, 37, 200], np.int32)
-    num_blocks, max_blocks = 64, 16
-    names = [("self_attn.q_proj", H, H), ("self_attn.k_proj", KVH * HD, H), ("self_attn.v_proj", KVH * HD, H),
-             ("self_attn.o_proj", H, H), ("mlp.gate_proj", F, H), ("mlp.up_proj", F, H), ("mlp.down_proj", H, F)]
+    H, F, QH, KVH, HD, L = 256, 512, 2, 1, 128, 2
+    dims = {"q": (H, H), "k": (KVH * HD, H), "v": (KVH * HD, H), "o": (H, H), "gate": (F, H), "up": (F, H), "down": (H, F)}
+    pre_on = {(0, "k"), (0, "up"), (0, "down"), (1, "q")} if variant == "pre" else set()
+    bf16_on = {(0, "v"), (0, "gate"), (1, "o")} if variant == "bf16" else set()
     ws = engine.WeightStore()
     layers = []
-    isc = 0.02
     for l in range(L):
         Lw = {}
-        for i, (nm, N, K) in enumerate(names):
-            pw, sw, g = o.seeded_weight(N, K, 100 * l + i)
-            w = ops.Fp4Tensor(torch.from_numpy(pw).cuda(), torch.from_numpy(sw).cuda(), g)
-            ws.add_fp4(f"language_model.model.layers.{l}.{nm}", w, isc)
-            Lw[nm.split(".")[1].split("_")[0]] = (pw, sw, g)
+        for i, (nm, short) in enumerate(TOY_NAMES):
+            N, K = dims[short]
+            isc = 0.02 * (1.0 + 0.25 * i) if variant == "scales" else 0.02
+            ent = {"pw": None, "sw": None, "g": None, "pre": None, "bf16": None, "isc": isc}
+            prefix = f"language_model.model.layers.{l}.{nm}"
+            if (l, short) in bf16_on:
+                wb = rnd_bits(rng, (N, K), 0.02)
+                ent["bf16"] = wb
+                ws.add(prefix + ".weight", to_dev_bf16(wb))
+            else:
+                pw, sw, g = o.seeded_weight(N, K, seed0 + 100 * l + i)
+                ent.update(pw=pw, sw=sw, g=g)
+                ws.add_fp4(prefix, ops.Fp4Tensor(torch.from_numpy(pw).cuda(), torch.from_numpy(sw).cuda(), g), isc)
+                if (l, short) in pre_on:
+                    pre = o.f32_to_bf16_bits(rng.uniform(0.5, 2.0, K).astype(np.float32))
+                    ent["pre"] = pre
+                    ws.add(prefix + ".pre_quant_scale", to_dev_bf16(pre))
+            Lw[short] = ent
         for nm in ("input_layernorm", "post_attention_layernorm"):
-            nb = rnd_bits(rng, (H,), 0.2) + 0                                   # weights around 0 -> add 1 below
-            nb = o.f32_to_bf16_bits(o.bf16_bits_to_f32(nb) + 1.0)
+            nb = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
             ws.add(f"language_model.model.layers.{l}.{nm}.weight", to_dev_bf16(nb))
             Lw["norm1" if nm == "input_layernorm" else "norm2"] = nb
         layers.append(Lw)
     fn = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
     ws.add("language_model.model.norm.weight", to_dev_bf16(fn))
     cfg = engine.model_config(H, L, QH, KVH, HD, F, 1000)
+    return ws, cfg, layers, fn, (H, F, QH, KVH, HD, L)
+
+
+def oracle_linears(layers, mode):
+    """decoder_oracle takes one dict name -> linear(x, w) for all layers; the variants differ per layer, so the
+    functions handed to it look the layer's own oracle up from the weight entry they are given."""
+    per_layer = [projection_oracles(Lw, mode) for Lw in layers]
+    index = {id(Lw[n]): per_layer[l][n] for l, Lw in enumerate(layers) for n in do.PROJECTIONS}
+    return {n: (lambda x, w: index[id(w)](x)) for n in do.PROJECTIONS}
+
+
+def run_decode_step_case(variant="plain", mode="w4a16"):
+    from glm_asr_stack_b200 import engine, ops
+    rng = np.random.default_rng(11)
+    ws, cfg, layers, fn, (H, F, QH, KVH, HD, L) = build_toy_model(rng, 0, variant)
+    bs, n = 16, 5
+    cached = np.array([0, 15, 16, 37, 200], np.int32)
+    num_blocks, max_blocks = 64, 16
     pool = engine.KVPool(num_blocks, bs, L, KVH, HD, max_seqs=8, max_blocks_per_seq=max_blocks)
     # block tables: enough blocks for cached + 1 tokens, taken from a permutation
     perm = rng.permutation(num_blocks).tolist()
@@ -249,22 +336,18 @@ def run_decode_step_case(w4a4: bool):
     assert ops.status() == 0
     # oracle
     slots = np.array([bt_np[i, cached[i] // bs] * bs + cached[i] % bs for i in range(n)], np.int64)
-    if w4a4:
-        lin = lambda x, w: o.nvfp4_linear(x, w[0], w[1], isc, w[2])
-    else:
-        lin = lambda x, w: o.linear_o1(x, *w)
     kc, vc = [kc0[l].copy() for l in range(L)], [vc0[l].copy() for l in range(L)]
-    want = do.decode_step(hidden, layers, fn, kc, vc, bt_np, cached, slots, QH, KVH, HD, bs, lin)
+    want = do.decode_step(hidden, layers, fn, kc, vc, bt_np, cached, slots, QH, KVH, HD, bs, oracle_linears(layers, mode))
     got = bits_of(hd_dev)
     err = o.rel_err(got, want)
     assert err <= REL_TOL_VS_ORACLE, err
     assert o.cosine(got, want) >= 0.999
     assert list(h_lens) == (cached + 1).tolist() and d_lens.cpu().numpy().tolist() == (cached + 1).tolist()
-    # the new token's K/V landed in its slot, everything else is untouched.  Under W4A4 the inputs of
-    # layers > 0 are re-quantised to e2m1, and a value that sits on a rounding boundary flips its code on a
-    # last-bit difference of the previous layer (summation order, bf16 P in the attention), so the rows of
-    # later layers are held to 5e-2 there; the step's output keeps the 1e-2 / cosine 0.999 bar above.
-    kv_tol = 5e-2 if w4a4 else REL_TOL_VS_ORACLE
+    # the new token's K/V landed in its slot, everything else is untouched.  Where a projection's input is
+    # re-quantised to e2m1 (W4A4), a value that sits on a rounding boundary flips its code on a last-bit
+    # difference of the previous layer (summation order, bf16 P in the attention), so the rows of later layers
+    # are held to 5e-2 there; the step's output keeps the 1e-2 / cosine 0.999 bar above.
+    kv_tol = 5e-2 if mode != "w4a16" else REL_TOL_VS_ORACLE
     for l in range(L):
         kd = bits_of(pool.k[l].reshape(num_blocks * bs, -1))
         mask = np.ones(num_blocks * bs, bool)
@@ -273,21 +356,6 @@ def run_decode_step_case(w4a4: bool):
         assert o.rel_err(kd[slots], kc[l][slots]) <= kv_tol
         assert o.rel_err(bits_of(pool.v[l].reshape(num_blocks * bs, -1))[slots], vc[l][slots]) <= kv_tol
     return err
-
-
-def test_decode_step_w4a16_vs_oracle():
-    os.environ.pop("GLMASR_USE_CUTLASS_NVFP4", None)
-    run_decode_step_case(False)
-
-
-def test_decode_step_w4a4_vs_oracle_in_subprocess():
-    """The W4A4 switch is read once per process (as in the reference), so run it in a child."""
-    env = dict(os.environ, GLMASR_USE_CUTLASS_NVFP4="1")
-    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_gpu_decoder as t; print('ERR', t.run_decode_step_case(True))"
-            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")))
-    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout + r.stderr
-    assert "ERR" in r.stdout
 
 
 # ---------------------------------------------------------------------------------------------
@@ -391,37 +459,19 @@ def test_prefill_attention_sequences_with_gaps(ops):
     assert np.array_equal(whole[lens[0]:lens[0] + lens[1]], alone)
 
 
-def run_prefill_case(w4a4: bool):
+def run_prefill_case(variant="plain", lens=(70, 1, 33, 130), mode="w4a16"):
     """decoder_prefill_paged_batched on a small model against the oracle's layer sequence, then one decode
     step on top of the cache the prefill wrote (the two drivers must agree on the cache layout)."""
     from glm_asr_stack_b200 import engine, ops
     rng = np.random.default_rng(21)
-    H, F, QH, KVH, HD, L, bs = 256, 512, 2, 1, 128, 2, 16
-    lens = [70, 1, 33, 130]
+    bs = 16
+    lens = list(lens)
     offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)[:-1]
     T, n = int(sum(lens)), len(lens)
-    num_blocks, max_blocks = 64, 16
-    names = [("self_attn.q_proj", H, H), ("self_attn.k_proj", KVH * HD, H), ("self_attn.v_proj", KVH * HD, H),
-             ("self_attn.o_proj", H, H), ("mlp.gate_proj", F, H), ("mlp.up_proj", F, H), ("mlp.down_proj", H, F)]
-    ws = engine.WeightStore()
-    layers = []
-    isc = 0.02
-    for l in range(L):
-        Lw = {}
-        for i, (nm, N, K) in enumerate(names):
-            pw, sw, g = o.seeded_weight(N, K, 300 + 100 * l + i)
-            ws.add_fp4(f"language_model.model.layers.{l}.{nm}",
-                       ops.Fp4Tensor(torch.from_numpy(pw).cuda(), torch.from_numpy(sw).cuda(), g), isc)
-            Lw[nm.split(".")[1].split("_")[0]] = (pw, sw, g)
-        for nm in ("input_layernorm", "post_attention_layernorm"):
-            nb = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
-            ws.add(f"language_model.model.layers.{l}.{nm}.weight", to_dev_bf16(nb))
-            Lw["norm1" if nm == "input_layernorm" else "norm2"] = nb
-        layers.append(Lw)
-    fn = o.f32_to_bf16_bits(o.bf16_bits_to_f32(rnd_bits(rng, (H,), 0.2)) + 1.0)
-    ws.add("language_model.model.norm.weight", to_dev_bf16(fn))
-    cfg = engine.model_config(H, L, QH, KVH, HD, F, 1000)
-    pool = engine.KVPool(num_blocks, bs, L, KVH, HD, max_seqs=8, max_blocks_per_seq=max_blocks)
+    ws, cfg, layers, fn, (H, F, QH, KVH, HD, L) = build_toy_model(rng, 300, variant)
+    max_blocks = (max(lens) + 1 + bs - 1) // bs + 1
+    num_blocks = sum((ln + 1 + bs - 1) // bs for ln in lens) + 8
+    pool = engine.KVPool(num_blocks, bs, L, KVH, HD, max_seqs=max(8, n), max_blocks_per_seq=max_blocks)
     perm = rng.permutation(num_blocks).tolist()
     tables = [[perm.pop() for _ in range((ln + 1 + bs - 1) // bs)] for ln in lens]     # room for one decoded token
     bts = engine.BlockTables(pool, tables)
@@ -435,7 +485,7 @@ def run_prefill_case(w4a4: bool):
     engine.prefill_paged_batched(ws, cfg, pool, bts, hd_dev, lens, offs.tolist())
     torch.cuda.synchronize()
     assert ops.status() == 0
-    lin = (lambda x, w: o.nvfp4_linear(x, w[0], w[1], isc, w[2])) if w4a4 else (lambda x, w: o.linear_o1(x, *w))
+    lin = oracle_linears(layers, mode)
     slots = np.concatenate([[bt_np[s, t // bs] * bs + t % bs for t in range(ln)] for s, ln in enumerate(lens)]).astype(np.int64)
     kc = [np.zeros((num_blocks * bs, KVH * HD), np.uint16) for _ in range(L)]
     vc = [np.zeros((num_blocks * bs, KVH * HD), np.uint16) for _ in range(L)]
@@ -444,7 +494,7 @@ def run_prefill_case(w4a4: bool):
     err = o.rel_err(got, want)
     assert err <= REL_TOL_VS_ORACLE, err
     assert o.cosine(got, want) >= 0.999
-    kv_tol = 5e-2 if w4a4 else REL_TOL_VS_ORACLE      # see run_decode_step_case for the W4A4 bound
+    kv_tol = 5e-2 if mode != "w4a16" else REL_TOL_VS_ORACLE      # see run_decode_step_case for the W4A4 bound
     for l in range(L):
         kd = bits_of(pool.k[l].reshape(num_blocks * bs, -1))
         mask = np.ones(num_blocks * bs, bool)
@@ -473,15 +523,27 @@ def run_prefill_case(w4a4: bool):
     return err
 
 
-def test_prefill_w4a16_vs_oracle():
-    os.environ.pop("GLMASR_USE_CUTLASS_NVFP4", None)
-    run_prefill_case(False)
+def run_driver_suite(mode="w4a16"):
+    """Every driver case of one arithmetic mode in ONE process (the switches are read once per process)."""
+    done = []
+    for variant in ("plain", "pre", "bf16", "scales"):
+        # plain: the mode's own mix.  pre: projections with a pre_quant_scale (their pairs are then not fused and go
+        # through linear_proj one by one).  bf16: projections stored as bf16.  scales: a different input_scale for
+        # every projection (pairs opted in to W4A4 then fall back to the fused W4A16 GEMM).
+        done.append(("decode", variant, run_decode_step_case(variant, mode)))
+        done.append(("prefill", variant, run_prefill_case(variant, (70, 1, 33, 130), mode)))
+    if mode != "w4a16":
+        # more than 1024 token rows: W4A16 pairs then dequantise each weight once and run the bf16 GEMM (whose
+        # SiLU-gate epilogue quantises for the native down projection)
+        done.append(("prefill-1151-rows", "plain", run_prefill_case("plain", (400, 394, 300, 57), mode)))
+    return done
 
 
-def test_prefill_w4a4_vs_oracle_in_subprocess():
-    env = dict(os.environ, GLMASR_USE_CUTLASS_NVFP4="1")
-    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_gpu_decoder as t; print('ERR', t.run_prefill_case(True))"
-            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")))
-    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout + r.stderr
-    assert "ERR" in r.stdout
+@pytest.mark.parametrize("mode", MODES)
+def test_decoder_drivers_vs_oracle(mode):
+    """decoder_decode_step_batched and decoder_prefill_paged_batched on the small model, against the oracle
+    with the same per-projection arithmetic: W4A16 (no switch), the reference's mix under
+    GLMASR_USE_CUTLASS_NVFP4=1 (q, o, down native; k|v and gate|up as fused W4A16 pairs) and the opt-in
+    all-W4A4 step (GLMASR_NVFP4_PAIRS=1), including the dispatcher's fall-backs."""
+    out = run_in_child("run_driver_suite", mode=mode)
+    assert "prefill" in out and "decode" in out

@@ -433,3 +433,39 @@ def test_split_k_in_subprocess():
         r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, GLMASR_SPLIT_K=factor), capture_output=True,
                            text=True, timeout=600)
         assert r.returncode == 0 and "SPLIT OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("mode_name", ["w4a4", "w4a16"])
+def test_config1_layer_row_sample_vs_oracle_chain(ops, mode_name):
+    """Benchmark configuration 1 at full size (M = 10000, hidden 2048, q|k|v 3072, ffn 6144): all four projections
+    through glmasr_fp4_layer_proj -- at these sizes the CTA-pair kernels, gate|up with the SiLU-gate epilogue
+    that quantises for down -- against the oracle's chain on a row sample (rows are independent): rows 0, 127, 128
+    (tile boundaries), 5000 and 9999 (last row of the 16-row tail tile)."""
+    from glm_asr_stack_b200 import synth
+    H, F, KVW, M = 2048, 6144, 512, 10000
+    names = [("q", H, H), ("k", KVW, H), ("v", KVW, H), ("o", H, H), ("gate", F, H), ("up", F, H), ("down", H, F)]
+    w = {n: synth.seeded_weight_fast(N, K, 1000 + i) for i, (n, N, K) in enumerate(names)}
+    x = synth.seeded_activation(M, H, 1)
+    isc = {"qkv": synth.default_input_scale(x), "o": 0.004, "gate_up": 0.004, "down": 0.002}
+    w["q"].input_scale = w["k"].input_scale = w["v"].input_scale = isc["qkv"]
+    w["o"].input_scale = isc["o"]
+    w["gate"].input_scale = w["up"].input_scale = isc["gate_up"]
+    w["down"].input_scale = isc["down"]
+    lw = ops.make_layer_weights(w["q"], w["k"], w["v"], w["o"], w["gate"], w["up"], w["down"], H, F)
+    mode = ops.MODE_W4A4 if mode_name == "w4a4" else ops.MODE_W4A16
+    got = ops.layer_proj(mode, x, lw)
+    assert ops.status() == 0
+    rows = [0, 127, 128, 5000, 9999]
+    xb = bits_of(x[rows])
+    npw = {n: (t.w_packed.cpu().numpy(), t.w_scales.cpu().numpy(), t.w_global_scale) for n, t in w.items()}
+    if mode_name == "w4a4":
+        lin = lambda xx, n, s: o.nvfp4_linear(xx, npw[n][0], npw[n][1], s, npw[n][2])
+    else:
+        lin = lambda xx, n, s: o.linear_o1(xx, *npw[n])
+    q = lin(xb, "q", isc["qkv"])                      # the q slice of q|k|v stands in for the attention output
+    h1 = o.residual_add(lin(q, "o", isc["o"]), xb)
+    act = o.silu_mul_split_packed(np.concatenate([lin(h1, "gate", isc["gate_up"]), lin(h1, "up", isc["gate_up"])], 1))
+    want = o.residual_add(lin(act, "down", isc["down"]), h1)
+    err = o.rel_err(bits_of(got[rows]), want)
+    assert err <= REL_TOL_VS_ORACLE, err
+    assert o.cosine(bits_of(got[rows]), want) >= 0.999

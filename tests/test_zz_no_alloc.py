@@ -57,3 +57,35 @@ def test_noalloc_rejects_sizes_beyond_its_scratch():
     assert lib.glmasr_nvfp4_linear_noalloc(P(out), P(x), P(w), P(s), 0.0, 1.0, 8, 128, 256) == -1       # bad input_scale
     torch.cuda.synchronize()
     assert torch.all(out == 3.0)
+
+
+def _cold_first_call():
+    """Body of the child process below: the allocation-free entry point is the FIRST call this process makes
+    into the library, so the look-up of its array, the kernels' shared-memory opt-in and the loading of the
+    module that holds them all happen inside it."""
+    from glm_asr_stack_b200 import ops
+    M, N, K, seed = 96, 384, 512, 930
+    pw, sw, g = o.seeded_weight(N, K, seed)
+    x = o.seeded_activation(M, K, seed + 1)
+    isc = o.default_input_scale(x)
+    xd, wd, sd = to_dev_bf16(x), to_dev_u8(pw), to_dev_u8(sw)
+    got = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    assert ops.launch_count() == 0
+    assert ops.nvfp4_linear_noalloc(got, xd, wd, sd, isc, g) == 0
+    torch.cuda.synchronize()
+    assert ops.status() == 0                  # reads the status word inside the library image as well
+    err = o.rel_err(bits_of(got), o.nvfp4_linear(x, pw, sw, isc, g))
+    assert err <= REL_TOL_TIGHT, err
+    print("COLD_OK", err)
+
+
+def test_noalloc_as_the_first_library_call_of_a_process():
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]; import test_zz_no_alloc as t; t._cold_first_call()"
+            % (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "COLD_OK" in r.stdout
