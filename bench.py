@@ -8,6 +8,14 @@ One step = q|k|v GEMM, o GEMM + residual, gate|up GEMM + SiLU-gate, down GEMM + 
 (964.7 GFLOP) on synthetic seeded weights and activations.  Prints ONE JSON line (rank 0).
 Under torchrun every rank runs the same workload on its own GPU (data-parallel replicas, no
 data-path collective); the value is the whole-job aggregate, time = max over ranks.
+
+The headline value is SUSTAINED: the K-step block is repeated back to back inside one CUDA-event pair
+until the timed region lasts at least a second (`repeats`, `timed_region_s`), with the SM clock sampled
+over that region; the figure of a single K-step block (a few milliseconds, before the power cap bites) is
+reported beside it as `burst`.  The same line carries, as `secondary`, benchmark configuration 2 (the
+batched decode step: tok/s and HBM fractions) and the whole batched prefill, each in the reference's
+projection mix and with every projection in W4A4, and in `roofline` the library FP4 GEMM (cuBLASLt)
+timed alone on the same shapes.
 """
 import argparse
 import json
@@ -161,18 +169,21 @@ def cpu_reference_leg(steps, warmup, sample_rows):
 
 
 def run_reference(args, rank):
+    """`--impl reference`: the reference's arithmetic for this path on the host cores, all 10000 rows of the
+    workload per step (the same configuration as the GPU arm), rank 0 only."""
     if rank != 0:
         return
-    sample = 512
-    tflops, sec, threads = cpu_reference_leg(args.steps, max(args.warmup, 1), sample)
+    rows = args.rows
+    warm = max(args.warmup, 1)
+    tflops, sec, threads = cpu_reference_leg(args.steps, warm, rows)
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x fp32-accumulate (weights dequantised from e2m1 every call)",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": f"first {sample} of {M_TOKENS} rows per step"},
+        "config": {"workload": WORKLOAD, "rows": rows, "sample": f"all {rows} rows per step"},
         "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{sample} of {M_TOKENS} rows, all four projections, full weights, torch CPU"},
+                         "sample": f"all {rows} rows, all four projections, full weights, torch CPU"},
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no CPU implementation of this path; this is its fallback arithmetic "
                 "(dequantise whole weight each call + fp32-accumulate GEMM) restated with torch on the host cores",
@@ -180,30 +191,164 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def run_decode(args, rank, local_rank, world):
-    """Benchmark configuration 2: one batched decode step of the 28-layer decoder + FP4 lm_head + arg-max for
-    256 sequences with paged bf16 KV (16-token pages, context 200-450).  tok/s = sequences / step time."""
-    os.environ["GLMASR_USE_CUTLASS_NVFP4"] = "1" if args.mode == "w4a4" else "0"
+# ---------------------------------------------------------------------------------------------------------
+# helpers shared by the workloads
+# ---------------------------------------------------------------------------------------------------------
+def set_projection_mix(mix):
+    """Select the decoder drivers' per-projection arithmetic: "w4a16", "reference" (GLMASR_USE_CUTLASS_NVFP4=1: q, o,
+    down native, k|v and gate|up fused W4A16 pairs, as the reference does) or "all_w4a4" (+ GLMASR_NVFP4_PAIRS=1).
+    The library re-reads the two variables after glmasr_decoder_forget_weights()."""
+    from glm_asr_stack_b200 import _lib
+    os.environ["GLMASR_USE_CUTLASS_NVFP4"] = "0" if mix == "w4a16" else "1"
+    os.environ["GLMASR_NVFP4_PAIRS"] = "1" if mix == "all_w4a4" else "0"
+    _lib.load().glmasr_decoder_forget_weights()
+
+
+def pin_to_gpu_numa_node(local_rank):
+    """Best effort: run this process on the cores of the NUMA node the GPU hangs off, BEFORE the pinned staging
+    buffers are allocated, so that they are first-touched in memory local to the GPU's PCIe root.  Returns the
+    node (or None when the topology files are not there)."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev = torch.cuda.get_device_properties(local_rank).pci_device_id
+        base = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0"
+        node = int(open(base + "/numa_node").read().strip())
+        cpus = open(base + "/local_cpulist").read().strip()
+        ids = set()
+        for part in cpus.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                ids.update(range(int(a), int(b) + 1))
+            elif part:
+                ids.add(int(part))
+        allowed = os.sched_getaffinity(0) & ids
+        if allowed and node >= 0:
+            os.sched_setaffinity(0, allowed)
+            return node
+    except Exception:
+        pass
+    return None
+
+
+def timed_steps(step, steps, barrier, sampler=None, min_seconds=0.0, counter=None):
+    """CUDA-event time of `steps` calls of step(i), repeated back to back inside ONE event pair until the region
+    lasts at least min_seconds (the repeat count comes from an untimed calibration block).  Returns
+    (ms per step, repeats, region seconds, launches counted by counter() inside the timed region)."""
+    import torch
+    repeats = 1
+    if min_seconds > 0.0:
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for i in range(steps):
+            step(i)
+        c1.record()
+        torch.cuda.synchronize()
+        block_s = max(c0.elapsed_time(c1) * 1e-3, 1e-6)
+        repeats = max(1, int(min_seconds / block_s * 1.1) + 1)
+    barrier()
+    if sampler is not None:
+        sampler.start()
+    n0 = counter() if counter is not None else 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for r in range(repeats):
+        for i in range(steps):
+            step(i)
+    e1.record()
+    launches = (counter() - n0) if counter is not None else 0
+    if sampler is not None:
+        sampler.sample_now()          # the GPU is still working through the timed steps queued above
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    return total_ms / (steps * repeats), repeats, total_ms * 1e-3, launches
+
+
+def pcie_floors(nbytes, dist, device):
+    """What the host link allows for one step's traffic: nbytes host->device alone, device->host alone, and both
+    at once (pinned buffers, two streams), each the best of 5 after a warm-up, max over ranks -- every rank
+    copies at the same time, as in the end-to-end region."""
+    import torch
+    h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    d_out = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    out = {}
+    for name in ("h2d", "d2h", "both"):
+        best = float("inf")
+        for it in range(6):
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if name in ("h2d", "both"):
+                with torch.cuda.stream(s_in):
+                    d_in.copy_(h_in, non_blocking=True)
+            if name in ("d2h", "both"):
+                with torch.cuda.stream(s_out):
+                    h_out.copy_(d_out, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) * 1e3
+            if it > 0:
+                best = min(best, dt)
+        out[name] = replicas.max_over_ranks(best, dist, "cuda")
+    return out
+
+
+def library_fp4_yardstick(shapes, big=8192):
+    """cuBLASLt's block-scaled FP4 GEMM timed alone (oracle/cublaslt_fp4_probe.cu) on 8192^3 and on the benchmark's
+    shapes.  Returns (dict, None) or (None, reason)."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "libcublaslt_fp4_probe.so")
+    if not os.path.exists(path):
+        return None, "oracle/libcublaslt_fp4_probe.so not built"
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        return None, f"cannot load the probe: {e}"
+    fn = lib.cublaslt_fp4_gemm_time
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int] * 7 + [ctypes.POINTER(ctypes.c_double)] * 2
+    res = {}
+    best, first = ctypes.c_double(), ctypes.c_double()
+    if fn(big, big, big, 20, 3, 2, 4, ctypes.byref(best), ctypes.byref(first)) != 0:
+        return None, "cublasLt FP4 GEMM probe failed at 8192^3"
+    res["peak_shape"] = f"{big}^3"
+    res["peak_ms"] = best.value
+    res["peak_tflops"] = 2.0 * big ** 3 / (best.value * 1e-3) / 1e12
+    res["shapes"] = {}
+    for name, (M, N, K) in shapes.items():
+        if fn(M, N, K, 20, 3, 4, 4, ctypes.byref(best), ctypes.byref(first)) == 0:
+            res["shapes"][name] = {"M": M, "N": N, "K": K, "ms": best.value, "ms_first_heuristic": first.value,
+                                   "tflops": 2.0 * M * N * K / (best.value * 1e-3) / 1e12}
+    return res, None
+
+
+# ---------------------------------------------------------------------------------------------------------
+# benchmark configuration 2 (decode) and the whole batched prefill
+# ---------------------------------------------------------------------------------------------------------
+def measure_decode(model, state, mix, steps, warmup, dist, local_rank, world, min_seconds=0.0):
+    """One batched decode step of the decoder + FP4 lm_head + arg-max for state's sequences, paged bf16 KV.
+    tok/s = sequences / step time.  Returns the result dict (all ranks; values are max-over-ranks based)."""
     import torch
 
-    from glm_asr_stack_b200 import engine, ops, workloads
-
-    torch.cuda.set_device(local_rank)
-    dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
-    model = workloads.build_decoder(layers=args.layers)
-    state = workloads.build_decode_state(model.cfg, num_seqs=args.seqs)
-    cfg, lm, n, vocab = model.cfg, model.lm_head, args.seqs, model.cfg.vocab_size
+    from glm_asr_stack_b200 import engine, ops
+    set_projection_mix(mix)
+    native = mix != "w4a16"
+    cfg, lm, n, vocab = model.cfg, model.lm_head, len(state.cached), model.cfg.vocab_size
     gen = torch.Generator(device="cpu").manual_seed(3)
     ids_host = torch.randint(0, vocab, (n,), generator=gen, dtype=torch.int32).pin_memory()
     ids = ids_host.cuda()
     logits = torch.empty((n, vocab), dtype=torch.bfloat16, device="cuda")
     tok_host = torch.empty(n, dtype=torch.int32).pin_memory()
 
-    def step(ids_dev):
+    def step_ids(ids_dev):
         state.reset_lengths()                      # same context every step: the step rewrites the same KV slot
         hidden = ops.embedding_lookup(model.embed, ids_dev)
         engine.decode_step(model.ws, cfg, state.pool, state.bts, hidden, state.d_seq_lens, state.h_seq_lens)
-        if args.mode == "w4a4":
+        if native:
             assert ops.nvfp4_linear(logits, hidden, lm.w_packed, lm.w_scales, model.lm_head_input_scale,
                                     lm.w_global_scale) == 0
         else:
@@ -215,77 +360,65 @@ def run_decode(args, rank, local_rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step(ids)
+    for _ in range(warmup):
+        step_ids(ids)
     torch.cuda.synchronize()
     _st = ops.status()
     assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
     sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    l0 = ops.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step(ids)
-    e1.record()
-    sampler.sample_now()          # the GPU is still working through the timed steps queued above
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = ops.launch_count() - l0
+    ms, repeats, region_s, launches = timed_steps(lambda i: step_ids(ids), steps, barrier, sampler, min_seconds,
+                                                  counter=ops.launch_count)
     clocks = sampler.stop()
+    # GEMM time of one step: every projection (and the lm_head) bracketed by events.  The brackets keep a launch
+    # from overlapping its neighbours, so the sum is an upper bound of what the GEMMs cost inside the live step.
+    ops.profile_enable(True)
+    step_ids(ids)
+    prof = ops.profile_read()
+    ops.profile_enable(False)
+    gemm_ms = sum(m for m, _, _ in prof)
     # end to end: token ids from pinned host memory in, next-token ids back to the host
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        tok_host.copy_(step(ids_host.cuda(non_blocking=True)), non_blocking=True)
+    for _ in range(steps):
+        tok_host.copy_(step_ids(ids_host.cuda(non_blocking=True)), non_blocking=True)
         torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    e2e_ms = (time.perf_counter() - t0) / steps * 1e3
     ms = replicas.max_over_ranks(ms, dist, "cuda")
     e2e_ms = replicas.max_over_ranks(e2e_ms, dist, "cuda")
-    H, KV = cfg.dec_hidden, cfg.dec_kv_heads * cfg.dec_head_dim
+    H, KVW = cfg.dec_hidden, cfg.dec_kv_heads * cfg.dec_head_dim
     # algorithmic bytes per step: FP4 weights once, K and V of every cached token once, the new token's K/V,
     # embedding rows, logits written then read by the arg-max
-    bytes_step = model.weight_bytes + state.kv_read_bytes + n * KV * 2 * 2 * cfg.dec_layers + n * H * 2 + 2 * n * vocab * 2
+    bytes_step = model.weight_bytes + state.kv_read_bytes + n * KVW * 2 * 2 * cfg.dec_layers + n * H * 2 + 2 * n * vocab * 2
     peaks = measured_peaks()
     peak = peaks["hbm_gbs"] if peaks else 6650.0
-    if rank == 0:
-        gbs = bytes_step / (ms * 1e-3) / 1e9
-        print(json.dumps({
-            "metric": "decode_tok_per_s", "value": replicas.whole_job_rate(n, world, ms * 1e-3), "unit": "tok/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
-            "config": {"workload": f"config2: batched decode step, {cfg.dec_layers} layers, {n} sequences, paged bf16 KV "
-                                   "(16-token pages, context 200-450), FP4 lm_head over 59264 + arg-max",
-                       "l2": f"{bytes_step / 1e9:.2f} GB touched per step > 126 MB L2"},
-            "e2e": {"value": replicas.whole_job_rate(n, world, e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": n * 4,
-                    "d2h_bytes_per_step": n * 4, "ms_per_step": e2e_ms},
-            "gpu_launches": int(launches), "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "whole decode step (weights + KV stream)", "achieved": gbs, "peak": peak,
-                         "unit": "GB/s", "frac": gbs / peak, "traffic": None, "bytes_per_step": bytes_step,
-                         "weight_bytes": model.weight_bytes, "kv_read_bytes": state.kv_read_bytes,
-                         "peak_source": "measured HBM copy bandwidth (MEASURED_PEAKS.json)" if peaks else "fallback"},
-        }), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    gbs = bytes_step / (ms * 1e-3) / 1e9
+    wgbs = model.weight_bytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else None
+    return {
+        "metric": "decode_tok_per_s", "value": replicas.whole_job_rate(n, world, ms * 1e-3), "unit": "tok/s",
+        "ms_per_step": ms, "steps": steps, "repeats": repeats, "timed_region_s": region_s, "projection_mix": mix,
+        "workload": f"config2: batched decode step, {cfg.dec_layers} layers, {n} sequences, paged bf16 KV "
+                    "(16-token pages, context 200-450), FP4 lm_head over 59264 + arg-max",
+        "e2e": {"value": replicas.whole_job_rate(n, world, e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": n * 4,
+                "d2h_bytes_per_step": n * 4, "ms_per_step": e2e_ms},
+        "gpu_launches_per_step": int(launches // max(1, steps * repeats)), "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "whole decode step (weights + KV stream)", "achieved": gbs, "peak": peak,
+                     "unit": "GB/s", "frac": gbs / peak, "bytes_per_step": bytes_step,
+                     "weight_bytes": model.weight_bytes, "kv_read_bytes": state.kv_read_bytes,
+                     "peak_source": "measured HBM copy bandwidth (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
+                     "weight_stream": {"gemm_ms_per_step": gemm_ms, "gemm_launches": len(prof), "achieved": wgbs,
+                                       "frac": (wgbs / peak) if wgbs else None,
+                                       "how": "FP4 weight bytes / sum of the event-bracketed GEMM launches of one step"}},
+    }
 
 
-def run_prefill(args, rank, local_rank, world):
-    """The whole batched prefill the config-1 projections belong to: 28 layers over 25 windows x 400 tokens
-    (10000 tokens) through decoder_prefill_paged_batched -- projections, RoPE + paged-cache write, causal
-    attention.  tok/s = prefilled tokens / step time; TFLOP/s counts the projections and the attention."""
-    os.environ["GLMASR_USE_CUTLASS_NVFP4"] = "1" if args.mode == "w4a4" else "0"
+def measure_prefill(model, st, mix, steps, warmup, dist, local_rank, world):
+    """The whole batched prefill: all layers over st's sequences through decoder_prefill_paged_batched --
+    projections, RoPE + paged-cache write, causal attention.  tok/s = prefilled tokens / step time."""
     import torch
 
-    from glm_asr_stack_b200 import engine, ops, synth, workloads
-
-    torch.cuda.set_device(local_rank)
-    dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
-    model = workloads.build_decoder(layers=args.layers)
+    from glm_asr_stack_b200 import engine, ops, synth
+    set_projection_mix(mix)
     cfg = model.cfg
-    nseq = max(1, args.rows // 400)
-    st = workloads.build_prefill_state(cfg, num_seqs=nseq, seq_len=400)
     T, H = st.total_tokens, cfg.dec_hidden
     xs = [synth.seeded_activation(T, H, 31 + i) for i in range(2)]
     hid = torch.empty_like(xs[0])
@@ -301,51 +434,71 @@ def run_prefill(args, rank, local_rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
+    for i in range(warmup):
         step(i)
     torch.cuda.synchronize()
     _st = ops.status()
     assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
     sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    l0 = ops.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    sampler.sample_now()          # the GPU is still working through the timed steps queued above
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = ops.launch_count() - l0
+    ms, _, region_s, launches = timed_steps(step, steps, barrier, sampler, counter=ops.launch_count)
     clocks = sampler.stop()
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(steps):
         hid.copy_(hin, non_blocking=True)
         engine.prefill_paged_batched(model.ws, cfg, st.pool, st.bts, hid, st.seq_lens, st.seq_offsets)
         hout.copy_(hid, non_blocking=True)
         torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    e2e_ms = (time.perf_counter() - t0) / steps * 1e3
     ms = replicas.max_over_ranks(ms, dist, "cuda")
     e2e_ms = replicas.max_over_ranks(e2e_ms, dist, "cuda")
     QH, HD = cfg.dec_heads, cfg.dec_head_dim
     attn_flops = sum(2 * 2 * QH * HD * (ln * (ln + 1) // 2) for ln in st.seq_lens)          # QK^T and PV, causal half
     flops = cfg.dec_layers * (layer_flops(T) + attn_flops)
+    return {
+        "metric": "prefill_tok_per_s", "value": replicas.whole_job_rate(T, world, ms * 1e-3), "unit": "tok/s",
+        "ms_per_step": ms, "steps": steps, "timed_region_s": region_s, "projection_mix": mix,
+        "workload": f"batched prefill, {cfg.dec_layers} layers, {len(st.seq_lens)} sequences x {st.seq_lens[0]} tokens = {T} "
+                    "tokens, paged bf16 KV (16-token pages)",
+        "tflops": replicas.whole_job_rate(flops, world, ms * 1e-3) / 1e12,
+        "e2e": {"value": replicas.whole_job_rate(T, world, e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": T * H * 2,
+                "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_ms},
+        "gpu_launches_per_step": int(launches // max(1, steps)), "clocks": clocks,
+    }
+
+
+def contract_line(res, args, world, mode_label):
+    """A secondary result dressed as a full benchmark line (for `--workload decode|prefill`)."""
+    line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": res["steps"],
+            "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": mode_label, "data": "synthetic",
+            "config": {"workload": res["workload"], "projection_mix": res["projection_mix"],
+                       "l2": "weights of 28 layers (0.76 GB) and the KV pages / activations of a step > 126 MB L2",
+                       "parallelism": f"dp{world} replicas, no collective"},
+            "e2e": res["e2e"], "gpu_launches": res["gpu_launches_per_step"] * res["steps"], "clocks": res["clocks"]}
+    for k in ("roofline", "tflops", "repeats", "timed_region_s"):
+        if k in res:
+            line[k] = res[k]
+    return line
+
+
+def run_secondary_only(args, rank, local_rank, world):
+    import torch
+
+    from glm_asr_stack_b200 import workloads
+    torch.cuda.set_device(local_rank)
+    dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
+    mix = args.mix if args.mode == "w4a4" else "w4a16"
+    model = workloads.build_decoder(layers=args.layers)
+    if args.workload == "decode":
+        state = workloads.build_decode_state(model.cfg, num_seqs=args.seqs)
+        res = measure_decode(model, state, mix, args.steps, args.warmup, dist, local_rank, world,
+                             min_seconds=0.0 if args.burst_only else 1.0)
+    else:
+        st = workloads.build_prefill_state(model.cfg, num_seqs=max(1, args.rows // 400), seq_len=400)
+        res = measure_prefill(model, st, mix, args.steps, args.warmup, dist, local_rank, world)
     if rank == 0:
-        print(json.dumps({
-            "metric": "prefill_tok_per_s", "value": replicas.whole_job_rate(T, world, ms * 1e-3), "unit": "tok/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
-            "config": {"workload": f"batched prefill, {cfg.dec_layers} layers, {nseq} sequences x 400 tokens = {T} tokens, "
-                                   "paged bf16 KV (16-token pages)",
-                       "l2": "weights of 28 layers (0.76 GB) and 41 MB of activations per layer > 126 MB L2"},
-            "tflops": replicas.whole_job_rate(flops, world, ms * 1e-3) / 1e12,
-            "e2e": {"value": replicas.whole_job_rate(T, world, e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": T * H * 2,
-                    "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_ms},
-            "gpu_launches": int(launches), "clocks": clocks,
-        }), flush=True)
+        print(json.dumps(contract_line(res, args, world, args.mode)), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -358,8 +511,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="w4a4", choices=["w4a4", "w4a16"])
+    ap.add_argument("--mix", default="all_w4a4", choices=["reference", "all_w4a4"],
+                    help="projection mix of the decoder drivers under --mode w4a4 (decode / prefill workloads)")
     ap.add_argument("--rows", type=int, default=M_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the decode / prefill measurements of the layer workload's line")
+    ap.add_argument("--no-yardstick", action="store_true", help="skip the library FP4 GEMM timing")
+    ap.add_argument("--burst-only", action="store_true", help="time exactly --steps steps once (profiler captures)")
     ap.add_argument("--workload", default="layer", choices=["layer", "decode", "prefill"],
                     help="layer = benchmark configuration 1 (default, the headline); decode = configuration 2; "
                          "prefill = the whole 28-layer batched prefill the config-1 projections belong to")
@@ -374,11 +532,8 @@ def main():
         run_reference(args, rank)
         return
 
-    if args.workload == "decode":
-        run_decode(args, rank, local_rank, world)
-        return
-    if args.workload == "prefill":
-        run_prefill(args, rank, local_rank, world)
+    if args.workload in ("decode", "prefill"):
+        run_secondary_only(args, rank, local_rank, world)
         return
 
     import torch
@@ -388,6 +543,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path")
     torch.cuda.set_device(local_rank)
+    numa_node = pin_to_gpu_numa_node(local_rank)
     dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
 
     mode = ops.MODE_W4A4 if args.mode == "w4a4" else ops.MODE_W4A16
@@ -431,24 +587,24 @@ def main():
     _st = ops.status()
     assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
 
-    # ---- device-resident timing -----------------------------------------------------------
-    sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    launches0 = ops.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    sampler.sample_now()          # the GPU is still working through the timed steps queued above
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    launches = ops.launch_count() - launches0
-    clocks = sampler.stop()
-    ms_total = replicas.max_over_ranks(ms_total, dist, "cuda")
-    ms_step = ms_total / args.steps
+    # ---- device-resident timing: one K-step block (burst), then K-step blocks back to back for >= 1 s ----
+    burst_ms, _, burst_region, burst_launches = timed_steps(step, args.steps, barrier, counter=ops.launch_count)
+    burst_ms = replicas.max_over_ranks(burst_ms, dist, "cuda")
+    if args.burst_only:
+        ms_step, repeats, region_s = burst_ms, 1, burst_region
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        sampler.sample_now()
+        clocks = sampler.stop()
+        launches = burst_launches
+    else:
+        sampler = ClockSampler(local_rank)
+        ms_step, repeats, region_s, launches = timed_steps(step, args.steps, barrier, sampler, min_seconds=1.0,
+                                                           counter=ops.launch_count)
+        clocks = sampler.stop()
+        ms_step = replicas.max_over_ranks(ms_step, dist, "cuda")
     value = replicas.whole_job_rate(layer_flops(M), world, ms_step * 1e-3) / 1e12
+    burst_value = replicas.whole_job_rate(layer_flops(M), world, burst_ms * 1e-3) / 1e12
 
     # ---- per-launch kernel timing for the roofline (separate pass, events around each GEMM) ----
     ops.profile_enable(True)
@@ -462,6 +618,12 @@ def main():
     top_ms = statistics.mean(ms for ms, _, _ in top)
     achieved = top_flops / (top_ms * 1e-3) / 1e12
     all_ms = sum(ms for ms, _, _ in prof) / max(1, min(args.steps, 8))
+    by_flops = {}
+    for ms, f, _ in prof:
+        by_flops.setdefault(f, []).append(ms)
+    shape_names = {2.0 * M * (HIDDEN + 2 * KV) * HIDDEN: "qkv", 2.0 * M * HIDDEN * HIDDEN: "o",
+                   2.0 * M * 2 * FFN * HIDDEN: "gate_up", 2.0 * M * HIDDEN * FFN: "down"}
+    ours_ms = {shape_names.get(f, str(f)): statistics.mean(v) for f, v in by_flops.items()}
     peaks = measured_peaks()
     if args.mode == "w4a4":
         peak, peak_src = NOMINAL_FP4_TFLOPS, "nominal dense FP4 9 PFLOP/s (MEASURED_PEAKS.json holds no FP4 figure)"
@@ -477,54 +639,71 @@ def main():
              else "umma_gemm_kernel (gate|up, SiLU-gate epilogue)")
     roofline = {"bound": "tensor", "kernel": kname, "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
-                "traffic": traffic, "launch_ms": top_ms, "gemm_ms_per_step": all_ms,
+                "traffic": traffic, "launch_ms": top_ms, "gemm_ms_per_step": all_ms, "launch_ms_by_shape": ours_ms,
                 "achieved_gbs": top[0][2] / (top_ms * 1e-3) / 1e9,
-                "frac_of_measured_bf16": (achieved / peaks["bf16_tflops"]) if peaks else None}
+                "frac_of_measured_bf16": (achieved / peaks["bf16_tflops"]) if peaks else None,
+                "how": "CUDA events around every GEMM launch of 8 steps run right after the timed region"}
 
-    # ---- what the tensor pipe delivers to this kernel when nothing else is in the way ----------------
-    # MEASURED_PEAKS.json has no FP4 figure, so measure one here: the dominant GEMM (same kernel, same
-    # shape) with its operands left resident in shared memory after the first round of the ring and its
-    # stores switched off, i.e. the k-loop at the rate of the MMA issue and the tensor pipe alone.
-    mma_loop_tflops = None
-    if args.mode == "w4a4":
-        import ctypes
-        from glm_asr_stack_b200 import _lib
-        lib = _lib.load()
-        w0 = keep[0]
-        lib.glmasr_debug_set_flags(ctypes.c_int(4 | 8))
-        try:
-            for _ in range(3):
-                ops.fp4_linear_fused(mode, xs[0], [w0["gate"], w0["up"]], epilogue=ops.EPI_SILU_GATE, input_scale=isc_h)
-            ops.profile_enable(True)
-            for _ in range(5):
-                ops.fp4_linear_fused(mode, xs[0], [w0["gate"], w0["up"]], epilogue=ops.EPI_SILU_GATE, input_scale=isc_h)
-            pk = [ms for ms, f, _ in ops.profile_read() if f == top_flops]
-            ops.profile_enable(False)
-            if pk:
-                mma_loop_tflops = top_flops / (statistics.median(pk) * 1e-3) / 1e12
-        finally:
-            lib.glmasr_debug_set_flags(ctypes.c_int(-1))
-        torch.cuda.synchronize()
-        ops.status()
-        roofline["mma_loop_tflops"] = mma_loop_tflops
-        roofline["frac_of_mma_loop"] = (achieved / mma_loop_tflops) if mma_loop_tflops else None
-        roofline["mma_loop_how"] = ("same kernel and shape with operands resident in shared memory (no loads after the "
-                                    "first ring round) and stores off: the rate of MMA issue + tensor pipe alone")
+    # ---- the yardstick: the library's FP4 GEMM alone, on 8192^3 and on this workload's four shapes ----
+    if args.mode == "w4a4" and not args.no_yardstick:
+        if rank == 0:
+            yard, why = library_fp4_yardstick({"qkv": (M, HIDDEN + 2 * KV, HIDDEN), "o": (M, HIDDEN, HIDDEN),
+                                               "gate_up": (M, 2 * FFN, HIDDEN), "down": (M, HIDDEN, FFN),
+                                               "decode_qkv": (256, HIDDEN + 2 * KV, HIDDEN), "decode_o": (256, HIDDEN, HIDDEN),
+                                               "decode_gate_up": (256, 2 * FFN, HIDDEN), "decode_down": (256, HIDDEN, FFN),
+                                               "decode_lm_head": (256, 59264, HIDDEN)})
+            if yard is not None:
+                roofline["fp4_measured_tflops"] = yard["peak_tflops"]
+                roofline["fp4_measured_source"] = (f"cuBLASLt block-scaled FP4 GEMM (e2m1 x e2m1, ue4m3 per 16, bf16 out) at "
+                                                   f"{yard['peak_shape']} on this GPU, best of the heuristic's algorithms, "
+                                                   "20 back-to-back calls (burst)")
+                roofline["frac_of_fp4_measured"] = achieved / yard["peak_tflops"]
+                roofline["library_gemm"] = yard["shapes"]
+            else:
+                roofline["fp4_measured_tflops"] = None
+                roofline["fp4_measured_source"] = why
+        barrier()
 
     # ---- end to end: host buffers in, host buffers out, through the C-ABI host entry point ----
     for i in range(2):
         ops.layer_proj_host(mode, hin[i % 2], hout, layers[i % n_sets])
+    e2e_steps = args.steps * (1 if args.burst_only else max(1, int(0.3 / (args.steps * 1.2e-3)) + 1))
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(e2e_steps):
         ops.layer_proj_host(mode, hin[i % 2], hout, layers[i % n_sets])
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_s = replicas.max_over_ranks(e2e_s, dist, "cuda")
-    e2e_val = replicas.whole_job_rate(layer_flops(M), world, e2e_s / args.steps) / 1e12
+    e2e_val = replicas.whole_job_rate(layer_flops(M), world, e2e_s / e2e_steps) / 1e12
     bytes_io = M * HIDDEN * 2
     _st = ops.status()
     assert _st == 0, f"device status word = {_st} (bounded wait expired or CUDA error)"
+    floors = pcie_floors(bytes_io, dist, torch.device("cuda", local_rank))
+
+    # ---- secondary: benchmark configuration 2 (decode) and the whole batched prefill, both projection mixes ----
+    secondary = None
+    if not args.no_secondary and args.mode == "w4a4":
+        from glm_asr_stack_b200 import workloads
+        del xs, out, layers, keep
+        ops.cleanup()
+        torch.cuda.empty_cache()
+        secondary = {}
+        model = workloads.build_decoder(layers=args.layers)
+        state = workloads.build_decode_state(model.cfg, num_seqs=args.seqs)
+        for mix in ("all_w4a4", "reference"):
+            secondary["decode" if mix == "all_w4a4" else "decode_reference_mix"] = measure_decode(
+                model, state, mix, args.steps, 3, dist, local_rank, world, min_seconds=0.0 if args.burst_only else 1.0)
+        del state
+        torch.cuda.empty_cache()
+        st = workloads.build_prefill_state(model.cfg, num_seqs=max(1, M // 400), seq_len=400)
+        for mix in ("all_w4a4", "reference"):
+            secondary["prefill" if mix == "all_w4a4" else "prefill_reference_mix"] = measure_prefill(
+                model, st, mix, max(3, args.steps // 4), 3, dist, local_rank, world)
+        secondary["note"] = ("decode / prefill: every projection block-scaled FP4 (W4A4), the arithmetic the path is built "
+                             "for (GLMASR_USE_CUTLASS_NVFP4=1 GLMASR_NVFP4_PAIRS=1); *_reference_mix: what the reference "
+                             "computes under GLMASR_USE_CUTLASS_NVFP4=1 and this library's drivers do by default -- q, o, down "
+                             "W4A4, the same-input pairs k|v and gate|up as fused W4A16 GEMMs")
 
     if rank == 0:
         line = {
@@ -537,14 +716,23 @@ def main():
             "config": {"workload": WORKLOAD, "rows": M, "arith": args.mode,
                        "l2": "4 weight sets + 2 inputs used round-robin; ~330 MB touched per step > 126 MB L2",
                        "parallelism": f"dp{world} replicas, no collective"},
+            "repeats": repeats, "timed_region_s": region_s,
+            "timing": f"{args.steps}-step blocks repeated {repeats}x back to back inside one CUDA-event pair (sustained)",
+            "burst": {"value": burst_value, "ms_per_step": burst_ms, "timed_region_s": burst_region,
+                      "how": f"one {args.steps}-step block"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io,
-                    "ms_per_step": e2e_s / args.steps * 1e3},
+                    "ms_per_step": e2e_s / e2e_steps * 1e3, "steps": e2e_steps,
+                    "pcie_floor_ms": floors, "staging_numa_node": numa_node,
+                    "pcie_floor_how": "this step's bytes host->device alone / device->host alone / both at once, pinned "
+                                      "buffers, best of 5, every rank copying at the same time, max over ranks"},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         }
+        if secondary is not None:
+            line["secondary"] = secondary
         if not args.no_cpu_baseline and world == 1:
-            tf, sec, threads = cpu_reference_leg(2, 1, 512)
+            tf, sec, threads = cpu_reference_leg(3, 1, M)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": f"512 of {M_TOKENS} rows, all four projections, full weights, "
+                                    "sample": f"all {M} rows, all four projections, full weights, 3 steps after 1 warm-up, "
                                               f"dequantise-every-call + fp32 GEMM in torch CPU ({sec:.2f} s/step)"}
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -49,6 +49,10 @@ SIGNATURES = {
     "decoder_prefill_paged_batched": (None, [P, P, P, c_int, c_int, P, P, P, P, P, P]),
     "flash_fwd_vllm_gqa_available": (c_int, []),
     "flash_fwd_vllm_gqa_launch": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, c_int]),
+    "safetensors_load": (c_int, [ctypes.c_char_p, P]),
+    "safetensors_free": (None, [P]),
+    "glmasr_safetensors_inspect": (c_int, [ctypes.c_char_p, P, POINTER(ctypes.c_size_t)]),
+    "glmasr_safetensors_release_index": (None, [P]),
     "glmasr_rope_single_token": (None, [P, P, c_int, c_int, c_int]),
     "glmasr_rope_qk_cache": (c_int, [P, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int]),
     "glmasr_rmsnorm_quant": (c_int, [P, P, P, P, c_float, c_float, c_int, c_int]),

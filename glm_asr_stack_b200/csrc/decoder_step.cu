@@ -60,6 +60,8 @@ struct ModelRefs {
 };
 
 static ModelRefs g_refs;
+// cached environment switches (-1 = not read yet), see prefer_w4a4() / pairs_w4a4()
+static int g_native_switch = -1, g_pairs_switch = -1;
 
 static const glmasr_Tensor *find_tensor(const glmasr_WeightStore *ws, const char *name) {
     for (int i = 0; i < ws->count; ++i)
@@ -148,16 +150,21 @@ static const ModelRefs &model_refs(const glmasr_WeightStore *ws, int num_layers)
     return g_refs;
 }
 
-void forget_model_refs() { g_refs = ModelRefs(); }
+void forget_model_refs() {
+    g_refs = ModelRefs();
+    g_native_switch = g_pairs_switch = -1;
+}
 
+// The two arithmetic switches are read from the environment on first use and kept (the reference reads its
+// switch once per process); glmasr_decoder_forget_weights() drops them together with the pointer table, so a
+// host that changes the environment between two models gets the new values.
 static bool prefer_w4a4() {
     // reference: prefer_nvfp4_cutlass, Infer-engine/cuda/decoder.cu:142-151
-    static int state = -1;
-    if (state < 0) {
+    if (g_native_switch < 0) {
         const char *e = getenv("GLMASR_USE_CUTLASS_NVFP4");
-        state = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
+        g_native_switch = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
     }
-    return state == 1;
+    return g_native_switch == 1;
 }
 
 // Which arithmetic the same-input PAIRS (k|v, gate|up) use when GLMASR_USE_CUTLASS_NVFP4 selects the native
@@ -168,12 +175,11 @@ static bool prefer_w4a4() {
 // here.  GLMASR_NVFP4_PAIRS=1 opts in to running the pairs in W4A4 as well (q|k|v and gate|up each one
 // block-scaled FP4 GEMM on a shared quantised input): faster, but not the reference's arithmetic.
 static bool pairs_w4a4() {
-    static int state = -1;
-    if (state < 0) {
+    if (g_pairs_switch < 0) {
         const char *e = getenv("GLMASR_NVFP4_PAIRS");
-        state = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
+        g_pairs_switch = (e && e[0] && strcmp(e, "0") != 0) ? 1 : 0;
     }
-    return state == 1 && prefer_w4a4();
+    return g_pairs_switch == 1 && prefer_w4a4();
 }
 
 static glmasr_fp4_weight as_weight(const ProjRef &p) {
@@ -191,13 +197,14 @@ static void single_proj(uint16_t *out, int ldo, const uint16_t *x, int ldx, cons
                         const uint16_t *residual, uint16_t *scratch) {
     if (p.dtype == GLMASR_DTYPE_BF16) {
         // bf16_linear keeps the reference's dense signature: go through the scratch buffer when the
-        // destination is a column slice of a wider buffer
+        // destination is a column slice of a wider buffer, or when it is also the residual (the drivers
+        // update the hidden state in place, and the GEMM must not overwrite what is still to be added)
         GLMASR_CHECK(ldx == p.K, "bf16 projection needs a dense input");
-        uint16_t *dst = ldo == p.N ? out : scratch;
+        uint16_t *dst = (ldo == p.N && out != residual) ? out : scratch;
         bf16_linear(nullptr, dst, x, (const uint16_t *)p.w, nullptr, M, p.N, p.K);
         if (residual) {
             GLMASR_CHECK(ldo == p.N, "bf16 projection with residual needs a dense output");
-            residual_add(out, out, residual, M * p.N);
+            residual_add(out, dst, residual, M * p.N);
         } else if (dst != out) {
             GLMASR_CUDA_CHECK(cudaMemcpy2DAsync(out, (size_t)ldo * 2, dst, (size_t)p.N * 2, (size_t)p.N * 2, M,
                                                 cudaMemcpyDeviceToDevice, current_stream()));

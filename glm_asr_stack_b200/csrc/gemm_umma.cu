@@ -493,13 +493,19 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                     }
                 }
             } else {
-                // plain / bias / residual: this warp's columns [half*HC, +HC) of the tile
-                const int sub = (half * HC) / 128;            // weight sub-tile the columns belong to
-                const int sub_c0 = (half * HC) % 128;         // first column inside that sub-tile
-                const SubTile st = resolve_subtile(p, n_tile, sub, NB);
-                const float alpha = p.alpha[st.seg];
+                // plain / bias / residual: this warp's columns [half*HC, +HC) of the tile.  They lie in one weight
+                // sub-tile when there are two epilogue warps per lane quadrant, and span both sub-tiles of a
+                // 256-column tile when there is one (the W4A16 variant): the sub-tile is resolved per 32-column chunk.
+                SubTile st = resolve_subtile(p, n_tile, (half * HC) / 128, NB);
+                int st_sub = (half * HC) / 128;
                 auto finish_chunk = [&](const uint32_t (&r)[32], int ch) {
-                    const int c0 = sub_c0 + ch * 32;
+                    const int tile_col = half * HC + ch * 32;
+                    if (tile_col / 128 != st_sub) {
+                        st_sub = tile_col / 128;
+                        st = resolve_subtile(p, n_tile, st_sub, NB);
+                    }
+                    const float alpha = p.alpha[st.seg];
+                    const int c0 = tile_col % 128;
                     const int nvalid = st.ncols - c0;
                     if (!(row_ok && nvalid > 0)) return;
                     const int col = st.col0 + c0;

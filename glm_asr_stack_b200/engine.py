@@ -7,6 +7,7 @@ include/glmasr_engine_types.h).  Used by the tests and the benchmark to call
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_int, c_int64, c_size_t, c_void_p
 from typing import Dict, List, Optional
 
@@ -97,6 +98,56 @@ class WeightStore:
         self.add(f"{prefix}.weight_scale_2", torch.tensor([w.w_global_scale], dtype=torch.float32, device=dev))
         if input_scale is not None:
             self.add(f"{prefix}.input_scale", torch.tensor([input_scale], dtype=torch.float32, device=dev))
+
+
+class LoadedWeightStore:
+    """A C ``WeightStore`` filled by ``safetensors_load`` (Infer-engine/src/safetensors.c:57-181): the library owns
+    the device memory (one allocation per file) until ``close()`` calls ``safetensors_free``."""
+
+    def __init__(self, path: str):
+        self.c = CWeightStore()
+        self.c.count = 0
+        rc = _lib.load().safetensors_load(os.fsencode(path), ctypes.byref(self.c))
+        if rc != 0:
+            raise OSError(f"safetensors_load({path!r}) failed")
+        self._open = True
+
+    def names(self) -> List[str]:
+        return [self.c.names[i].decode() for i in range(self.c.count)]
+
+    def entry(self, i: int):
+        t = self.c.tensors[i]
+        return {"name": self.c.names[i].decode(), "dtype": t.dtype, "shape": [int(t.shape[d]) for d in range(t.ndim)],
+                "nbytes": int(t.nbytes), "data": int(t.data or 0)}
+
+    def close(self):
+        if self._open:
+            _lib.load().safetensors_free(ctypes.byref(self.c))
+            self._open = False
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def inspect_safetensors(path: str):
+    """glmasr_safetensors_inspect: the header pass alone (no CUDA).  Returns (entries, arena_bytes); an entry's
+    ``data`` is its offset inside the one device allocation a load would make."""
+    lib = _lib.load()
+    c = CWeightStore()
+    c.count = 0
+    arena = c_size_t(0)
+    if lib.glmasr_safetensors_inspect(os.fsencode(path), ctypes.byref(c), ctypes.byref(arena)) != 0:
+        raise OSError(f"glmasr_safetensors_inspect({path!r}) failed")
+    out = []
+    for i in range(c.count):
+        t = c.tensors[i]
+        out.append({"name": c.names[i].decode(), "dtype": t.dtype, "shape": [int(t.shape[d]) for d in range(t.ndim)],
+                    "nbytes": int(t.nbytes), "data": int(t.data or 0)})
+    lib.glmasr_safetensors_release_index(ctypes.byref(c))
+    return out, int(arena.value)
 
 
 def model_config(hidden=2048, layers=28, heads=16, kv_heads=4, head_dim=128, ffn=6144, vocab=59264) -> CModelConfig:

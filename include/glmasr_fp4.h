@@ -113,12 +113,36 @@ void paged_decode_attention(uint16_t *out, const uint16_t *query, const uint16_t
 
 /* Infer-engine/include/cuda_kernels.h:164-170, Infer-engine/cuda/decoder.cu:1849-2173.
  * ws: WeightStore*, cfg: ModelConfig*, pool: KVPool*, bts: BlockTable[num_seqs]; handle and
- * dequant_buf are ignored.  GLMASR_USE_CUTLASS_NVFP4 selects W4A4 as in the reference. */
+ * dequant_buf are ignored.  Arithmetic per projection as in the reference: without
+ * GLMASR_USE_CUTLASS_NVFP4 every FP4 projection is W4A16 (fp4_linear); with it q, o and down are W4A4
+ * (nvfp4_linear) while the same-input pairs k|v and gate|up stay W4A16 (the reference's fused pair,
+ * Infer-engine/cuda/decoder.cu:923-978, always dequantises), unless a pair carries a pre_quant_scale and is
+ * therefore run one projection at a time.  GLMASR_NVFP4_PAIRS=1 (additive, not in the reference) runs the
+ * pairs in W4A4 too. */
 void decoder_decode_step_batched(void *handle, const void *ws, uint16_t **query_ptrs, void *pool, void *bts,
                                  int *d_seq_lens, int *h_seq_lens, int num_seqs, int *seq_indices,
                                  uint16_t *dequant_buf, const void *cfg);
 
+/* Infer-engine/include/safetensors.h:6-7, Infer-engine/src/safetensors.c:57-193.  ws: WeightStore*.
+ * safetensors_load fills the store with every tensor of the file whose dtype the engine knows (BF16, F32,
+ * F16, U8, F8_E4M3), in header order: name, dtype tag, shape (<= 4 dims), byte count, device pointer; at most
+ * 2048 entries; "__metadata__" and other dtypes are skipped.  Returns 0, or -1 (message on stderr) when the
+ * file cannot be read or device memory runs out.  Unlike the reference, which allocates every tensor on its
+ * own, the tensors of one file live at 256-byte aligned offsets of ONE device allocation, filled through two
+ * pinned staging buffers in 64 MiB copies; so a store filled here must be released with this library's
+ * safetensors_free (which also accepts stores whose tensors were allocated one by one), and single tensors
+ * must not be passed to cudaFree. */
+int safetensors_load(const char *path, void *ws);
+void safetensors_free(void *ws);
+
 /* ======================= 2. additive entry points ======================= */
+
+/* The header pass of safetensors_load on its own: names, dtype tags, shapes and byte counts exactly as the load
+ * would set them, with every tensor's OFFSET inside the one device allocation stored in `data`, and that
+ * allocation's size in *arena_bytes.  No device memory is touched and no CUDA call is made.  The names are
+ * malloc'd; release them with glmasr_safetensors_release_index.  Returns 0 or -1. */
+int glmasr_safetensors_inspect(const char *path, void *ws, size_t *arena_bytes);
+void glmasr_safetensors_release_index(void *ws);
 
 /* Batched variable-length prefill, in place on hidden [total_tokens, dec_hidden]
  * (Infer-engine/cuda/decoder.cu:1219-1557; include/cuda_kernels.h): sequence s owns rows
@@ -157,7 +181,8 @@ int glmasr_rope_qk_cache(uint16_t *qkv, int ld, int k_col, int v_col, const int 
  * glmasr_quantize_bf16_to_fp4 + glmasr_swizzle_rowwise_scales.  dim % 64 == 0.  Returns -1 otherwise. */
 int glmasr_rmsnorm_quant(uint8_t *packed_out, uint8_t *tiled_scale_out, const uint16_t *x, const uint16_t *weight,
                          float eps, float input_scale, int rows, int dim);
-/* Forget the per-layer pointer table built from a WeightStore (call before freeing the store). */
+/* Forget the per-layer pointer table built from a WeightStore (call before freeing the store).  Also drops
+ * the cached values of GLMASR_USE_CUTLASS_NVFP4 and GLMASR_NVFP4_PAIRS: they are read again on next use. */
 void glmasr_decoder_forget_weights(void);
 
 #define GLMASR_MODE_W4A4  0   /* nvfp4_linear arithmetic */

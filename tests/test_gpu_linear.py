@@ -469,3 +469,26 @@ def test_config1_layer_row_sample_vs_oracle_chain(ops, mode_name):
     err = o.rel_err(bits_of(got[rows]), want)
     assert err <= REL_TOL_VS_ORACLE, err
     assert o.cosine(bits_of(got[rows]), want) >= 0.999
+
+
+def test_w4a16_two_subtile_tiles_store_every_column(ops):
+    """W4A16 below 1024 rows dequantises inside the GEMM; with enough tiles (here 7 row tiles x 24 column tiles)
+    a CTA tile spans two 128-row weight sub-tiles and its four epilogue warps own 256 columns each.  Every output
+    column must be written (the output starts as NaN) and agree with the fp32 oracle on a row sample."""
+    from glm_asr_stack_b200 import synth
+    M, N, K = 896, 6144, 2048
+    w = synth.seeded_weight_fast(N, K, 77)
+    x = synth.seeded_activation(M, K, 78)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.fp4_linear(x, w.w_packed, w.w_scales, w.w_global_scale, out=out)
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    assert not torch.isnan(out).any()
+    rows = [0, 127, 128, 500, 895]
+    want = o.linear_o1(bits_of(x[rows]), w.w_packed.cpu().numpy(), w.w_scales.cpu().numpy(), w.w_global_scale)
+    assert o.rel_err(bits_of(out[rows]), want) <= REL_TOL_TIGHT
+    # residual epilogue over the same tiles
+    res = synth.seeded_activation(M, N, 79)
+    fused = ops.fp4_linear_fused(ops.MODE_W4A16, x, [w], epilogue=ops.EPI_RESIDUAL, residual=res)
+    assert not torch.isnan(fused).any()
+    assert o.rel_err(bits_of(fused[rows]), o.residual_add(want, bits_of(res[rows]))) <= REL_TOL_TIGHT
