@@ -49,6 +49,9 @@ SIGNATURES = {
     "decoder_prefill_paged_batched": (None, [P, P, P, c_int, c_int, P, P, P, P, P, P]),
     "flash_fwd_vllm_gqa_available": (c_int, []),
     "flash_fwd_vllm_gqa_launch": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, c_int]),
+    "mel_spectrogram": (None, [P, c_int, P, P, P]),
+    "mel_cleanup": (None, []),
+    "glmasr_mel_spectrogram_batched": (c_int, [P, c_longlong, P, c_int, P, P, c_longlong, c_int, P]),
     "safetensors_load": (c_int, [ctypes.c_char_p, P]),
     "safetensors_free": (None, [P]),
     "glmasr_safetensors_inspect": (c_int, [ctypes.c_char_p, P, POINTER(ctypes.c_size_t)]),

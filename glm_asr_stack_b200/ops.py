@@ -365,6 +365,39 @@ def layer_proj_host(mode: int, hidden_in_host: torch.Tensor, hidden_out_host: to
     return hidden_out_host
 
 
+def mel_spectrogram(pcm: torch.Tensor, mel_filters_t: torch.Tensor) -> torch.Tensor:
+    """reference: mel_spectrogram, Infer-engine/cuda/mel.cu:253-294.  pcm float32 [num_samples] and the
+    transposed filterbank float32 [201, 128] on the device -> bf16 [128, n_frames]."""
+    lib = _lib.load()
+    _check(pcm, torch.float32, "pcm")
+    _check(mel_filters_t, torch.float32, "mel_filters_t")
+    ns = pcm.numel()
+    n = min(max((ns + 159) // 160, 1), 3000)
+    out = torch.empty((128, n), dtype=torch.bfloat16, device=pcm.device)
+    frames = ctypes.c_int(0)
+    lib.mel_spectrogram(_ptr(pcm), ns, _ptr(mel_filters_t), _ptr(out), ctypes.byref(frames))
+    assert frames.value == n
+    return out
+
+
+def mel_spectrogram_batched(pcm: torch.Tensor, num_samples: Sequence[int], mel_filters_t: torch.Tensor,
+                            time_major: bool = False, out: Optional[torch.Tensor] = None):
+    """glmasr_mel_spectrogram_batched: pcm float32 [windows, stride]; returns (bf16 [windows, 128 * 3000] buffer whose
+    window i holds [128, n_i] or [n_i, 128] at its start, list of n_i)."""
+    lib = _lib.load()
+    _check(pcm, torch.float32, "pcm")
+    w = pcm.shape[0]
+    if out is None:
+        out = torch.zeros((w, 128 * 3000), dtype=torch.bfloat16, device=pcm.device)
+    ns = (ctypes.c_int * w)(*[int(v) for v in num_samples])
+    frames = (ctypes.c_int * w)()
+    rc = lib.glmasr_mel_spectrogram_batched(_ptr(pcm), pcm.stride(0), ns, w, _ptr(mel_filters_t), _ptr(out), out.stride(0),
+                                            1 if time_major else 0, frames)
+    if rc != 0:
+        raise ValueError("glmasr_mel_spectrogram_batched rejected the arguments")
+    return out, list(frames)
+
+
 def status() -> int:
     """Synchronise; return and clear the first device-side status code (0 = ok)."""
     return _lib.load().glmasr_fp4_status()

@@ -135,7 +135,27 @@ void decoder_decode_step_batched(void *handle, const void *ws, uint16_t **query_
 int safetensors_load(const char *path, void *ws);
 void safetensors_free(void *ws);
 
+/* Infer-engine/include/cuda_kernels.h:12-14, Infer-engine/cuda/mel.cu:253-294.  Log-mel features of one 16 kHz
+ * window: pcm float [num_samples] and mel_filters_transposed float [201, 128] on the device; mel_out bf16
+ * [128, n_frames] (mel-major) with n_frames = clamp(ceil(num_samples / 160), 1, 3000) returned in *out_frames
+ * (host).  Periodic Hann window, 400-point DFT, power, filterbank, log10(p + 1e-10), clamp to (maximum - 8),
+ * (v + 4) / 4.  The maximum is taken over the WHOLE window; the reference's second reduction pass
+ * (mel.cu:195-206) lets only one warp's share through, which is treated as a defect and not reproduced. */
+void mel_spectrogram(const float *pcm, int num_samples, const float *mel_filters_transposed, uint16_t *mel_out,
+                     int *out_frames);
+/* Infer-engine/cuda/mel.cu:86-109.  Nothing to release here beyond what glmasr_fp4_cleanup frees. */
+void mel_cleanup(void);
+
 /* ======================= 2. additive entry points ======================= */
+
+/* mel_spectrogram for a batch of windows in two launches: window i reads pcm + i * pcm_stride (floats,
+ * num_samples_host[i] of them) and writes mel_out + i * out_stride (bf16 elements) as [128, n_frames_i]
+ * (time_major = 0, the reference's layout) or [n_frames_i, 128] (time_major = 1, rows = frames: what the
+ * encoder's convolution-as-GEMM reads); out_frames_host[i] = n_frames_i (may be NULL).  num_windows <= 4096.
+ * Returns 0 or -1. */
+int glmasr_mel_spectrogram_batched(const float *pcm, long long pcm_stride, const int *num_samples_host, int num_windows,
+                                   const float *mel_filters_transposed, uint16_t *mel_out, long long out_stride,
+                                   int time_major, int *out_frames_host);
 
 /* The header pass of safetensors_load on its own: names, dtype tags, shapes and byte counts exactly as the load
  * would set them, with every tensor's OFFSET inside the one device allocation stored in `data`, and that

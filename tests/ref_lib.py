@@ -38,6 +38,9 @@ class RefLib:
         L.reshape_and_cache.restype = None
         L.paged_decode_attention.argtypes = [P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]
         L.paged_decode_attention.restype = None
+        if hasattr(L, "mel_spectrogram"):
+            L.mel_spectrogram.argtypes = [P, c_int, P, P, P]
+            L.mel_spectrogram.restype = None
         # the reference's fp4_linear / bf16_linear take a cublasHandle_t
         self.cublas = ctypes.CDLL("libcublas.so.12")
         self.handle = c_void_p()
@@ -78,6 +81,17 @@ class RefLib:
                                    self._p(scales), input_scale, g, self._p(pre), None, M, N, K)
         torch.cuda.synchronize()
         return rc, out
+
+    def mel_spectrogram(self, pcm, filters_t):
+        """Infer-engine/cuda/mel.cu:253-294 -> bf16 [128, n_frames]."""
+        ns = pcm.numel()
+        n = min(max((ns + 159) // 160, 1), 3000)
+        out = torch.empty((128, n), dtype=torch.bfloat16, device="cuda")
+        frames = ctypes.c_int(0)
+        self.lib.mel_spectrogram(self._p(pcm), ns, self._p(filters_t), self._p(out), ctypes.byref(frames))
+        torch.cuda.synchronize()
+        assert frames.value == n
+        return out
 
     def rmsnorm(self, x, w, eps=1e-5):
         out = torch.empty_like(x)
