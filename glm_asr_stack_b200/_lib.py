@@ -49,6 +49,18 @@ SIGNATURES = {
     "decoder_prefill_paged_batched": (None, [P, P, P, c_int, c_int, P, P, P, P, P, P]),
     "flash_fwd_vllm_gqa_available": (c_int, []),
     "flash_fwd_vllm_gqa_launch": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, c_int]),
+    "layernorm": (None, [P, P, P, P, c_float, c_int, c_int]),
+    "gelu_inplace": (None, [P, c_int]),
+    "rope_encoder": (None, [P, P, c_int, c_int, c_int, c_float]),
+    "residual_add_bias": (None, [P, P, P, P, c_int, c_int]),
+    "concat_4frames": (None, [P, P, c_int, c_int]),
+    "conv1d_forward": (None, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "transpose_2d": (None, [P, P, c_int, c_int]),
+    "bf16_linear_gelu": (None, [P, P, P, P, P, c_int, c_int, c_int]),
+    "encoder_forward": (None, [P, P, P, c_int, P]),
+    "encoder_forward_packed": (None, [P, P, P, c_int, c_int, P, P, P]),
+    "encoder_cleanup": (None, []),
+    "glmasr_audio_encode_batched": (c_int, [P, P, P, c_longlong, P, c_int, P, c_longlong, P]),
     "mel_spectrogram": (None, [P, c_int, P, P, P]),
     "mel_cleanup": (None, []),
     "glmasr_mel_spectrogram_batched": (c_int, [P, c_longlong, P, c_int, P, P, c_longlong, c_int, P]),

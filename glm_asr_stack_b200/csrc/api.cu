@@ -50,7 +50,7 @@ struct TimedLaunch {
 };
 static std::vector<TimedLaunch> g_timed;
 
-static constexpr int kSlots = 40;   // 0..12, 24..25, 30..31 used here, 13..23 and 26..29 by the decode step (decoder_step.cu),
+static constexpr int kSlots = 56;   // (35..37: mel.cu, 38..47: encoder.cu) 0..12, 24..25, 30..31 used here, 13..23 and 26..29 by the decode step (decoder_step.cu),
                                     // 32..33 by the prefill attention (prefill_attention_umma.cu)
 static void *g_ws[kSlots] = {nullptr};
 static size_t g_ws_bytes[kSlots] = {0};
@@ -108,6 +108,7 @@ static void clear_tmap_cache();
 
 void free_all_private_state() {
     cudaDeviceSynchronize();
+    encoder_forget_all();          // its tables live in workspace slots
     for (int i = 0; i < kSlots; ++i) {
         if (g_ws[i]) cudaFree(g_ws[i]);
         g_ws[i] = nullptr;
@@ -372,7 +373,8 @@ static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 static bool tensor_core_eligible(const FusedArgs &a) {
     if (force_simt()) return false;
-    if (a.K % 256 != 0) return false;
+    // operand tiles are 128 bytes of K per step: 256 e2m1 elements, 64 bf16; W4A16 stages raw weights 256 at a time
+    if (a.K % (a.mode == GEMM_BF16 ? 64 : 256) != 0) return false;
     if (!aligned16(a.x) || !aligned16(a.out) || (a.ldx % 8) != 0) return false;
     if (a.mode == GEMM_BF16) {
         for (int i = 0; i < a.num_w; ++i)
@@ -797,6 +799,39 @@ int fp4_linear_w4a16_silu_quantized(uint8_t *q_out, uint8_t *q_out_sf, float q_o
     return run_fused(a);
 }
 
+// bf16 GEMM with the epilogues of the audio encoder: out[M, sum N_i] = epilogue(x[M, K] * concat_i(w_i[N_i, K])^T)
+// for up to three weight tensors that share the input (q | k | v without copying them together), bias indexed by
+// output column.  epi: EPI_STORE (+ bias), EPI_GELU (bias, tanh-GELU), EPI_RESIDUAL (bf16(bf16(acc) + bias) + residual,
+// residual row pitch ldo).  x row pitch ldx, out row pitch ldo.  Returns 0, or -1 when the shape cannot run on
+// the tensor-core path (K % 64, 16-byte alignment).
+int bf16_linear_ex(uint16_t *out, int ldo, const uint16_t *x, int ldx, const uint16_t *const *w, const int *n, int num_w,
+                   const uint16_t *bias, int epi, const uint16_t *residual, int M, int K) {
+    if (out == nullptr || x == nullptr || w == nullptr || n == nullptr || num_w < 1 || num_w > kMaxSegments || M <= 0 || K <= 0)
+        return -1;
+    if (epi == EPI_RESIDUAL && residual == nullptr) return -1;
+    FusedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.mode = GEMM_BF16;
+    a.out = (__nv_bfloat16 *)out;
+    a.ldo = ldo;
+    a.x = (const __nv_bfloat16 *)x;
+    a.ldx = ldx;
+    for (int i = 0; i < num_w; ++i) {
+        if (w[i] == nullptr || n[i] <= 0) return -1;
+        a.w_bf16[i] = (const __nv_bfloat16 *)w[i];
+        a.n_bf16[i] = n[i];
+    }
+    a.num_w = num_w;
+    a.epi = epi;
+    a.bias = (const __nv_bfloat16 *)bias;
+    a.residual = (const __nv_bfloat16 *)residual;
+    a.M = M;
+    a.K = K;
+    if (ldo < total_out_cols(a) || ldx < K) return -1;
+    if (!tensor_core_eligible(a)) return -1;
+    return run_fused(a);
+}
+
 }  // namespace glmasr
 
 using namespace glmasr;
@@ -886,6 +921,18 @@ extern "C" void bf16_linear(void *handle, uint16_t *out, const uint16_t *x, cons
     a.M = M;
     a.K = K;
     GLMASR_CHECK(run_fused(a) == 0, "bf16_linear failed (M=%d N=%d K=%d)", M, N, K);
+    GLMASR_CUDA_CHECK(cudaGetLastError());
+}
+
+// Infer-engine/include/cuda_kernels.h:71-75, Infer-engine/cuda/kernels.cu:1211-1250: bf16 linear + bias + tanh-GELU.
+extern "C" void bf16_linear_gelu(void *handle, uint16_t *out, const uint16_t *x, const uint16_t *w, const uint16_t *bias,
+                                 int M, int N, int K) {
+    (void)handle;
+    if (M <= 0 || N <= 0 || K <= 0) return;
+    const uint16_t *ws[1] = {w};
+    const int ns[1] = {N};
+    GLMASR_CHECK(bf16_linear_ex(out, N, x, K, ws, ns, 1, bias, EPI_GELU, nullptr, M, K) == 0,
+                 "bf16_linear_gelu: unsupported shape or alignment (M=%d N=%d K=%d)", M, N, K);
     GLMASR_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -203,6 +203,14 @@ __device__ __forceinline__ Packed16 load_packed(const __nv_bfloat16 *src, int nv
     return load_packed_any(src, nvalid);
 }
 
+__device__ __forceinline__ float gelu_tanh(float v) {
+    // 0.5 v (1 + tanh(0.79788456 (v + 0.044715 v^3))) as in the reference (Infer-engine/cuda/kernels.cu:364-372,
+    // 844-856), with the hardware tanh (relative error ~2^-11, below the bf16 output's resolution)
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.79788456f * (v + 0.044715f * v * v * v)));
+    return 0.5f * v * (1.0f + t);
+}
+
 __device__ __forceinline__ float silu_gate(float g, float u) {
     // (g * sigmoid(g)) * u as in the reference SiLU-gate (Infer-engine/cuda/kernels.cu:1259-1263), with
     // the hardware exponential and reciprocal: the fused epilogue is compared with the reference

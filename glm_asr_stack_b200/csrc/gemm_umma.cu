@@ -512,17 +512,30 @@ __global__ void __launch_bounds__(Cfg<MODE, NB>::THREADS, 1) umma_gemm_kernel(co
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-                    if (p.bias != nullptr) {
-                        float b[32];
-                        load_row_chunk(p.bias + col, b, nvalid);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] += b[i];
-                    }
                     if (p.epi == EPI_RESIDUAL) {
+                        // the reference adds to the linear's bf16 OUTPUT: bf16(acc) (+ bias, rounded again:
+                        // residual_add_bias, Infer-engine/cuda/kernels.cu:763-782), then the residual
+                        if (p.bias != nullptr) {
+                            float b[32];
+                            load_row_chunk(p.bias + col, b, nvalid);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + b[i];
+                        }
                         float res[32];
                         load_row_chunk(p.residual + (size_t)row * p.ldo + col, res, nvalid);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
+                    } else {
+                        if (p.bias != nullptr) {
+                            float b[32];
+                            load_row_chunk(p.bias + col, b, nvalid);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += b[i];
+                        }
+                        if (p.epi == EPI_GELU) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+                        }
                     }
                     if (!GLMASR_EXP(p, 4)) store_row_chunk(out_row + col, v, nvalid);
                 };

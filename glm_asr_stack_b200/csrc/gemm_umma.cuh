@@ -16,7 +16,9 @@ enum GemmMode : int {
 enum EpilogueMode : int {
     EPI_STORE = 0,      // out[m, n] = bf16(acc * alpha_seg (+ bias[n]))
     EPI_SILU_GATE = 1,  // segments 0/1 = gate/up: out[m, n] = bf16(silu(bf16(g)) * bf16(u))
-    EPI_RESIDUAL = 2,   // out[m, n] = bf16(float(bf16(acc * alpha)) + float(residual[m, n]))
+    EPI_RESIDUAL = 2,   // out[m, n] = bf16(float(bf16(acc * alpha)) + float(residual[m, n])); with a bias:
+                        // bf16(float(bf16(float(bf16(acc * alpha)) + bias[n])) + float(residual[m, n]))
+    EPI_GELU = 3,       // out[m, n] = bf16(gelu_tanh(acc * alpha_seg + bias[n]))   (single-CTA kernel only)
 };
 
 static constexpr int kMaxSegments = 3;

@@ -1,4 +1,6 @@
-// Variable-length causal GQA self-attention for batched prefill, head_dim 128 (the attention
+// Variable-length GQA self-attention, head_dim 128 (causal, batched prefill) or 64 (non-causal, the audio
+// encoder's attention, Infer-engine/cuda/encoder.cu:1870-1970): the kernel is a template on the head dimension.
+// Head_dim 128 is the attention
 // step of decoder_prefill_paged_batched, Infer-engine/cuda/decoder.cu:1401-1441: per sequence
 // softmax(Q K^T / sqrt(d) + causal mask) V over the sequence's own new tokens, q heads sharing
 // kv head q / group).  The reference reaches it through a compiled plug-in
@@ -24,9 +26,15 @@ namespace {
 
 constexpr int kQTile = 64;                 // queries per CTA
 constexpr int kKTile = 64;                 // keys per step
-constexpr int kRowBytes = 256;             // 128 bf16
-constexpr int kTileBytes = kKTile * kRowBytes;             // 16 KB
-constexpr int kSmem = 2 * 2 * kTileBytes;                  // K and V, double-buffered: 64 KB
+template <int HD>
+struct AttnCfg {
+    static constexpr int kRowBytes = HD * 2;                       // one K / V row of a head
+    static constexpr int kChunks = HD / 8;                         // 16-byte chunks per row
+    static constexpr int kTileBytes = kKTile * kRowBytes;          // 16 KB (head_dim 128) / 8 KB (64)
+    static constexpr int kSmem = 2 * 2 * kTileBytes;               // K and V, double-buffered
+    static constexpr int kKSteps = HD / 16;                        // k steps of the S product, dim-tile pairs of PV
+    static constexpr int kDimTiles = HD / 8;                       // 8-column accumulator tiles of O
+};
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void *src, bool valid) {
     const int n = valid ? 16 : 0;
@@ -53,9 +61,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&b);
 }
-// swizzled byte offset of 16-byte chunk c (0..15) of row r inside a tile
-__device__ __forceinline__ uint32_t toff(int r, int c) { return (uint32_t)(r * kRowBytes + ((c ^ (r & 7)) << 4)); }
+// swizzled byte offset of 16-byte chunk c of row r inside a tile (rows of 16 or 8 chunks)
+template <int HD>
+__device__ __forceinline__ uint32_t toff(int r, int c) { return (uint32_t)(r * AttnCfg<HD>::kRowBytes + ((c ^ (r & 7)) << 4)); }
 
+template <int HD>
 __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *__restrict__ out, int ldo,
                                                                const __nv_bfloat16 *__restrict__ q, int ldq,
                                                                const __nv_bfloat16 *__restrict__ k, int ldk,
@@ -63,6 +73,8 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
                                                                const int *__restrict__ seq_offsets,
                                                                const int *__restrict__ seq_lens, int group, float scale,
                                                                int causal) {
+    using C = AttnCfg<HD>;
+    constexpr int kTileBytes = C::kTileBytes;
     extern __shared__ __align__(1024) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -82,16 +94,17 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
     auto load_tile = [&](int t) {
         const uint32_t kdst = sbase + (uint32_t)(t & 1) * (2 * kTileBytes);
         const uint32_t vdst = kdst + kTileBytes;
-        const int c = threadIdx.x & 15;
-        const int r0 = threadIdx.x >> 4;                 // 8 rows per pass
+        constexpr int kRowsPerPass = 128 / C::kChunks;   // 8 (head_dim 128) or 16 (64) rows per pass
+        const int c = threadIdx.x % C::kChunks;
+        const int r0 = threadIdx.x / C::kChunks;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int r = j * 8 + r0;
+        for (int j = 0; j < kKTile / kRowsPerPass; ++j) {
+            const int r = j * kRowsPerPass + r0;
             const int tok = t * kKTile + r;
             const bool valid = tok < len;
             const size_t row = (size_t)(off + (valid ? tok : 0));
-            cp16(kdst + toff(r, c), k + row * ldk + (size_t)kv_head * 128 + c * 8, valid);
-            cp16(vdst + toff(r, c), v + row * ldv + (size_t)kv_head * 128 + c * 8, valid);
+            cp16(kdst + toff<HD>(r, c), k + row * ldk + (size_t)kv_head * HD + c * 8, valid);
+            cp16(vdst + toff<HD>(r, c), v + row * ldv + (size_t)kv_head * HD + c * 8, valid);
         }
     };
 
@@ -100,12 +113,12 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
 
     // Q fragments of this warp's 16 rows (rows past the sequence read zeros)
     const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
-    uint32_t qa[8][4];
+    uint32_t qa[C::kKSteps][4];
     {
-        const __nv_bfloat16 *qa_p = q + (size_t)(off + row_a) * ldq + (size_t)head * 128;
-        const __nv_bfloat16 *qb_p = q + (size_t)(off + row_b) * ldq + (size_t)head * 128;
+        const __nv_bfloat16 *qa_p = q + (size_t)(off + row_a) * ldq + (size_t)head * HD;
+        const __nv_bfloat16 *qb_p = q + (size_t)(off + row_b) * ldq + (size_t)head * HD;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < C::kKSteps; ++ks) {
             qa[ks][0] = row_a < len ? *reinterpret_cast<const uint32_t *>(qa_p + ks * 16 + tq * 2) : 0u;
             qa[ks][1] = row_b < len ? *reinterpret_cast<const uint32_t *>(qb_p + ks * 16 + tq * 2) : 0u;
             qa[ks][2] = row_a < len ? *reinterpret_cast<const uint32_t *>(qa_p + ks * 16 + 8 + tq * 2) : 0u;
@@ -113,9 +126,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
         }
     }
 
-    float acc[16][4];
+    float acc[C::kDimTiles][4];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    for (int n = 0; n < C::kDimTiles; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;      // running max / partial sum of rows a, b
 
     for (int t = 0; t < nt; ++t) {
@@ -138,11 +151,11 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
 #pragma unroll
             for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
+            for (int ks = 0; ks < C::kKSteps; ++ks) {
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {           // 16 keys per ldmatrix.x4
                     uint32_t kb[4];
-                    ldsm4(kbase + toff(jj * 16 + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), kb);
+                    ldsm4(kbase + toff<HD>(jj * 16 + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), kb);
                     mma16816(s[2 * jj], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[0], kb[1]);
                     mma16816(s[2 * jj + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[2], kb[3]);
                 }
@@ -187,13 +200,13 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
             m_a = mn_a;
             m_b = mn_b;
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
+            for (int n = 0; n < C::kDimTiles; ++n) {
                 acc[n][0] *= corr_a;
                 acc[n][1] *= corr_a;
                 acc[n][2] *= corr_b;
                 acc[n][3] *= corr_b;
             }
-            // ---- O += P V: 4 key steps of 16, 16 dim tiles of 8 ----
+            // ---- O += P V: 4 key steps of 16, head_dim / 8 dim tiles of 8 ----
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
                 const uint32_t pa0 = pack2(s[2 * kk][0], s[2 * kk][1]);
@@ -201,9 +214,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
                 const uint32_t pa2 = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
                 const uint32_t pa3 = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < C::kKSteps; ++j) {
                     uint32_t vb[4];
-                    ldsm4t(vbase + toff(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * j + (lane >> 4)), vb);
+                    ldsm4t(vbase + toff<HD>(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * j + (lane >> 4)), vb);
                     mma16816(acc[2 * j], pa0, pa1, pa2, pa3, vb[0], vb[1]);
                     mma16816(acc[2 * j + 1], pa0, pa1, pa2, pa3, vb[2], vb[3]);
                 }
@@ -220,14 +233,14 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(__nv_bfloat16 *_
     const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f;
     const float inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
     if (row_a < len) {
-        __nv_bfloat16 *o = out + (size_t)(off + row_a) * ldo + (size_t)head * 128 + tq * 2;
+        __nv_bfloat16 *o = out + (size_t)(off + row_a) * ldo + (size_t)head * HD + tq * 2;
 #pragma unroll
-        for (int n = 0; n < 16; ++n) *reinterpret_cast<uint32_t *>(o + n * 8) = pack2(acc[n][0] * inv_a, acc[n][1] * inv_a);
+        for (int n = 0; n < C::kDimTiles; ++n) *reinterpret_cast<uint32_t *>(o + n * 8) = pack2(acc[n][0] * inv_a, acc[n][1] * inv_a);
     }
     if (row_b < len) {
-        __nv_bfloat16 *o = out + (size_t)(off + row_b) * ldo + (size_t)head * 128 + tq * 2;
+        __nv_bfloat16 *o = out + (size_t)(off + row_b) * ldo + (size_t)head * HD + tq * 2;
 #pragma unroll
-        for (int n = 0; n < 16; ++n) *reinterpret_cast<uint32_t *>(o + n * 8) = pack2(acc[n][2] * inv_b, acc[n][3] * inv_b);
+        for (int n = 0; n < C::kDimTiles; ++n) *reinterpret_cast<uint32_t *>(o + n * 8) = pack2(acc[n][2] * inv_b, acc[n][3] * inv_b);
     }
 }
 
@@ -244,20 +257,28 @@ bool launch_prefill_attention(__nv_bfloat16 *out, int ldo, const __nv_bfloat16 *
                                       q_input_scale))
         return true;
     if (q_packed != nullptr) return false;      // only the tcgen05 kernel quantises its output
-    if (head_dim != 128 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return false;
+    if ((head_dim != 128 && head_dim != 64) || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return false;
     if ((ldq % 2) != 0 || (ldo % 2) != 0 || (ldk % 8) != 0 || (ldv % 8) != 0) return false;
     if ((((uintptr_t)k | (uintptr_t)v) & 15) != 0 || (((uintptr_t)q | (uintptr_t)out) & 3) != 0) return false;
     if (num_seqs <= 0 || max_seq_len <= 0) return true;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(prefill_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<128>::kSmem) !=
+            cudaSuccess)
             return false;
         configured = true;
     }
-    GLMASR_PREFER_MAX_SMEM(prefill_attention_kernel);
     const dim3 grid((max_seq_len + kQTile - 1) / kQTile, num_q_heads, num_seqs);
-    launch_chained(prefill_attention_kernel, grid, dim3(128), (size_t)kSmem, st, out, ldo, q, ldq, k, ldk, v, ldv, seq_offsets,
-                   seq_lens, num_q_heads / num_kv_heads, 1.0f / sqrtf((float)head_dim), causal ? 1 : 0);
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    if (head_dim == 128) {
+        GLMASR_PREFER_MAX_SMEM(prefill_attention_kernel<128>);
+        launch_chained(prefill_attention_kernel<128>, grid, dim3(128), (size_t)AttnCfg<128>::kSmem, st, out, ldo, q, ldq, k, ldk, v,
+                       ldv, seq_offsets, seq_lens, num_q_heads / num_kv_heads, scale, causal ? 1 : 0);
+    } else {
+        GLMASR_PREFER_MAX_SMEM(prefill_attention_kernel<64>);
+        launch_chained(prefill_attention_kernel<64>, grid, dim3(128), (size_t)AttnCfg<64>::kSmem, st, out, ldo, q, ldq, k, ldk, v,
+                       ldv, seq_offsets, seq_lens, num_q_heads / num_kv_heads, scale, causal ? 1 : 0);
+    }
     return true;
 }
 

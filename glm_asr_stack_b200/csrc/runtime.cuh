@@ -20,6 +20,7 @@ void *workspace_slot(int slot, size_t bytes);
 // Slots owned outside api.cu / decoder_step.cu (those two number their own, 0..31).
 enum : int { WS_ATTN_VT = 32, WS_ATTN_VT_COL = 33, WS_ATTN_DEBUG = 34 };
 void free_all_private_state();
+void encoder_forget_all();         // encoder.cu: per-store weight table, re-packed convolution weights, rotary table
 void note_launches(int n);          // launch accounting for kernels started outside api.cu
 size_t tiled_scale_bytes(int rows, int K);
 // Cached TMA descriptor of a row-major bf16 matrix [rows, inner] (row pitch in bytes, a multiple of 16; base

@@ -150,6 +150,14 @@ def inspect_safetensors(path: str):
     return out, int(arena.value)
 
 
+def encoder_config(cfg: CModelConfig, hidden=1280, layers=32, heads=20, head_dim=64, ffn=5120, mels=128, max_frames=3000,
+                   proj_mid=4096) -> CModelConfig:
+    """Fill the audio side of a ModelConfig (Infer-engine/include/types.h:37-72; the defaults are the checkpoint's)."""
+    cfg.enc_hidden, cfg.enc_layers, cfg.enc_heads, cfg.enc_head_dim, cfg.enc_ffn = hidden, layers, heads, head_dim, ffn
+    cfg.num_mel_bins, cfg.max_audio_frames, cfg.proj_mid = mels, max_frames, proj_mid
+    return cfg
+
+
 def model_config(hidden=2048, layers=28, heads=16, kv_heads=4, head_dim=128, ffn=6144, vocab=59264) -> CModelConfig:
     c = CModelConfig()
     c.dec_hidden, c.dec_layers, c.dec_heads, c.dec_kv_heads = hidden, layers, heads, kv_heads

@@ -365,6 +365,89 @@ def layer_proj_host(mode: int, hidden_in_host: torch.Tensor, hidden_out_host: to
     return hidden_out_host
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, eps: float = 1e-5,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference: layernorm, Infer-engine/cuda/kernels.cu:299-356."""
+    lib = _lib.load()
+    _check(x, torch.bfloat16, "x")
+    rows, dim = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    lib.layernorm(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), float(eps), rows, dim)
+    return out
+
+
+def gelu_inplace(x: torch.Tensor) -> torch.Tensor:
+    """reference: gelu_inplace, Infer-engine/cuda/kernels.cu:364-381."""
+    _check(x, torch.bfloat16, "x")
+    _lib.load().gelu_inplace(_ptr(x), x.numel())
+    return x
+
+
+def rope_encoder(q: torch.Tensor, k: torch.Tensor, num_heads: int, head_dim: int, partial_factor: float = 0.5):
+    """reference: rope_encoder, Infer-engine/cuda/kernels.cu:427-484; q, k [seq_len, num_heads * head_dim] in place."""
+    _lib.load().rope_encoder(_ptr(q), _ptr(k), q.shape[0], num_heads, head_dim, float(partial_factor))
+    return q, k
+
+
+def residual_add_bias(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """reference: residual_add_bias, Infer-engine/cuda/kernels.cu:763-795."""
+    out = torch.empty_like(a)
+    _lib.load().residual_add_bias(_ptr(out), _ptr(a), _ptr(b), _ptr(bias), a.shape[0], a.shape[1])
+    return out
+
+
+def conv1d_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], stride: int, padding: int) -> torch.Tensor:
+    """reference: conv1d_forward, Infer-engine/cuda/kernels.cu:1561-1629; x [in_ch, len], weight [out_ch, in_ch, k]."""
+    in_ch, ln = x.shape
+    out_ch, _, ks = weight.shape
+    out_len = (ln + 2 * padding - ks) // stride + 1
+    out = torch.empty((out_ch, out_len), dtype=torch.bfloat16, device=x.device)
+    _lib.load().conv1d_forward(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), in_ch, out_ch, ln, ks, stride, padding)
+    return out
+
+
+def transpose_2d(x: torch.Tensor) -> torch.Tensor:
+    out = torch.empty((x.shape[1], x.shape[0]), dtype=x.dtype, device=x.device)
+    _lib.load().transpose_2d(_ptr(out), _ptr(x), x.shape[0], x.shape[1])
+    return out
+
+
+def bf16_linear_gelu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """reference: bf16_linear_gelu, Infer-engine/cuda/kernels.cu:1211-1250."""
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _lib.load().bf16_linear_gelu(None, _ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K)
+    return out
+
+
+def encoder_forward_packed(ws, cfg, hidden: torch.Tensor, seq_lens: Sequence[int], seq_offsets: Sequence[int]) -> torch.Tensor:
+    """reference: encoder_forward_packed, Infer-engine/cuda/encoder.cu:2441-2462; in place on hidden [rows, enc_hidden].
+    ws: an object whose ``.c`` is the C WeightStore, cfg: the C ModelConfig."""
+    n = len(seq_lens)
+    lens = (ctypes.c_int * n)(*[int(v) for v in seq_lens])
+    offs = (ctypes.c_int * n)(*[int(v) for v in seq_offsets])
+    _lib.load().encoder_forward_packed(None, ctypes.byref(ws.c), _ptr(hidden), hidden.shape[0], n, lens, offs, ctypes.byref(cfg))
+    return hidden
+
+
+def audio_encode_batched(ws, cfg, mel_time_major: torch.Tensor, n_frames: Sequence[int], out: Optional[torch.Tensor] = None):
+    """glmasr_audio_encode_batched: mel_time_major bf16 [windows, stride] (window i holds [n_i, num_mel_bins]) ->
+    (bf16 [windows, max_tokens, dec_hidden], tokens per window)."""
+    w = mel_time_major.shape[0]
+    max_tokens = max(((int(n) + 1) // 2) // 4 for n in n_frames)
+    if out is None:
+        out = torch.zeros((w, max_tokens, cfg.dec_hidden), dtype=torch.bfloat16, device=mel_time_major.device)
+    nf = (ctypes.c_int * w)(*[int(v) for v in n_frames])
+    tok = (ctypes.c_int * w)()
+    rc = _lib.load().glmasr_audio_encode_batched(ctypes.byref(ws.c), ctypes.byref(cfg), _ptr(mel_time_major),
+                                                 mel_time_major.stride(0), nf, w, _ptr(out), out.stride(0), tok)
+    if rc != 0:
+        raise ValueError("glmasr_audio_encode_batched rejected the arguments")
+    return out, list(tok)
+
+
 def mel_spectrogram(pcm: torch.Tensor, mel_filters_t: torch.Tensor) -> torch.Tensor:
     """reference: mel_spectrogram, Infer-engine/cuda/mel.cu:253-294.  pcm float32 [num_samples] and the
     transposed filterbank float32 [201, 128] on the device -> bf16 [128, n_frames]."""

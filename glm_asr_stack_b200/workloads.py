@@ -113,3 +113,56 @@ def build_prefill_state(cfg, num_seqs=25, seq_len=400, block_size=16, seed=4, de
     tables = [[perm.pop() for _ in range(nb)] for nb in need]
     bts = engine.BlockTables(pool, tables)
     return PrefillState(pool, bts, lens, [int(o) for o in offs], int(sum(lens)))
+
+
+def add_audio_tower(ws: engine.WeightStore, cfg, layers=32, hidden=1280, heads=20, head_dim=64, ffn=5120, mels=128,
+                    proj_mid=4096, device="cuda", seed0=5000):
+    """Random-init bf16 audio encoder, convolution front end and projector under the checkpoint's tensor names
+    (Infer-engine/cuda/encoder.cu:1996-2186, Infer-engine/src/engine.c:1116-1153): weights ~ N(0, 0.02), LayerNorm
+    weights around 1, small biases (k_proj has none).  Fills the audio fields of cfg.  Returns the bytes added."""
+    engine.encoder_config(cfg, hidden, layers, heads, head_dim, ffn, mels, 3000, proj_mid)
+    gen = torch.Generator(device=device).manual_seed(seed0)
+    nbytes = 0
+
+    def add(name, shape, std, mean=0.0):
+        nonlocal nbytes
+        t = (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std + mean).to(torch.bfloat16)
+        ws.add(name, t)
+        nbytes += t.numel() * 2
+
+    add("audio_tower.conv1.weight", (hidden, mels, 3), 0.02)
+    add("audio_tower.conv1.bias", (hidden,), 0.02)
+    add("audio_tower.conv2.weight", (hidden, hidden, 3), 0.02)
+    add("audio_tower.conv2.bias", (hidden,), 0.02)
+    for l in range(layers):
+        p = f"audio_tower.layers.{l}."
+        for ln in ("input_layernorm", "post_attention_layernorm"):
+            add(p + ln + ".weight", (hidden,), 0.1, 1.0)
+            add(p + ln + ".bias", (hidden,), 0.02)
+        for proj in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            add(p + f"self_attn.{proj}.weight", (hidden, hidden), 0.02)
+            if proj != "k_proj":
+                add(p + f"self_attn.{proj}.bias", (hidden,), 0.02)
+        add(p + "mlp.fc1.weight", (ffn, hidden), 0.02)
+        add(p + "mlp.fc1.bias", (ffn,), 0.02)
+        add(p + "mlp.fc2.weight", (hidden, ffn), 0.02)
+        add(p + "mlp.fc2.bias", (hidden,), 0.02)
+    add("audio_tower.norm.weight", (hidden,), 0.1, 1.0)
+    add("audio_tower.norm.bias", (hidden,), 0.02)
+    add("multi_modal_projector.linear_1.weight", (proj_mid, 4 * hidden), 0.02)
+    add("multi_modal_projector.linear_1.bias", (proj_mid,), 0.02)
+    add("multi_modal_projector.linear_2.weight", (cfg.dec_hidden, proj_mid), 0.02)
+    add("multi_modal_projector.linear_2.bias", (cfg.dec_hidden,), 0.02)
+    return nbytes
+
+
+def encoder_flops(rows_per_window: int, windows: int, hidden=1280, heads=20, head_dim=64, ffn=5120, layers=32, mels=128,
+                  proj_mid=4096, dec_hidden=2048) -> float:
+    """Multiply-add flops (x2) of the audio path for `windows` windows of rows_per_window encoder frames: the two
+    convolutions, the layers' six GEMMs and attention (non-causal, both products), the projector."""
+    t2 = rows_per_window
+    t1 = 2 * t2
+    conv = 2.0 * t1 * hidden * 3 * mels + 2.0 * t2 * hidden * 3 * hidden
+    layer = 2.0 * t2 * (4 * hidden * hidden + 2 * hidden * ffn) + 2.0 * 2 * heads * head_dim * t2 * t2
+    proj = 2.0 * (t2 // 4) * (4 * hidden * proj_mid + proj_mid * dec_hidden)
+    return windows * (conv + layers * layer + proj)

@@ -146,7 +146,54 @@ void mel_spectrogram(const float *pcm, int num_samples, const float *mel_filters
 /* Infer-engine/cuda/mel.cu:86-109.  Nothing to release here beyond what glmasr_fp4_cleanup frees. */
 void mel_cleanup(void);
 
+/* ---- audio encoder (bf16) ---- */
+
+/* Infer-engine/include/cuda_kernels.h:26-28, Infer-engine/cuda/kernels.cu:299-356.  out = bf16(((x - mean) / sqrt(var
+ * + eps)) * weight + bias) per row, the reference's summation order; bias may be NULL; out may alias x. */
+void layernorm(uint16_t *out, const uint16_t *x, const uint16_t *weight, const uint16_t *bias, float eps, int rows, int dim);
+/* Infer-engine/include/cuda_kernels.h:30, Infer-engine/cuda/kernels.cu:364-381: tanh-GELU in place. */
+void gelu_inplace(uint16_t *x, int n);
+/* Infer-engine/include/cuda_kernels.h:34-36, Infer-engine/cuda/kernels.cu:427-484: the encoder's partial rotary
+ * embedding of q and k [seq_len, num_heads, head_dim] in place (rot_dim = head_dim * partial_factor = 32 only). */
+void rope_encoder(uint16_t *q, uint16_t *k, int seq_len, int num_heads, int head_dim, float partial_factor);
+/* Infer-engine/include/cuda_kernels.h:47-51, Infer-engine/cuda/kernels.cu:763-795: out = bf16(bf16(a + bias[col]) + b). */
+void residual_add_bias(uint16_t *out, const uint16_t *a, const uint16_t *b, const uint16_t *bias, int M, int N);
+/* Infer-engine/include/cuda_kernels.h:53-54, Infer-engine/cuda/kernels.cu:801-826: [seq, dim] -> [seq / 4, 4 dim]. */
+void concat_4frames(uint16_t *out, const uint16_t *in, int seq_len, int dim);
+/* Infer-engine/include/cuda_kernels.h:56-59, Infer-engine/cuda/kernels.cu:1561-1629: input [in_ch, seq_len], weight
+ * [out_ch, in_ch, kernel_size], out [out_ch, out_len] bf16, bias per output channel.  One GEMM with K = kernel_size
+ * * in_ch (the reference: one accumulating GEMM per tap, partial sums rounded to bf16 in between). */
+void conv1d_forward(uint16_t *out, const uint16_t *input, const uint16_t *weight, const uint16_t *bias, int in_ch, int out_ch,
+                    int seq_len, int kernel_size, int stride, int padding);
+/* Infer-engine/include/cuda_kernels.h:61-62, Infer-engine/cuda/kernels.cu:1631-1660: out[c, r] = in[r, c]. */
+void transpose_2d(uint16_t *out, const uint16_t *in, int rows, int cols);
+/* Infer-engine/include/cuda_kernels.h:71-75, Infer-engine/cuda/kernels.cu:1211-1250: bf16 linear + bias + tanh-GELU
+ * in one tcgen05 GEMM (K % 64 == 0, 16-byte aligned pointers; otherwise exit(1)). */
+void bf16_linear_gelu(void *handle, uint16_t *out, const uint16_t *x, const uint16_t *w, const uint16_t *bias, int M, int N,
+                      int K);
+/* Infer-engine/include/cuda_kernels.h:101-111, Infer-engine/cuda/encoder.cu:1974-2188, 2427-2462: the encoder stack
+ * (enc_layers pre-norm layers: LayerNorm, q|k|v, partial rotary embedding, non-causal attention over the sequence's
+ * own frames, o + bias + residual, LayerNorm, fc1 + bias + GELU, fc2 + bias + residual; final LayerNorm) in place on
+ * hidden [total_rows, enc_hidden]; sequence s owns rows [seq_offsets[s], + seq_lens[s]) (host arrays).  ws:
+ * WeightStore*, cfg: ModelConfig* (enc_head_dim must be 64); handle is unused. */
+void encoder_forward(void *handle, const void *ws, uint16_t *hidden, int seq_len, const void *cfg);
+void encoder_forward_packed(void *handle, const void *ws, uint16_t *hidden, int total_rows, int num_seqs, const int *seq_lens,
+                            const int *seq_offsets, const void *cfg);
+/* Infer-engine/include/cuda_kernels.h:121, Infer-engine/cuda/encoder.cu:2421-2423: drop what the encoder cached
+ * about a WeightStore (call before freeing the store). */
+void encoder_cleanup(void);
+
 /* ======================= 2. additive entry points ======================= */
+
+/* The whole audio path after the log-mel features for a batch of windows (Infer-engine/src/engine.c:1111-1160,
+ * 1561-1601): convolution front end (k 3 stride 1, k 3 stride 2, tanh-GELU after each), encoder stack, projector
+ * (four frames concatenated, linear + GELU, linear).  mel: TIME-MAJOR features as glmasr_mel_spectrogram_batched
+ * (time_major = 1) writes them, window i at mel + i * mel_stride holding [n_frames_host[i], num_mel_bins]; out:
+ * window i's audio embeddings at out + i * out_stride as [tokens_i, dec_hidden], tokens_i = ((n_i + 1) / 2) / 4 =
+ * out_tokens_host[i] (may be NULL).  Returns 0 or -1. */
+int glmasr_audio_encode_batched(const void *ws, const void *cfg, const uint16_t *mel, long long mel_stride,
+                                const int *n_frames_host, int num_windows, uint16_t *out, long long out_stride,
+                                int *out_tokens_host);
 
 /* mel_spectrogram for a batch of windows in two launches: window i reads pcm + i * pcm_stride (floats,
  * num_samples_host[i] of them) and writes mel_out + i * out_stride (bf16 elements) as [128, n_frames_i]

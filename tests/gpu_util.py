@@ -26,3 +26,16 @@ def ulp_diff(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:
 # Tolerances of the parity bars (bf16 outputs, fp32 accumulation in an unspecified order):
 REL_TOL_VS_ORACLE = 1e-2      # stated bar: bf16-out relative error <= 1e-2
 REL_TOL_TIGHT = 4e-3          # what the same arithmetic with a different summation order gives
+
+
+def bf16_unit_excess(got_bits: np.ndarray, want_bits: np.ndarray, floor: float = 2.0 ** -6):
+    """How far two finite bf16 arrays are apart, in units of one bf16 step AT THE VALUE'S MAGNITUDE (the step of
+    `floor` for values closer to zero than that: where a result comes out of a cancellation -- 1 + tanh, a*c - b*s,
+    v + 4 -- a unit in the last place of the tiny result says nothing).  Returns (largest distance in such units,
+    fraction of elements whose bits differ)."""
+    def f32(b):
+        return (b.astype(np.uint32) << 16).view(np.float32)
+    got, want = f32(np.ascontiguousarray(got_bits)), f32(np.ascontiguousarray(want_bits))
+    mag = np.maximum(np.maximum(np.abs(want), np.abs(got)), floor)
+    unit = 2.0 ** (np.floor(np.log2(mag)) - 7)
+    return float((np.abs(got - want) / unit).max()), float((got_bits != want_bits).mean())

@@ -41,6 +41,17 @@ class RefLib:
         if hasattr(L, "mel_spectrogram"):
             L.mel_spectrogram.argtypes = [P, c_int, P, P, P]
             L.mel_spectrogram.restype = None
+        if hasattr(L, "encoder_forward_packed"):
+            L.layernorm.argtypes = [P, P, P, P, c_float, c_int, c_int]
+            L.layernorm.restype = None
+            L.gelu_inplace.argtypes = [P, c_int]
+            L.gelu_inplace.restype = None
+            L.conv1d_forward.argtypes = [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int]
+            L.conv1d_forward.restype = None
+            L.encoder_forward_packed.argtypes = [P, P, P, c_int, c_int, P, P, P]
+            L.encoder_forward_packed.restype = None
+            L.bf16_linear_gelu.argtypes = [P, P, P, P, P, c_int, c_int, c_int]
+            L.bf16_linear_gelu.restype = None
         # the reference's fp4_linear / bf16_linear take a cublasHandle_t
         self.cublas = ctypes.CDLL("libcublas.so.12")
         self.handle = c_void_p()
@@ -81,6 +92,40 @@ class RefLib:
                                    self._p(scales), input_scale, g, self._p(pre), None, M, N, K)
         torch.cuda.synchronize()
         return rc, out
+
+    def has_encoder(self):
+        return hasattr(self.lib, "encoder_forward_packed")
+
+    def layernorm(self, x, w, b, eps=1e-5):
+        out = torch.empty_like(x)
+        self.lib.layernorm(self._p(out), self._p(x), self._p(w), self._p(b), eps, x.shape[0], x.shape[1])
+        torch.cuda.synchronize()
+        return out
+
+    def gelu_inplace(self, x):
+        y = x.clone()
+        self.lib.gelu_inplace(self._p(y), y.numel())
+        torch.cuda.synchronize()
+        return y
+
+    def conv1d_forward(self, x, w, b, stride, padding):
+        in_ch, ln = x.shape
+        out_ch, _, ks = w.shape
+        out_len = (ln + 2 * padding - ks) // stride + 1
+        out = torch.empty((out_ch, out_len), dtype=torch.bfloat16, device="cuda")
+        self.lib.conv1d_forward(self._p(out), self._p(x), self._p(w), self._p(b), in_ch, out_ch, ln, ks, stride, padding)
+        torch.cuda.synchronize()
+        return out
+
+    def encoder_forward_packed(self, ws, cfg, hidden, seq_lens, seq_offsets):
+        """The reference's encoder on a ctypes WeightStore / ModelConfig (same struct layouts); returns a new tensor."""
+        h = hidden.clone()
+        n = len(seq_lens)
+        lens = (ctypes.c_int * n)(*[int(v) for v in seq_lens])
+        offs = (ctypes.c_int * n)(*[int(v) for v in seq_offsets])
+        self.lib.encoder_forward_packed(self.handle, ctypes.byref(ws.c), self._p(h), h.shape[0], n, lens, offs, ctypes.byref(cfg))
+        torch.cuda.synchronize()
+        return h
 
     def mel_spectrogram(self, pcm, filters_t):
         """Infer-engine/cuda/mel.cu:253-294 -> bf16 [128, n_frames]."""

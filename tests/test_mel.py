@@ -53,12 +53,10 @@ def test_oracle_reference_maximum_sees_one_eighth_of_the_window():
 
 
 def _check(got_bits, want_f32, what):
-    want_bits = o.f32_to_bf16_bits(want_f32)
-    got, want = o.bf16_bits_to_f32(got_bits), o.bf16_bits_to_f32(want_bits)
-    unit = 2.0 ** -8 * np.maximum(np.abs(want), 2.0 ** -6)         # one bf16 unit at the value's magnitude
-    excess = np.abs(got - want) / unit
-    assert excess.max() <= 1.0 + 1e-3, (what, float(excess.max()))
-    assert (got_bits != want_bits).mean() <= 0.05, (what, float((got_bits != want_bits).mean()))
+    from gpu_util import bf16_unit_excess
+    excess, differ = bf16_unit_excess(got_bits, o.f32_to_bf16_bits(want_f32))
+    assert excess <= 1.0, (what, excess)
+    assert differ <= 0.05, (what, differ)
 
 
 @pytest.mark.gpu
