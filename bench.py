@@ -20,6 +20,8 @@ timed alone on the same shapes.
 import argparse
 import json
 import os
+
+import numpy as np
 import statistics
 import subprocess
 import sys
@@ -467,6 +469,140 @@ def measure_prefill(model, st, mix, steps, warmup, dist, local_rank, world):
     }
 
 
+# ---------------------------------------------------------------------------------------------------------
+# benchmark configuration 3 (audio encoder) and 4 (end to end over 1431 windows)
+# ---------------------------------------------------------------------------------------------------------
+def measure_encoder(model, steps, warmup, dist, local_rank, world, windows=16):
+    """Configuration 3: the audio path after the log-mel features for a batch of `windows` windows of 128 x 3000
+    features ~ U[-1.5, 1.5]: two-convolution front end, 32 encoder layers at d = 1280, the 4x projector to the
+    decoder width.  TFLOP/s over the model's multiply-adds, against the measured bf16 peak."""
+    import torch
+
+    from glm_asr_stack_b200 import ops, workloads
+    cfg = model.cfg
+    gen = torch.Generator(device="cuda").manual_seed(33)
+    mel = ((torch.rand((windows, 3000, cfg.num_mel_bins), generator=gen, device="cuda") * 3.0 - 1.5).to(torch.bfloat16)
+           .reshape(windows, -1).contiguous())
+    frames = [3000] * windows
+    out = torch.zeros((windows, 375, cfg.dec_hidden), dtype=torch.bfloat16, device="cuda")
+    mel_host = mel.cpu().pin_memory()
+    out_host = torch.empty_like(out, device="cpu").pin_memory()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        ops.audio_encode_batched(model.ws, cfg, mel, frames, out=out)
+    torch.cuda.synchronize()
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st}"
+    sampler = ClockSampler(local_rank)
+    ms, _, region_s, launches = timed_steps(lambda i: ops.audio_encode_batched(model.ws, cfg, mel, frames, out=out), steps,
+                                            barrier, sampler, counter=ops.launch_count)
+    clocks = sampler.stop()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        mel.copy_(mel_host, non_blocking=True)
+        ops.audio_encode_batched(model.ws, cfg, mel, frames, out=out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / steps * 1e3
+    ms = replicas.max_over_ranks(ms, dist, "cuda")
+    e2e_ms = replicas.max_over_ranks(e2e_ms, dist, "cuda")
+    flops = workloads.encoder_flops(1500, windows, cfg.enc_hidden, cfg.enc_heads, cfg.enc_head_dim, cfg.enc_ffn, cfg.enc_layers,
+                                    cfg.num_mel_bins, cfg.proj_mid, cfg.dec_hidden)
+    peaks = measured_peaks()
+    peak = peaks["bf16_tflops_sustained"] if peaks else 1400.0
+    tf = replicas.whole_job_rate(flops, world, ms * 1e-3) / 1e12
+    return {
+        "metric": "encoder_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "timed_region_s": region_s,
+        "windows_per_s": replicas.whole_job_rate(windows, world, ms * 1e-3),
+        "workload": f"config3: {windows} windows x [128, 3000] log-mel ~U[-1.5, 1.5] -> conv front end -> {cfg.enc_layers} layers "
+                    f"d={cfg.enc_hidden}, {cfg.enc_heads} heads, FFN {cfg.enc_ffn} -> 4x projector to {cfg.dec_hidden}; bf16",
+        "e2e": {"value": replicas.whole_job_rate(flops, world, e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": mel.numel() * 2, "d2h_bytes_per_step": out.numel() * 2, "ms_per_step": e2e_ms},
+        "gpu_launches_per_step": int(launches // max(1, steps)), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak,
+                     "peak_source": "measured sustained bf16 GEMM (MEASURED_PEAKS.json)" if peaks else "fallback 1400 TFLOP/s"},
+    }
+
+
+def measure_e2e(model, total_windows, new_tokens, dist, rank, local_rank, world, warm_windows=8):
+    """Configuration 4: `total_windows` synthetic 30 s windows (seeded pink noise under random amplitude envelopes), cut
+    across the ranks by replicas.shard_rows, each through log-mel -> encoder -> projector -> prefill -> greedy decode of
+    exactly `new_tokens` tokens (EOS ignored), GLMASR_MAX_SEQS = 256 and GLMASR_MAX_BATCHED_TOKENS = 10000; the token
+    ids are gathered on rank 0 in window order.  RTFx = seconds of audio / seconds of the slowest rank."""
+    import torch
+
+    from glm_asr_stack_b200 import pipeline
+    set_projection_mix("all_w4a4")
+    begin, end = replicas.shard_rows(total_windows, rank, world)
+    n = end - begin
+    from glm_asr_stack_b200 import synth
+    filt = synth.mel_filterbank()
+    pcm = torch.empty((max(n, 1), pipeline.SAMPLES_PER_WINDOW), dtype=torch.float32).pin_memory()
+    for i in range(n):
+        pcm[i].copy_(pipeline.synthetic_window(begin + i))
+    torch.cuda.synchronize()
+    pipe = pipeline.AsrPipeline(model, filt, max_seqs=256, max_batched_tokens=10000, new_tokens=new_tokens)
+    pipe.new_tokens = 4                                        # warm-up: a few windows, a few tokens, same buffers
+    pipe.transcribe(pcm[:min(warm_windows, max(n, 1))])
+    pipe.new_tokens = new_tokens
+    torch.cuda.synchronize()
+    from glm_asr_stack_b200 import ops
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st}"
+    times = pipeline.PipelineTimes()
+    sampler = ClockSampler(local_rank)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    l0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    tokens = pipe.transcribe(pcm[:n], times=times) if n > 0 else torch.zeros((0, new_tokens), dtype=torch.int32)
+    # the transcripts of all ranks on rank 0, in window order (the only cross-rank traffic of the job)
+    if dist is not None:
+        base, extra = divmod(total_windows, world)
+        padded = torch.zeros((base + 1, new_tokens), dtype=torch.int32, device="cuda")
+        padded[:n] = tokens.cuda(non_blocking=True)
+        parts = [torch.empty_like(padded) for _ in range(world)] if rank == 0 else None
+        dist.gather(padded, parts, dst=0)
+        if rank == 0:
+            tokens = torch.cat([p[:replicas.shard_rows(total_windows, r, world)[1] - replicas.shard_rows(total_windows, r, world)[0]]
+                                for r, p in enumerate(parts)]).cpu()
+    e1.record()
+    torch.cuda.synchronize()
+    wall_s = time.perf_counter() - t0
+    launches = ops.launch_count() - l0
+    clocks = sampler.stop()
+    sec = replicas.max_over_ranks(e0.elapsed_time(e1) * 1e-3, dist, "cuda")
+    wall_s = replicas.max_over_ranks(wall_s, dist, "cuda")
+    audio_s = total_windows * 30.0
+    _st = ops.status()
+    assert _st == 0, f"device status word = {_st}"
+    res = {
+        "metric": "rtfx", "value": audio_s / sec, "unit": "x real time", "seconds": sec, "wall_seconds": wall_s,
+        "windows": total_windows, "windows_this_rank": n, "new_tokens": new_tokens, "scaling": "strong",
+        "workload": f"config4: {total_windows} x 30 s windows of seeded pink noise with random amplitude envelopes, log-mel -> "
+                    f"encoder -> projector -> 394-token prefill -> {new_tokens} greedy tokens (EOS ignored), sharded by window "
+                    f"over {world} GPU(s), max_seqs 256, max_batched_tokens 10000, every FP4 projection W4A4, FP4 lm_head",
+        "phases_rank0_s": {"audio": times.audio, "prefill": times.prefill, "decode": times.decode},
+        "h2d_bytes": n * pipeline.SAMPLES_PER_WINDOW * 4, "d2h_bytes": n * new_tokens * 4,
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if rank == 0:
+        t = tokens.numpy().astype(np.int64)
+        res["tokens_shape"] = list(t.shape)
+        res["tokens_checksum"] = int((t * (np.arange(t.size).reshape(t.shape) % 9973 + 1)).sum() % (1 << 61))
+    return res
+
+
 def contract_line(res, args, world, mode_label):
     """A secondary result dressed as a full benchmark line (for `--workload decode|prefill`)."""
     line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": res["steps"],
@@ -489,6 +625,27 @@ def run_secondary_only(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dist = replicas.init_group("nccl", world, torch.device("cuda", local_rank))
     mix = args.mix if args.mode == "w4a4" else "w4a16"
+    if args.workload in ("encoder", "e2e"):
+        model = workloads.build_asr_model(dec_layers=args.layers if args.workload == "e2e" else 1, enc_layers=args.enc_layers)
+        if args.workload == "encoder":
+            res = measure_encoder(model, args.steps, args.warmup, dist, local_rank, world)
+            res["projection_mix"] = "bf16"
+            line = contract_line(res, args, world, "bf16")
+        else:
+            res = measure_e2e(model, args.windows, args.new_tokens, dist, rank, local_rank, world)
+            line = {"metric": "rtfx", "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": 1, "warmup": 1,
+                    "ms_per_step": res["seconds"] * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                    "dtype": "bf16 encoder, e2m1 x e2m1 decoder", "data": "synthetic",
+                    "config": {"workload": res["workload"], "parallelism": f"dp{world} by window, no collective on the data path"},
+                    "e2e": {"value": res["value"], "unit": res["unit"], "h2d_bytes_per_step": res["h2d_bytes"],
+                            "d2h_bytes_per_step": res["d2h_bytes"]},
+                    "gpu_launches": res["gpu_launches"], "clocks": res["clocks"], "detail": res}
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     model = workloads.build_decoder(layers=args.layers)
     if args.workload == "decode":
         state = workloads.build_decode_state(model.cfg, num_seqs=args.seqs)
@@ -518,9 +675,13 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the decode / prefill measurements of the layer workload's line")
     ap.add_argument("--no-yardstick", action="store_true", help="skip the library FP4 GEMM timing")
     ap.add_argument("--burst-only", action="store_true", help="time exactly --steps steps once (profiler captures)")
-    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "prefill"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "decode", "prefill", "encoder", "e2e"],
                     help="layer = benchmark configuration 1 (default, the headline); decode = configuration 2; "
-                         "prefill = the whole 28-layer batched prefill the config-1 projections belong to")
+                         "prefill = the whole 28-layer batched prefill the config-1 projections belong to; encoder = "
+                         "configuration 3; e2e = configuration 4 (RTFx over --windows windows)")
+    ap.add_argument("--windows", type=int, default=1431, help="windows of the end-to-end workload")
+    ap.add_argument("--new-tokens", type=int, default=256, help="greedy tokens per window of the end-to-end workload")
+    ap.add_argument("--enc-layers", type=int, default=32)
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--layers", type=int, default=28)
     args = ap.parse_args()
@@ -532,7 +693,7 @@ def main():
         run_reference(args, rank)
         return
 
-    if args.workload in ("decode", "prefill"):
+    if args.workload in ("decode", "prefill", "encoder", "e2e"):
         run_secondary_only(args, rank, local_rank, world)
         return
 
@@ -700,6 +861,13 @@ def main():
         for mix in ("all_w4a4", "reference"):
             secondary["prefill" if mix == "all_w4a4" else "prefill_reference_mix"] = measure_prefill(
                 model, st, mix, max(3, args.steps // 4), 3, dist, local_rank, world)
+        del st
+        torch.cuda.empty_cache()
+        # configurations 3 and 4 on the same decoder plus a random-init audio tower
+        workloads.add_audio_tower(model.ws, model.cfg, layers=args.enc_layers)
+        secondary["encoder"] = measure_encoder(model, max(2, args.steps // 5), 2, dist, local_rank, world)
+        if not args.burst_only:
+            secondary["e2e_rtfx"] = measure_e2e(model, args.windows, args.new_tokens, dist, rank, local_rank, world)
         secondary["note"] = ("decode / prefill: every projection block-scaled FP4 (W4A4), the arithmetic the path is built "
                              "for (GLMASR_USE_CUTLASS_NVFP4=1 GLMASR_NVFP4_PAIRS=1); *_reference_mix: what the reference "
                              "computes under GLMASR_USE_CUTLASS_NVFP4=1 and this library's drivers do by default -- q, o, down "

@@ -226,16 +226,17 @@ def decode_step(ws: WeightStore, cfg: CModelConfig, pool: KVPool, bts: BlockTabl
 
 
 def prefill_paged_batched(ws: WeightStore, cfg: CModelConfig, pool: KVPool, bts: BlockTables, hidden: torch.Tensor,
-                          seq_lens, seq_offsets):
+                          seq_lens, seq_offsets, first: int = 0):
     """Call decoder_prefill_paged_batched on hidden [total_tokens, hidden] (updated in place).
     seq_lens / seq_offsets: host sequences of ints, one entry per sequence (rows of sequence s are
-    [seq_offsets[s], seq_offsets[s] + seq_lens[s]))."""
+    [seq_offsets[s], seq_offsets[s] + seq_lens[s])); sequence s uses block table bts[first + s]."""
     lib = _lib.load()
     n = len(seq_lens)
     lens = (ctypes.c_int * n)(*[int(v) for v in seq_lens])
     offs = (ctypes.c_int * n)(*[int(v) for v in seq_offsets])
+    tables = c_void_p(ctypes.addressof(bts.arr) + first * ctypes.sizeof(CBlockTable))
     lib.decoder_prefill_paged_batched(None, ctypes.byref(ws.c), c_void_p(hidden.data_ptr()), hidden.shape[0], n, lens, offs,
-                                      ctypes.byref(pool.c), bts.arr, None, ctypes.byref(cfg))
+                                      ctypes.byref(pool.c), tables, None, ctypes.byref(cfg))
     return hidden
 
 

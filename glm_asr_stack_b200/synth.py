@@ -73,3 +73,25 @@ def default_input_scale(x: torch.Tensor) -> float:
     """Per-tensor activation scale of the W4A4 path: amax(x)/(6*448)."""
     a = float(x.float().abs().max())
     return a / (6.0 * 448.0) if a > 0 else 1.0
+
+
+def mel_filterbank(sr: int = 16000, n_fft: int = 400, n_mels: int = 128, device="cuda") -> torch.Tensor:
+    """A Slaney-style mel filterbank (linear below 1 kHz, logarithmic above, area-normalised triangles) in the form the
+    log-mel front end takes it: float32 [n_fft / 2 + 1, n_mels], i.e. transposed.  Stands in for the filter file the
+    engine loads at start-up (Infer-engine/src/main.c:271-309), which is not part of the reference tree."""
+    import numpy as np
+
+    def hz_to_mel(f):
+        f = np.asarray(f, np.float64)
+        return np.where(f >= 1000.0, 15.0 + np.log(np.maximum(f, 1e-12) / 1000.0) / (np.log(6.4) / 27.0), f / (200.0 / 3.0))
+
+    def mel_to_hz(m):
+        m = np.asarray(m, np.float64)
+        return np.where(m >= 15.0, 1000.0 * np.exp((np.log(6.4) / 27.0) * (m - 15.0)), m * (200.0 / 3.0))
+
+    freqs = np.linspace(0.0, sr / 2.0, n_fft // 2 + 1)
+    pts = mel_to_hz(np.linspace(hz_to_mel(0.0), hz_to_mel(sr / 2.0), n_mels + 2))
+    ramps = pts[:, None] - freqs[None, :]
+    w = np.maximum(0.0, np.minimum(-ramps[:-2] / np.diff(pts)[:-1, None], ramps[2:] / np.diff(pts)[1:, None]))
+    w *= (2.0 / (pts[2:n_mels + 2] - pts[:n_mels]))[:, None]
+    return torch.from_numpy(np.ascontiguousarray(w.T.astype(np.float32))).to(device)

@@ -166,3 +166,10 @@ def encoder_flops(rows_per_window: int, windows: int, hidden=1280, heads=20, hea
     layer = 2.0 * t2 * (4 * hidden * hidden + 2 * hidden * ffn) + 2.0 * 2 * heads * head_dim * t2 * t2
     proj = 2.0 * (t2 // 4) * (4 * hidden * proj_mid + proj_mid * dec_hidden)
     return windows * (conv + layers * layer + proj)
+
+
+def build_asr_model(dec_layers=28, enc_layers=32, device="cuda", **dec_kwargs) -> DecoderModel:
+    """The FP4 decoder of build_decoder plus the bf16 audio tower and projector in the same weight store."""
+    model = build_decoder(layers=dec_layers, device=device, **dec_kwargs)
+    add_audio_tower(model.ws, model.cfg, layers=enc_layers, device=device)
+    return model
