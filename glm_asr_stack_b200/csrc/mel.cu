@@ -186,12 +186,13 @@ bool launch_mel_batched(const float *pcm, long long pcm_stride, const int *d_num
     float *win_max = (float *)workspace_slot(WS_MEL_MAX, (size_t)num_windows * sizeof(float));
     if (cudaMemsetAsync(win_max, 0xFF, (size_t)num_windows * sizeof(float), st) != cudaSuccess) return false;
     const int tiles = (max_frames + kTileFrames - 1) / kTileFrames;
-    launch_chained(mel_power_kernel, dim3(tiles, num_windows), dim3(kMelThreads), sizeof(MelSmem), st, pcm, pcm_stride,
-                   d_num_samples, filters_t, logmel, win_max);
-    launch_chained(mel_normalize_kernel, dim3((max_frames + 31) / 32, num_windows), dim3(32, 8), (size_t)0, st,
-                   (const float *)logmel, (const float *)win_max, d_num_samples, out, out_stride, time_major);
+    // only the two launches' own results decide: an error some earlier call of the process left behind is not ours
+    const cudaError_t e1 = launch_chained(mel_power_kernel, dim3(tiles, num_windows), dim3(kMelThreads), sizeof(MelSmem), st, pcm,
+                                          pcm_stride, d_num_samples, filters_t, logmel, win_max);
+    const cudaError_t e2 = launch_chained(mel_normalize_kernel, dim3((max_frames + 31) / 32, num_windows), dim3(32, 8), (size_t)0, st,
+                                          (const float *)logmel, (const float *)win_max, d_num_samples, out, out_stride, time_major);
     note_launches(2);
-    return cudaGetLastError() == cudaSuccess;
+    return e1 == cudaSuccess && e2 == cudaSuccess;
 }
 
 static int frames_for(int ns) {
@@ -214,9 +215,11 @@ extern "C" void mel_spectrogram(const float *pcm, int num_samples, const float *
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_ns, &num_samples, sizeof(int), cudaMemcpyHostToDevice, st));
     const int n = frames_for(num_samples);
     if (out_frames != nullptr) *out_frames = n;
+    // an empty clip has no samples to point at: nothing is read from pcm then, any valid pointer will do
+    if (pcm == nullptr && num_samples <= 0) pcm = mel_filters_transposed;
     GLMASR_CHECK(launch_mel_batched(pcm, 0, d_ns, 1, n, mel_filters_transposed, (__nv_bfloat16 *)mel_out, 0, 0, st),
-                 "mel_spectrogram: bad arguments");
-    GLMASR_CUDA_CHECK(cudaGetLastError());
+                 "mel_spectrogram: bad arguments (pcm %p, %d samples, filters %p, out %p)", (const void *)pcm, num_samples,
+                 (const void *)mel_filters_transposed, (void *)mel_out);
 }
 
 // Infer-engine/cuda/mel.cu:86-109: the reference frees its FFT plan and buffers; here the buffers are private
