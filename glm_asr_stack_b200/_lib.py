@@ -71,6 +71,8 @@ SIGNATURES = {
     "glmasr_rope_single_token": (None, [P, P, c_int, c_int, c_int]),
     "glmasr_rope_qk_cache": (c_int, [P, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int]),
     "glmasr_rmsnorm_quant": (c_int, [P, P, P, P, c_float, c_float, c_int, c_int]),
+    "glmasr_decode_layer_tail": (c_int, [P, c_int, P, P, P, P, P, P, P, P, P, P, P, c_int]),
+    "glmasr_fp4_linear_quantized": (c_int, [c_int, P, c_int, P, P, P, c_int, c_float, c_int, P, c_int, c_int, P, P, c_float]),
     "glmasr_decoder_forget_weights": (None, []),
     "glmasr_fp4_linear_fused": (c_int, [c_int, P, c_int, P, c_int, POINTER(Fp4Weight), c_int, c_float, P, P,
                                         c_int, P, c_int, c_int]),

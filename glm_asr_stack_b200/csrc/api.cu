@@ -116,6 +116,7 @@ void free_all_private_state() {
     }
     for (auto &kv : g_prepack) cudaFree(kv.second.tiled);
     g_prepack.clear();
+    tail_forget_scales(nullptr);
     clear_tmap_cache();
     if (g_status) cudaFree(g_status);
     g_status = nullptr;
@@ -741,6 +742,28 @@ static int run_fused(const FusedArgs &a) {
 
 size_t tiled_scale_bytes(int rows, int K) { return tiled_sf_bytes(rows, K); }
 
+bool make_u8_tmap_sw128(CUtensorMap *tm, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_inner, uint32_t box_rows) {
+    return make_tmap(tm, base, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, inner, rows, pitch_bytes, box_inner, box_rows, true);
+}
+
+// Event bracket around a launch made outside this file, recorded like the GEMM launches above when
+// glmasr_profile_enable is on (no-ops otherwise).
+static TimedLaunch g_open_bracket;
+void profile_bracket_begin(double flops, double bytes) {
+    if (!g_profile) return;
+    cudaEventCreate(&g_open_bracket.start);
+    cudaEventCreate(&g_open_bracket.stop);
+    g_open_bracket.flops = flops;
+    g_open_bracket.bytes = bytes;
+    cudaEventRecord(g_open_bracket.start, g_stream);
+}
+void profile_bracket_end() {
+    if (!g_profile) return;
+    cudaEventRecord(g_open_bracket.stop, g_stream);
+    g_timed.push_back(g_open_bracket);
+}
+
 // W4A4 GEMM whose activation has already been quantised (e2m1 bytes [M, K/2] + tiled scales) by
 // a producer kernel of this library.  Tensor-core path only; -1 when the shape cannot take it.
 int fp4_linear_w4a4_prequantized(uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
@@ -1017,9 +1040,10 @@ extern "C" int glmasr_fp4_prepack(const uint8_t *w_scales, int N, int K) {
 }
 
 extern "C" void glmasr_fp4_forget(const void *w_scales) {
+    cudaStreamSynchronize(g_stream);
+    tail_forget_scales(w_scales);
     auto it = g_prepack.find(w_scales);
     if (it == g_prepack.end()) return;
-    cudaStreamSynchronize(g_stream);
     cudaFree(it->second.tiled);
     g_prepack.erase(it);
 }

@@ -25,6 +25,7 @@
 
 #include "../../include/glmasr_engine_types.h"
 #include "../../include/glmasr_fp4.h"
+#include "decode_tail.cuh"
 #include "decoder_ops.cuh"
 #include "runtime.cuh"
 
@@ -372,6 +373,157 @@ static int project_mlp(const LayerRef &R, uint16_t *hid, const StepBuffers &B, i
     return 1;
 }
 
+// ---- the layer tail as one co-resident kernel (decode_tail.cu) -----------------------------------------------
+// Taken when every projection of the step runs in W4A4 (GLMASR_USE_CUTLASS_NVFP4=1 GLMASR_NVFP4_PAIRS=1), the batch
+// is at most 256 rows and every shape divides into the kernel's units; GLMASR_DECODE_TAIL=0 keeps the step on one
+// launch per operation.
+static bool g_tail_refused = false;     // a launch was refused by the runtime: do not try again in this process
+static bool tail_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_DECODE_TAIL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1 && !g_tail_refused && pairs_w4a4();
+}
+
+// GLMASR_TAIL_CPM="o,gate_up,down,qkv": CTAs per row tile for the four GEMM phases of the layer tail (0 or
+// missing: the library's own choice, tail_choose_cpm).  For measurements.
+static int tail_cpm_override(int which) {
+    static int v[4] = {-1, 0, 0, 0};
+    if (v[0] < 0) {
+        v[0] = 0;
+        const char *e = getenv("GLMASR_TAIL_CPM");
+        if (e != nullptr) sscanf(e, "%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3]);
+    }
+    return which >= 0 && which < 4 ? v[which] : 0;
+}
+
+static bool tail_fill_gemm(TailGemm &g, const uint8_t *xq, const uint8_t *xsf, int M, int num_m_tiles, int grid,
+                           const ProjRef *const *ps, int n, int epi, uint16_t *out, int ldo, uint8_t *q_out, uint8_t *q_out_sf,
+                           float q_out_scale, int which = -1) {
+    memset(&g, 0, sizeof(g));
+    const int K = ps[0]->K;
+    if (n < 1 || n > kTailMaxSegs || (K % 256) != 0) return false;
+    int units = 0;
+    for (int i = 0; i < n; ++i) {
+        const ProjRef &p = *ps[i];
+        if (p.dtype != GLMASR_DTYPE_UINT8 || p.pre != nullptr || p.scales == nullptr || p.K != K || !(p.input_scale > 0.0f) ||
+            p.input_scale != ps[0]->input_scale || (p.N % 32) != 0 || p.N < 32 * kTailMaxRunUnits)
+            return false;
+        g.seg_units[i] = p.N / 32;
+        g.alpha[i] = p.input_scale * p.global_scale;
+        units += g.seg_units[i];
+        if (!make_u8_tmap_sw128(&g.tm_w[i], p.w, (uint64_t)K / 2, (uint64_t)p.N, (uint64_t)K / 2, 128, 32)) return false;
+    }
+    if (epi == TAIL_EPI_SILU_QUANT && n == 2) units = g.seg_units[0];
+    int cpm = tail_choose_cpm(units, K, epi == TAIL_EPI_SILU_QUANT, grid, num_m_tiles);
+    const int forced = tail_cpm_override(which);
+    if (forced > 0 && forced <= grid / num_m_tiles && (units + forced - 1) / forced <= kTailMaxRunUnits) cpm = forced;
+    if (cpm <= 0) return false;
+    g.cpm = cpm;
+    for (int i = 0, first = 0; i < n; ++i) {
+        const bool silu = epi == TAIL_EPI_SILU_QUANT;
+        g.sfb[i] = tail_tiled_scales(ps[i]->scales, ps[i]->N, K, cpm, silu ? g.seg_units[0] : units, silu ? 0 : first, current_stream());
+        if (g.sfb[i] == nullptr) return false;
+        first += g.seg_units[i];
+    }
+    if (epi == TAIL_EPI_SILU_QUANT) {
+        if (n != 2 || ps[0]->N != ps[1]->N || (ps[0]->N % 64) != 0 || q_out == nullptr || q_out_sf == nullptr || !(q_out_scale > 0.0f))
+            return false;
+        units = g.seg_units[0];
+        g.q_packed = q_out;
+        g.q_sf = q_out_sf;
+        g.q_inv_in = 1.0f / q_out_scale;
+        g.q_ld = ps[0]->N / 2;
+        g.q_sf_chunks = ps[0]->N / 64;
+    }
+    if (!make_u8_tmap_sw128(&g.tm_a, xq, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, 128, 128)) return false;
+    g.sfa = xsf;
+    g.num_segs = n;
+    g.K = K;
+    g.epi = epi;
+    g.out = (__nv_bfloat16 *)out;
+    g.ldo = ldo;
+    return true;
+}
+
+// o + residual, norm + quantiser, gate|up + SiLU-gate + quantiser, down + residual of layer R and, when `next`
+// is given, that layer's input norm + quantiser and its q|k|v projection, in one launch.  aq / asf: the quantised
+// attention output (K = H).  False (nothing launched) when a shape or weight kind is not covered.
+static bool launch_layer_tail(const LayerRef &R, const LayerRef *next, uint16_t *hid, const StepBuffers &B, uint8_t *gq,
+                              uint8_t *gsf, unsigned int *counter, unsigned int &base, int M, int H, int KV, int F,
+                              cudaStream_t st, int max_phases = 0) {
+    const int grid = tail_grid_size();
+    if (grid <= 0 || M > 256 || (H % 64) != 0 || H > 4096) return false;
+    const int num_m_tiles = (M + 127) / 128;
+    static TailParams P;       // 3 KB: not on the stack of every call
+    P.num_phases = 0;
+    auto add = [&](int kind, int index) {
+        P.kind[P.num_phases] = kind;
+        P.index[P.num_phases] = index;
+        ++P.num_phases;
+    };
+    auto fill_norm = [&](TailNorm &nm, const uint16_t *w, float input_scale) {
+        nm.x = (const __nv_bfloat16 *)hid;
+        nm.weight = (const __nv_bfloat16 *)w;
+        nm.q_packed = B.nq;
+        nm.q_sf = B.nsf;
+        nm.eps = 1e-5f;
+        nm.inv_in = 1.0f / input_scale;
+        nm.dim = H;
+    };
+    const ProjRef *o_p[1] = {&R.o}, *gu_p[2] = {&R.gate, &R.up}, *down_p[1] = {&R.down};
+    if (R.o.K != H || R.o.N != H || R.gate.K != H || R.gate.N != F || R.down.K != F || R.down.N != H) return false;
+    if (!tail_fill_gemm(P.g[0], B.aq, B.asf, M, num_m_tiles, grid, o_p, 1, TAIL_EPI_RESIDUAL, hid, H, nullptr, nullptr, 0.0f, 0)) return false;
+    if (!tail_fill_gemm(P.g[1], B.nq, B.nsf, M, num_m_tiles, grid, gu_p, 2, TAIL_EPI_SILU_QUANT, nullptr, 0, gq, gsf, R.down.input_scale, 1))
+        return false;
+    if (!tail_fill_gemm(P.g[2], gq, gsf, M, num_m_tiles, grid, down_p, 1, TAIL_EPI_RESIDUAL, hid, H, nullptr, nullptr, 0.0f, 2)) return false;
+    fill_norm(P.n[0], R.norm2, R.gate.input_scale);
+    add(TAIL_GEMM, 0);
+    add(TAIL_NORM, 0);
+    add(TAIL_GEMM, 1);
+    add(TAIL_GEMM, 2);
+    double flops = 2.0 * M * ((double)H * H + 2.0 * F * H + (double)H * F);
+    double wbytes = 0.5625 * ((double)H * H + 2.0 * F * H + (double)H * F);
+    if (next != nullptr) {
+        const ProjRef *qkv_p[3] = {&next->q, &next->k, &next->v};
+        if (next->q.K != H || next->q.N != H || next->k.N != KV || next->v.N != KV) return false;
+        if (!tail_fill_gemm(P.g[3], B.nq, B.nsf, M, num_m_tiles, grid, qkv_p, 3, TAIL_EPI_STORE, B.qkv, H + 2 * KV, nullptr, nullptr, 0.0f, 3))
+            return false;
+        fill_norm(P.n[1], next->norm1, next->q.input_scale);
+        add(TAIL_NORM, 1);
+        add(TAIL_GEMM, 3);
+        flops += 2.0 * M * (double)(H + 2 * KV) * H;
+        wbytes += 0.5625 * (double)(H + 2 * KV) * H;
+    }
+    if (max_phases > 0 && max_phases < P.num_phases) P.num_phases = max_phases;
+    P.M = M;
+    P.num_m_tiles = num_m_tiles;
+    P.counter = counter;
+    P.base = base;
+    P.status = device_status_word();
+#ifdef GLMASR_EXPERIMENTS
+    {
+        const char *e = getenv("GLMASR_TAIL_DEBUG");
+        P.debug = e ? atoi(e) : 0;
+    }
+#endif
+    profile_bracket_begin(flops, wbytes);
+    const cudaError_t e = launch_decode_tail(P, st);
+    profile_bracket_end();
+    if (e != cudaSuccess) {
+        // e.g. a device that cannot keep the whole grid co-resident: nothing ran, the caller takes the
+        // one-launch-per-operation path from here on
+        (void)cudaGetLastError();
+        g_tail_refused = true;
+        return false;
+    }
+    base += (unsigned int)grid;
+    note_launches(1);
+    return true;
+}
+
 }  // namespace glmasr
 
 using namespace glmasr;
@@ -383,6 +535,7 @@ enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
     // 30, 31: api.cu (split-K).  Quantised hand-overs of the decode step share the layer path's slots 24, 25
     // (both are temporaries of one call).
     WS_D_AQ = 24, WS_D_ASF = 25,
+    WS_D_GQ = 48, WS_D_GSF = 49, WS_D_COUNTER = 50,   // layer tail: quantised SiLU-gate output, grid counter
 };
 
 // ============================================================================================
@@ -452,6 +605,112 @@ extern "C" int glmasr_rmsnorm_quant(uint8_t *packed_out, uint8_t *tiled_scale_ou
         return -1;
     note_launches(1);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// W4A4 linear on an activation that is already quantised (e2m1 bytes [M, K/2] + 128x4-tiled scales, as
+// glmasr_rmsnorm_quant or a quantising epilogue writes them).  resident = 0: the library's regular GEMM kernels;
+// resident = 1: one GEMM phase of the co-resident layer-tail kernel (M <= 256; GLMASR_EPI_RESIDUAL adds in place,
+// residual == out; GLMASR_EPI_SILU_GATE writes only the quantised product q_out / q_out_sf).  Both give the same bytes.
+extern "C" int glmasr_fp4_linear_quantized(int resident, uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
+                                           const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
+                                           const uint16_t *residual, int M, int K, uint8_t *q_out, uint8_t *q_out_sf,
+                                           float q_out_input_scale) {
+    if (xq == nullptr || xq_sf == nullptr || weights == nullptr || num_weights < 1 || num_weights > 3 || M <= 0) return -1;
+    if (!resident)
+        return fp4_linear_w4a4_prequantized(out, ldo, xq, xq_sf, weights, num_weights, input_scale, epilogue, residual, M, K, q_out,
+                                            q_out_sf, q_out_input_scale);
+    const int grid = tail_grid_size();
+    if (grid <= 0 || M > 256) return -1;
+    ProjRef refs[3];
+    const ProjRef *ps[3];
+    for (int i = 0; i < num_weights; ++i) {
+        refs[i].dtype = GLMASR_DTYPE_UINT8;
+        refs[i].w = weights[i].w_packed;
+        refs[i].scales = weights[i].w_scales;
+        refs[i].global_scale = weights[i].w_global_scale;
+        refs[i].input_scale = input_scale;
+        refs[i].N = weights[i].N;
+        refs[i].K = K;
+        ps[i] = &refs[i];
+    }
+    int epi = TAIL_EPI_STORE;
+    if (epilogue == GLMASR_EPI_RESIDUAL) {
+        if (residual != out || out == nullptr) return -1;
+        epi = TAIL_EPI_RESIDUAL;
+    } else if (epilogue == GLMASR_EPI_SILU_GATE) {
+        if (q_out == nullptr || q_out_sf == nullptr) return -1;
+        epi = TAIL_EPI_SILU_QUANT;
+    } else if (out == nullptr) {
+        return -1;
+    }
+    static TailParams P;
+    const int num_m_tiles = (M + 127) / 128;
+    if (!tail_fill_gemm(P.g[0], xq, xq_sf, M, num_m_tiles, grid, ps, num_weights, epi, out, ldo, q_out, q_out_sf, q_out_input_scale))
+        return -1;
+    unsigned int *counter = (unsigned int *)workspace_slot(WS_D_COUNTER, kTailCounterBytes);
+    if (cudaMemsetAsync(counter, 0, kTailCounterBytes, current_stream()) != cudaSuccess) return -1;
+    P.kind[0] = TAIL_GEMM;
+    P.index[0] = 0;
+    P.num_phases = 1;
+    P.M = M;
+    P.num_m_tiles = num_m_tiles;
+    P.counter = counter;
+    P.base = 0;
+    P.status = device_status_word();
+    if (launch_decode_tail(P, current_stream()) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    note_launches(1);
+    return 0;
+}
+
+static ProjRef proj_of(const glmasr_fp4_weight &w, float input_scale, int K) {
+    ProjRef r;
+    r.dtype = GLMASR_DTYPE_UINT8;
+    r.w = w.w_packed;
+    r.scales = w.w_scales;
+    r.global_scale = w.w_global_scale;
+    r.input_scale = input_scale;
+    r.N = w.N;
+    r.K = K;
+    return r;
+}
+
+// One launch of the co-resident layer-tail kernel on the caller's buffers (the decode driver above does the same
+// on its private workspace): o + residual | norm + quantiser | gate|up + SiLU-gate + quantiser | down + residual
+// and, with `next`, | norm + quantiser | q|k|v of the following layer.
+extern "C" int glmasr_decode_layer_tail(uint16_t *hidden, int M, const uint8_t *attn_q, const uint8_t *attn_sf,
+                                        const glmasr_layer_weights *lw, const uint16_t *post_attention_norm,
+                                        const glmasr_layer_weights *next, const uint16_t *next_input_norm, uint16_t *next_qkv,
+                                        uint8_t *norm_q, uint8_t *norm_sf, uint8_t *act_q, uint8_t *act_sf, int max_phases) {
+    if (hidden == nullptr || attn_q == nullptr || attn_sf == nullptr || lw == nullptr || post_attention_norm == nullptr ||
+        norm_q == nullptr || norm_sf == nullptr || act_q == nullptr || act_sf == nullptr || M <= 0 || M > 256)
+        return -1;
+    if (next != nullptr && (next_input_norm == nullptr || next_qkv == nullptr)) return -1;
+    const int H = lw->hidden, F = lw->ffn;
+    LayerRef R, N;
+    R.norm2 = post_attention_norm;
+    R.o = proj_of(lw->o, lw->in_o, H);
+    R.gate = proj_of(lw->gate, lw->in_gate_up, H);
+    R.up = proj_of(lw->up, lw->in_gate_up, H);
+    R.down = proj_of(lw->down, lw->in_down, F);
+    int KV = 0;
+    if (next != nullptr) {
+        N.norm1 = next_input_norm;
+        N.q = proj_of(next->q, next->in_qkv, H);
+        N.k = proj_of(next->k, next->in_qkv, H);
+        N.v = proj_of(next->v, next->in_qkv, H);
+        KV = next->k.N;
+    }
+    StepBuffers B = {nullptr, next_qkv, nullptr, nullptr, norm_q, norm_sf, const_cast<uint8_t *>(attn_q), const_cast<uint8_t *>(attn_sf)};
+    unsigned int *counter = (unsigned int *)workspace_slot(WS_D_COUNTER, kTailCounterBytes);
+    if (cudaMemsetAsync(counter, 0, kTailCounterBytes, current_stream()) != cudaSuccess) return -1;
+    unsigned int base = 0;
+    return launch_layer_tail(R, next != nullptr ? &N : nullptr, hidden, B, act_q, act_sf, counter, base, M, H, KV, F,
+                             current_stream(), max_phases)
+               ? 0
+               : -1;
 }
 
 // ============================================================================================
@@ -532,13 +791,26 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     launch_gather_block_tables(d_bt, pool->d_block_tables, d_rows, M, pool->max_blocks_per_seq, st);
     // the vectors above are pageable host memory: the async copies have completed staging on return
 
+    // the layer tail (o .. next layer's q|k|v) as one co-resident launch where it applies
+    const bool tail = tail_enabled() && M <= 256;
+    uint8_t *gq = nullptr, *gsf = nullptr;
+    unsigned int *tail_counter = nullptr, tail_base = 0;
+    if (tail) {
+        gq = (uint8_t *)workspace_slot(WS_D_GQ, (size_t)M * F / 2);
+        gsf = (uint8_t *)workspace_slot(WS_D_GSF, tiled_scale_bytes(M, F));
+        tail_counter = (unsigned int *)workspace_slot(WS_D_COUNTER, kTailCounterBytes);
+        GLMASR_CUDA_CHECK(cudaMemsetAsync(tail_counter, 0, kTailCounterBytes, st));
+    }
+    bool have_qkv = false;      // the previous layer's tail already projected this layer's q | k | v
+
     for (int l = 0; l < L; ++l) {
         const LayerRef &R = refs.layers[l];
         __nv_bfloat16 *k_base = (__nv_bfloat16 *)pool->k_cache + (size_t)l * pool->layer_stride;
         __nv_bfloat16 *v_base = (__nv_bfloat16 *)pool->v_cache + (size_t)l * pool->layer_stride;
 
         // q | k | v into one [M, H + 2 KV] buffer
-        int glue = project_qkv(R, hid, B, M, H, KV, st);
+        int glue = have_qkv ? 0 : project_qkv(R, hid, B, M, H, KV, st);
+        have_qkv = false;
         // RoPE on q and k in place (position = cached length), KV write, attention over cached + 1 tokens
         if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_seq_lens, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
             glue += 1;
@@ -556,6 +828,12 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
             ok = launch_paged_decode_attention_mma((__nv_bfloat16 *)att, H, (const __nv_bfloat16 *)qkv, NQKV, k_base, v_base, d_bt,
                                                    d_total, M, QH, KVH, HD, pool->block_size, pool->max_blocks_per_seq, st, aq,
                                                    asf, R.o.input_scale);
+        if (ok && tail &&
+            launch_layer_tail(R, l + 1 < L ? &refs.layers[l + 1] : nullptr, hid, B, gq, gsf, tail_counter, tail_base, M, H, KV, F, st)) {
+            have_qkv = l + 1 < L;
+            note_launches(glue + 1);
+            continue;
+        }
         if (ok) {
             single_proj_prequantized(hid, H, aq, asf, R.o, M, hid);
         } else {

@@ -19,6 +19,7 @@ enum : int {
     ST_TIMEOUT_SPLITK = 5,     // split-K reduction waited too long for partial results
     ST_TIMEOUT_ATTENTION = 6,  // a role of the prefill attention kernel waited too long
     ST_BAD_LAYOUT = 7,         // shared-memory base or workspace extent not as the kernel needs it
+    ST_TIMEOUT_GRID = 8,       // a grid-wide phase hand-over of the decode layer-tail kernel did not complete
 };
 
 // ~1.5 s at 1.3-1.9 GHz: far beyond any legitimate wait, short enough not to look like a hang.

@@ -20,13 +20,21 @@ void *workspace_slot(int slot, size_t bytes);
 // Slots owned outside api.cu / decoder_step.cu (those two number their own, 0..31).
 enum : int { WS_ATTN_VT = 32, WS_ATTN_VT_COL = 33, WS_ATTN_DEBUG = 34 };
 void free_all_private_state();
+void tail_forget_scales(const void *w_scales);   // decode_tail.cu: per-CTA re-tiled weight scales (nullptr: all)
 void encoder_forget_all();         // encoder.cu: per-store weight table, re-packed convolution weights, rotary table
 void note_launches(int n);          // launch accounting for kernels started outside api.cu
-size_t tiled_scale_bytes(int rows, int K);
+size_t tiled_scale_bytes(int rows, int K);   // bytes of the 128x4-tiled scale layout for [rows, K]
 // Cached TMA descriptor of a row-major bf16 matrix [rows, inner] (row pitch in bytes, a multiple of 16; base
 // 16-byte aligned) cut into box_rows x box_inner boxes with the 128-byte swizzle.  False if it cannot be encoded.
 bool make_bf16_tmap_sw128(CUtensorMap *tm, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
-                          uint32_t box_inner, uint32_t box_rows);   // bytes of the 128x4-tiled scale layout for [rows, K]
+                          uint32_t box_inner, uint32_t box_rows);
+
+// Same for a byte matrix (packed e2m1 operands): inner = bytes per row.
+bool make_u8_tmap_sw128(CUtensorMap *tm, const void *base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_inner, uint32_t box_rows);
+// CUDA-event bracket around launches made outside api.cu; recorded only while profiling is enabled.
+void profile_bracket_begin(double flops, double bytes);
+void profile_bracket_end();
 
 // Ask once for the largest shared-memory carve-out for `kernel`.  The GEMM kernels need almost all
 // of an SM's shared memory; a small kernel launched between two of them with the default

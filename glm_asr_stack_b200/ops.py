@@ -336,6 +336,60 @@ def fp4_linear_fused(mode: int, x: torch.Tensor, weights: Sequence[Fp4Tensor], e
     return out
 
 
+def fp4_linear_quantized(xq: torch.Tensor, xq_sf: torch.Tensor, weights: Sequence[Fp4Tensor], input_scale: float,
+                         epilogue: int = EPI_STORE, out: Optional[torch.Tensor] = None, resident: bool = False,
+                         q_out_input_scale: float = 0.0, M: Optional[int] = None):
+    """W4A4 linear on an activation that is already quantised (glmasr_fp4_linear_quantized): xq e2m1 bytes
+    [M, K/2] and its 128x4-tiled scales as rmsnorm_quant returns them.  EPI_RESIDUAL adds into `out` in place.
+    EPI_SILU_GATE with q_out_input_scale > 0 returns (packed [M, N/2] u8, tiled scales u8) for a following W4A4
+    GEMM instead of a bf16 tensor.  resident=True runs it as one phase of the co-resident layer-tail kernel."""
+    lib = _lib.load()
+    K = weights[0].K
+    M = xq.shape[0] if M is None else M
+    for w in weights:
+        _track_scales(w.w_scales)
+    arr = (Fp4Weight * len(weights))(*[w.c_struct() for w in weights])
+    n_out = weights[0].N if epilogue == EPI_SILU_GATE else sum(w.N for w in weights)
+    q_out = q_sf = None
+    if epilogue == EPI_SILU_GATE and q_out_input_scale > 0.0:
+        q_out = torch.empty((M, n_out // 2), dtype=torch.uint8, device=xq.device)
+        q_sf = torch.zeros(((M + 127) // 128) * (n_out // 64) * 512, dtype=torch.uint8, device=xq.device)
+    if out is None and not (q_out is not None and resident):
+        out = torch.empty((M, n_out), dtype=torch.bfloat16, device=xq.device)
+    rc = lib.glmasr_fp4_linear_quantized(1 if resident else 0, _ptr(out), out.stride(0) if out is not None else n_out,
+                                         _ptr(xq), _ptr(xq_sf), arr, len(weights), float(input_scale), epilogue,
+                                         _ptr(out) if epilogue == EPI_RESIDUAL else None, M, K, _ptr(q_out), _ptr(q_sf),
+                                         float(q_out_input_scale))
+    if rc != 0:
+        raise ValueError("glmasr_fp4_linear_quantized rejected the arguments")
+    return (q_out, q_sf) if q_out is not None else out
+
+
+def decode_layer_tail(hidden: torch.Tensor, attn_q: torch.Tensor, attn_sf: torch.Tensor, lw: "LayerWeights",
+                      post_attention_norm: torch.Tensor, next_lw: Optional["LayerWeights"] = None,
+                      next_input_norm: Optional[torch.Tensor] = None, max_phases: int = 0):
+    """o + residual | norm + quantiser | gate|up + SiLU-gate + quantiser | down + residual [| norm + quantiser |
+    q|k|v of the next layer] as one co-resident launch (glmasr_decode_layer_tail), in place on `hidden`.
+    Returns (next_qkv or None, norm_q, norm_sf, act_q, act_sf)."""
+    M, H = hidden.shape
+    F = lw.ffn
+    dev = hidden.device
+    norm_q = torch.zeros((M, H // 2), dtype=torch.uint8, device=dev)
+    norm_sf = torch.zeros(((M + 127) // 128) * (H // 64) * 512, dtype=torch.uint8, device=dev)
+    act_q = torch.zeros((M, F // 2), dtype=torch.uint8, device=dev)
+    act_sf = torch.zeros(((M + 127) // 128) * (F // 64) * 512, dtype=torch.uint8, device=dev)
+    qkv = None
+    if next_lw is not None:
+        qkv = torch.zeros((M, next_lw.q.N + next_lw.k.N + next_lw.v.N), dtype=torch.bfloat16, device=dev)
+    rc = _lib.load().glmasr_decode_layer_tail(_ptr(hidden), M, _ptr(attn_q), _ptr(attn_sf), ctypes.byref(lw),
+                                              _ptr(post_attention_norm), ctypes.byref(next_lw) if next_lw is not None else None,
+                                              _ptr(next_input_norm), _ptr(qkv), _ptr(norm_q), _ptr(norm_sf), _ptr(act_q),
+                                              _ptr(act_sf), int(max_phases))
+    if rc != 0:
+        raise ValueError("glmasr_decode_layer_tail rejected the arguments")
+    return qkv, norm_q, norm_sf, act_q, act_sf
+
+
 def make_layer_weights(q, k, v, o, gate, up, down, hidden: int, ffn: int) -> LayerWeights:
     for w in (q, k, v, o, gate, up, down):
         _track_scales(w.w_scales)

@@ -279,6 +279,23 @@ int glmasr_fp4_linear_fused(int mode, uint16_t *out, int ldo, const uint16_t *x,
                             const uint16_t *pre_quant_scale, uint16_t *prequant_scratch,
                             int epilogue, const uint16_t *residual, int M, int K);
 
+/* W4A4 linear on an activation that is ALREADY quantised: xq = e2m1 bytes [M, K/2], xq_sf = its e4m3 block
+ * scales in the 128x4-tiled layout, exactly as glmasr_rmsnorm_quant (or a quantising epilogue of this library)
+ * writes them; up to three same-input weight tensors side by side as in glmasr_fp4_linear_fused.  No reference
+ * counterpart: the reference re-quantises the bf16 activation inside every nvfp4_linear call
+ * (Infer-engine/cuda/nvfp4_cutlass.cu:155-166).
+ *   resident = 0  the library's regular GEMM kernels.
+ *   resident = 1  one phase of the co-resident layer-tail kernel the decode step uses at M <= 256 (every SM takes a
+ *                 share of the output columns).  GLMASR_EPI_RESIDUAL then adds in place (residual == out) and
+ *                 GLMASR_EPI_SILU_GATE writes only the quantised product (q_out / q_out_sf, required).
+ * q_out / q_out_sf / q_out_input_scale (GLMASR_EPI_SILU_GATE): the SiLU-gate product quantised for a following
+ * W4A4 GEMM, e2m1 bytes [M, N/2] + tiled scales.  Both settings produce the same bytes.  Returns 0, or -1 when the
+ * shape is not covered (K % 256, N % 32, M > 256 for resident = 1, missing scales). */
+int glmasr_fp4_linear_quantized(int resident, uint16_t *out, int ldo, const uint8_t *xq, const uint8_t *xq_sf,
+                                const glmasr_fp4_weight *weights, int num_weights, float input_scale, int epilogue,
+                                const uint16_t *residual, int M, int K, uint8_t *q_out, uint8_t *q_out_sf,
+                                float q_out_input_scale);
+
 /* One-time re-tiling of a weight's e4m3 scales into the 128x4 tile order the tensor core
  * reads (what Infer-engine/cuda/nvfp4_cutlass.cu:184-188 redoes on every call; the slot of
  * the declared-but-undefined swizzle_weight_scale, Infer-engine/cuda/kernels.cuh:24).
@@ -313,6 +330,22 @@ int glmasr_fp4_layer_proj(int mode, uint16_t *hidden_out, const uint16_t *hidden
  * copies out and synchronises -- the end-to-end call the benchmark times. */
 int glmasr_fp4_layer_proj_host(int mode, uint16_t *hidden_out_host, const uint16_t *hidden_in_host,
                                const glmasr_layer_weights *lw, int M);
+
+/* The part of a decoder layer that follows attention, at decode batch sizes (M <= 256), as ONE launch of a
+ * co-resident kernel (one CTA per SM, phases separated by a grid-wide counter; no reference counterpart -- the
+ * reference runs these as ~10 launches, Infer-engine/cuda/decoder.cu:2050-2160):
+ *     o projection + residual | RMSNorm + activation quantiser | gate|up + SiLU-gate + quantiser | down + residual
+ * and, when `next` is given, | RMSNorm + quantiser | q|k|v of the FOLLOWING layer into next_qkv [M, H + 2 KV].
+ * Every projection is W4A4.  hidden [M, H] is updated in place.  attn_q / attn_sf: the attention output already
+ * quantised with input scale lw->in_o (e2m1 bytes [M, H/2] + 128x4-tiled scales).  norm_q / norm_sf ([M, H/2],
+ * tiled scales for K = H) and act_q / act_sf ([M, F/2], K = F) are scratch the phases hand over through; after the
+ * call they hold the last quantised norm output and the quantised SiLU-gate product.  max_phases > 0 stops the
+ * program after that many phases (for tests).  Same bytes as glmasr_fp4_linear_quantized / glmasr_rmsnorm_quant
+ * run one after the other.  Returns 0, or -1 when a shape is not covered (then nothing was launched). */
+int glmasr_decode_layer_tail(uint16_t *hidden, int M, const uint8_t *attn_q, const uint8_t *attn_sf,
+                             const glmasr_layer_weights *lw, const uint16_t *post_attention_norm,
+                             const glmasr_layer_weights *next, const uint16_t *next_input_norm, uint16_t *next_qkv,
+                             uint8_t *norm_q, uint8_t *norm_sf, uint8_t *act_q, uint8_t *act_sf, int max_phases);
 
 /* W4A4 linear (nvfp4_linear arithmetic, no pre_quant_scale, no bias) for callers that must not
  * allocate device memory.  No counterpart in the reference.  The engine sizes its paged-KV pool
