@@ -36,9 +36,9 @@
 // (Infer-engine/cuda/kernels.cu:252-295) and the activation quantiser of nvfp4_cutlass.cu:35-87 behind it, i.e. the
 // same bytes as rmsnorm_quant_kernel.
 //
-// Data written by one phase and read by the next crosses CTAs through global memory (L2): writers fence
-// (generic -> async proxy, then gpu scope) before the CTA's arrival, readers acquire the counter, fence again and
-// only then issue TMA loads; generic reads of such data use ld.global.cg.
+// Data written by one phase and read by the next crosses CTAs through global memory (L2): the writing CTA's warps
+// meet at a barrier, one thread fences at gpu scope and adds the CTA's arrival; readers acquire the counter,
+// fence generic -> async proxy and only then issue TMA loads; generic reads of such data use ld.global.cg.
 #include <cuda_bf16.h>
 #include <cuda_fp4.h>
 #include <stdint.h>
@@ -56,6 +56,21 @@ namespace glmasr {
 
 namespace {
 
+// cycle accounting of experiment builds: per CTA, phase and role, where the time goes
+#ifdef GLMASR_EXPERIMENTS
+#define TAIL_T0() long long _t0 = clock64()
+#define TAIL_ACC(ph, slot)                                                                                      \
+    do {                                                                                                        \
+        const long long _t1 = clock64();                                                                        \
+        if (P.dbg != nullptr && lane == 0)                                                                      \
+            P.dbg[((size_t)blockIdx.x * kTailMaxPhases + (ph)) * 16 + (slot)] += (unsigned long long)(_t1 - _t0); \
+        _t0 = _t1;                                                                                              \
+    } while (0)
+#else
+#define TAIL_T0() do { } while (0)
+#define TAIL_ACC(ph, slot) do { } while (0)
+#endif
+
 constexpr int MAX_STAGES = 8;                            // mbarrier pairs of the operand ring
 constexpr int A_BYTES = 128 * 128;                       // 128 rows x 256 K-elements, packed
 constexpr int SF_TILE = 2048;                            // scales of 128 rows x 256 K-elements (4 chunks of 512 B)
@@ -63,8 +78,9 @@ constexpr int SF_CHUNK = 512;
 constexpr int UNIT_BYTES = 32 * 128;                     // 32 weight rows x 256 K-elements
 constexpr int OFF_ASF = A_BYTES;
 constexpr int OFF_W = OFF_ASF + SF_TILE;                 // weight units of the runs, then one scale tile per run
-constexpr int BAR_BYTES = 1024;
+constexpr int BAR_BYTES = 2048;                          // mbarriers, a few status words, the quantiser's look-up table
 constexpr int NORM_ROW_BYTES = 8192;                     // one row of up to 4096 bf16
+constexpr int OFF_OS_TABLE = 1024;                       // 128 floats in the second half of the barrier block
 constexpr int OFF_TILES = BAR_BYTES;
 constexpr int POOL_BYTES = 208 * 1024;                   // operand ring: cut into stages phase by phase (Geo below)
 constexpr int OFF_NORM = OFF_TILES + POOL_BYTES;
@@ -246,6 +262,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
         tmem_alloc(smem_u32((const void *)tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
+    // the quantising epilogue's second division (inv_in / scale, one of 127 values) looked up: one table per launch
+    // (a program has at most one SiLU-gate phase)
+    float *os_table = reinterpret_cast<float *>(smem_gen + OFF_OS_TABLE);
+    if (warp >= 2) {
+        for (int ph = 0; ph < P.num_phases; ++ph)
+            if (P.kind[ph] == TAIL_GEMM && P.g[P.index[ph]].epi == TAIL_EPI_SILU_QUANT)
+                fill_os_table(os_table, P.g[P.index[ph]].q_inv_in, (int)threadIdx.x - 64, EPI_WARPS * 32);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -271,26 +295,44 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
             const int nkb = g.K >> 8;
             const int sf_k_chunks = g.K >> 6;
             const int cta_in_tile = (int)blockIdx.x - w.m_tile * g.cpm;
+            // per-run state in scalars: the two loops below are the producer's hot path, and indexing the run arrays
+            // with a run-time index would put them in local memory
+            const bool two = w.nruns > 1;
+            const int units0 = w.r[0].units, units1 = two ? w.r[1].units : 0;
+            const int row00 = w.r[0].unit0 * 32, row01 = two ? w.r[1].unit0 * 32 : 0;
+            const CUtensorMap *tm0 = &g.tm_w[w.r[0].seg], *tm1 = &g.tm_w[two ? w.r[1].seg : 0];
+            const uint8_t *sf0 = g.sfb[w.r[0].seg] + (size_t)cta_in_tile * sf_k_chunks * SF_CHUNK;
+            const uint8_t *sf1 = g.sfb[two ? w.r[1].seg : 0] + (size_t)cta_in_tile * sf_k_chunks * SF_CHUNK;
+            const int off_w0 = G.off_w[0], off_w1 = G.off_w[1], off_sf0 = G.off_sf[0], off_sf1 = G.off_sf[1];
             auto issue_weights = [&](int s, int kb) {
                 const uint32_t sb = pool + (uint32_t)(s * G.stage_bytes);
-                for (int r = 0; r < w.nruns; ++r) {
-                    for (int u = 0; u < w.r[r].units; ++u)
-                        tma_load_2d(sb + G.off_w[r] + u * UNIT_BYTES, &g.tm_w[w.r[r].seg], full_bar(s), kb * 128,
-                                    (w.r[r].unit0 + u) * 32);
-                    bulk_load_1d(sb + G.off_sf[r],
-                                 g.sfb[w.r[r].seg] + ((size_t)cta_in_tile * sf_k_chunks + (size_t)kb * 4) * SF_CHUNK, SF_TILE, full_bar(s));
+                const uint32_t fb = full_bar(s);
+#pragma unroll
+                for (int u = 0; u < kTailMaxRunUnits; ++u)
+                    if (u < units0) tma_load_2d(sb + off_w0 + u * UNIT_BYTES, tm0, fb, kb * 128, row00 + u * 32);
+                bulk_load_1d(sb + off_sf0, sf0 + (size_t)kb * SF_TILE, SF_TILE, fb);
+                if (two) {
+#pragma unroll
+                    for (int u = 0; u < kTailMaxRunUnits; ++u)
+                        if (u < units1) tma_load_2d(sb + off_w1 + u * UNIT_BYTES, tm1, fb, kb * 128, row01 + u * 32);
+                    bulk_load_1d(sb + off_sf1, sf1 + (size_t)kb * SF_TILE, SF_TILE, fb);
                 }
             };
+            const CUtensorMap *tma = &g.tm_a;
+            const uint8_t *sfa = g.sfa + (size_t)w.m_tile * sf_k_chunks * SF_CHUNK;
+            const int a_row = w.m_tile * 128;
             auto issue_acts = [&](int s, int kb) {
                 const uint32_t sb = pool + (uint32_t)(s * G.stage_bytes);
-                tma_load_2d(sb, &g.tm_a, full_bar(s), kb * 128, w.m_tile * 128);
-                bulk_load_1d(sb + OFF_ASF, g.sfa + ((size_t)w.m_tile * sf_k_chunks + (size_t)kb * 4) * SF_CHUNK, SF_TILE, full_bar(s));
+                tma_load_2d(sb, tma, full_bar(s), kb * 128, a_row);
+                bulk_load_1d(sb + OFF_ASF, sfa + (size_t)kb * SF_TILE, SF_TILE, full_bar(s));
             };
+            TAIL_T0();
             // the stages of this phase lie differently in the pool: everything the previous phase put there must
             // have been consumed first (the wait is the one that would precede the next fill of each stage)
             for (int s = 0; ok && s < prev_ns; ++s)
                 if (!mbar_wait_warp(empty_bar(s), ((fills >> s) & 1u) ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) ok = false;
             if (!ok) break;
+            TAIL_ACC(ph, 0);     // producer: drain
             prev_ns = G.ns;
             // weights of the first ring stages go out before the hand-over of the previous phase is awaited
             const int pre = nkb < G.ns ? nkb : G.ns;
@@ -301,6 +343,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                 }
                 fills ^= 1u << i;
             }
+            TAIL_ACC(ph, 1);     // producer: early weight issue
             if (!waited) {
                 pdl_wait();
                 waited = true;
@@ -312,11 +355,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                 if (!got) { ok = false; break; }
                 fence_proxy_async_all();
             }
+            TAIL_ACC(ph, 2);     // producer: hand-over wait
             for (int i = 0; i < pre; ++i)
                 if (leader) issue_acts(i, i);
+            TAIL_ACC(ph, 3);     // producer: first activation issues
             for (int kb = pre; kb < nkb; ++kb) {
                 const int s = kb % G.ns;
                 if (!mbar_wait_warp(empty_bar(s), ((fills >> s) & 1u) ^ 1u, abort_word, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                TAIL_ACC(ph, 4); // producer: waiting for a free stage
                 if (GLMASR_EXP(P, 1)) {                 // experiment: no memory traffic after the first ring round
                     if (leader) mbar_arrive(full_bar(s));
                 } else if (leader) {
@@ -325,6 +371,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                     if (!no_w) issue_weights(s, kb);
                     if (!no_a) issue_acts(s, kb);
                 }
+                TAIL_ACC(ph, 5); // producer: issuing a stage
                 fills ^= 1u << s;
             }
         }
@@ -341,43 +388,56 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
             if (w.nruns == 0) continue;
             const Geo G = stage_geometry(w);
             const int nkb = g.K >> 8;
-            uint32_t idesc[2] = {0, 0};
-            for (int r = 0; r < w.nruns; ++r) idesc[r] = idesc_nvfp4(128, 32 * w.r[r].units);
+            const bool two = w.nruns > 1;
+            const uint32_t idesc0 = idesc_nvfp4(128, 32 * w.r[0].units);
+            const uint32_t idesc1 = idesc_nvfp4(128, 32 * (two ? w.r[1].units : 1));
+            // descriptors of stage 0; a stage adds its byte offset to the start-address field (no carry: every
+            // shared-memory address is below 2^18)
+            const uint64_t adesc_base = smem_desc_sw128(pool);
+            const uint64_t b0desc_base = smem_desc_sw128(pool + (uint32_t)G.off_w[0]);
+            const uint64_t b1desc_base = smem_desc_sw128(pool + (uint32_t)G.off_w[1]);
+            const uint64_t sfa_base = smem_desc_sf_chunk(pool + OFF_ASF);
+            const uint64_t sfb0_base = smem_desc_sf_chunk(pool + (uint32_t)G.off_sf[0]);
+            const uint64_t sfb1_base = smem_desc_sf_chunk(pool + (uint32_t)G.off_sf[1]);
+            const uint32_t stage_step = (uint32_t)G.stage_bytes >> 4;
+            TAIL_T0();
             if (!mbar_wait_warp(tempty_bar, (acc_it & 1u) ^ 1u, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
             tc_fence_after();
+            TAIL_ACC(ph, 6);     // MMA: accumulator free
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % G.ns;
                 if (!mbar_wait_warp(full_bar(s), (uses >> s) & 1u, abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
+                if (kb == 0) TAIL_ACC(ph, 7); else TAIL_ACC(ph, 8);   // MMA: waiting for the first / a later stage
                 uses ^= 1u << s;
                 tc_fence_after();
-                const uint32_t sb = pool + (uint32_t)(s * G.stage_bytes);
+                const uint64_t soff = (uint64_t)((uint32_t)s * stage_step);
                 const uint32_t set = tmem_base + SF_BASE + (it & 1u) * SF_SET_COLS;
                 if (leader) {
-                    const uint64_t sfa_desc = smem_desc_sf_chunk(sb + OFF_ASF);
                     if (!(GLMASR_EXP(P, 4) && kb > 0)) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_cp_32x128b_warpx4(set + 4 * c, sfa_desc + (uint64_t)((c * SF_CHUNK) >> 4));
-                    }
-                    for (int r = 0; r < w.nruns && !(GLMASR_EXP(P, 4) && kb > 0); ++r) {
-                        const uint64_t sfb_desc = smem_desc_sf_chunk(sb + G.off_sf[r]);
+                        for (int c = 0; c < 4; ++c) tmem_cp_32x128b_warpx4(set + 4 * c, sfa_base + soff + (uint64_t)((c * SF_CHUNK) >> 4));
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
-                            tmem_cp_32x128b_warpx4(set + 16 + 16 * r + 4 * c, sfb_desc + (uint64_t)((c * SF_CHUNK) >> 4));
+                            tmem_cp_32x128b_warpx4(set + 16 + 4 * c, sfb0_base + soff + (uint64_t)((c * SF_CHUNK) >> 4));
+                        if (two) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                tmem_cp_32x128b_warpx4(set + 32 + 4 * c, sfb1_base + soff + (uint64_t)((c * SF_CHUNK) >> 4));
+                        }
                     }
-                    const uint64_t adesc0 = smem_desc_sw128(sb);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         if (GLMASR_EXP(P, 2) && k > 0) break;    // experiment: a quarter of the MMAs
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                        for (int r = 0; r < w.nruns; ++r) {
-                            const uint64_t bdesc0 = smem_desc_sw128(sb + G.off_w[r]);
-                            umma_nvfp4(tmem_base + (uint32_t)(r * ACC_RUN1), adesc0 + (uint64_t)((k * 32) >> 4),
-                                       bdesc0 + (uint64_t)((k * 32) >> 4), idesc[r], accumulate, set + 4 * k,
-                                       set + 16 + 16 * r + 4 * k);
-                        }
+                        const uint64_t koff = soff + (uint64_t)((k * 32) >> 4);
+                        umma_nvfp4(tmem_base, adesc_base + koff, b0desc_base + koff, idesc0, accumulate, set + 4 * k, set + 16 + 4 * k);
+                        if (two)
+                            umma_nvfp4(tmem_base + ACC_RUN1, adesc_base + koff, b1desc_base + koff, idesc1, accumulate, set + 4 * k,
+                                       set + 32 + 4 * k);
                     }
                     umma_commit(empty_bar(s));
                 }
+                TAIL_ACC(ph, 9); // MMA: issuing a stage
                 ++it;
             }
             if (!ok) break;
@@ -394,14 +454,34 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
         bool alive = true;
         pdl_wait();
         for (int ph = 0; ph < P.num_phases; ++ph) {
+#ifdef GLMASR_EXPERIMENTS
+            long long _t0 = clock64();
+#endif
             if (P.kind[ph] == TAIL_GEMM) {
                 const TailGemm &g = P.g[P.index[ph]];
                 const Work w = resolve_work(g, P.num_m_tiles, (int)blockIdx.x);
                 if (w.nruns != 0 && alive) {
-                    bool ok = mbar_wait(tfull_bar, acc_it & 1u, abort_word, ST_TIMEOUT_EPILOGUE);
-                    // data of earlier phases read below (the residual) was written by other CTAs: acquire their arrival
-                    if (ok && ph > 0 && g.epi == TAIL_EPI_RESIDUAL && lane == 0) ok = grid_wait(phase_counter(ph - 1), phase_target, abort_word, P.status);
+                    bool ok = true;
+                    // a residual written earlier in this launch by OTHER threads: acquire their arrival first
+                    if (g.epi == TAIL_EPI_RESIDUAL && ph > 0 && !g.res_local) {
+                        if (lane == 0) ok = grid_wait(phase_counter(ph - 1), phase_target, abort_word, P.status);
+                        ok = __all_sync(0xFFFFFFFFu, ok);
+                    }
+                    // the residual can be fetched while the accumulator is still being computed: the chunk this warp
+                    // will finish first, 64 bytes of the thread's row
+                    uint4 res_pre[4];
+                    const bool pre_res = ok && g.epi == TAIL_EPI_RESIDUAL && (w.m_tile * 128 + quad * 32 + lane) < P.M && half < w.r[0].units + (w.nruns > 1 ? w.r[1].units : 0);
+                    if (pre_res) {
+                        const int ci0 = half;                                  // first chunk of this warp
+                        const int r0 = ci0 < w.r[0].units ? 0 : 1;
+                        const int j0 = r0 == 0 ? ci0 : ci0 - w.r[0].units;
+                        const __nv_bfloat16 *src = g.out + (size_t)(w.m_tile * 128 + quad * 32 + lane) * g.ldo + w.r[r0].col0 + 32 * j0;
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) res_pre[q4] = ldcg_u4(src + 8 * q4);
+                    }
+                    ok = ok && mbar_wait(tfull_bar, acc_it & 1u, abort_word, ST_TIMEOUT_EPILOGUE);
                     ok = __all_sync(0xFFFFFFFFu, ok);
+                    if (ew == 0) TAIL_ACC(ph, 10);   // epilogue: waiting for the accumulator
                     if (ok) {
                         tc_fence_after();
                         const int row = w.m_tile * 128 + quad * 32 + lane;
@@ -424,7 +504,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                                         const float uu = bf16_round(__uint_as_float(ru[16 * b + i]) * au);
                                         blk[i] = bf16_round(silu_gate(gg, uu));
                                     }
-                                    sf |= quantize_block16(blk, g.q_inv_in, q[2 * b], q[2 * b + 1]) << (8 * b);
+                                    sf |= quantize_block16_lut(blk, g.q_inv_in, os_table, q[2 * b], q[2 * b + 1]) << (8 * b);
                                 }
                                 if (row_ok) {
                                     const int col = w.r[0].col0 + 32 * j;
@@ -451,7 +531,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                                     if (g.epi == TAIL_EPI_RESIDUAL) {
 #pragma unroll
                                         for (int q4 = 0; q4 < 4; ++q4) {
-                                            const uint4 rv = ldcg_u4(dst + 8 * q4);
+                                            const uint4 rv = (pre_res && ci == half) ? res_pre[q4] : ldcg_u4(dst + 8 * q4);
                                             const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
                                             for (int i = 0; i < 4; ++i) {
@@ -490,17 +570,25 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                 // one thread of the group acquires the previous phase's hand-over; the group barrier passes it on
                 if (ok && ph > 0 && gtid == 0) ok = grid_wait(phase_counter(ph - 1), phase_target, abort_word, P.status);
                 ok = named_bar_and(2 + half, 128, ok);
+                if (ew == 0) TAIL_ACC(ph, 10);       // norm: waiting for the hand-over
                 if (ok && has_row) {
                     const uint4 *xr = reinterpret_cast<const uint4 *>(nm.x + (size_t)row * nm.dim);
                     for (int i = gtid; i < nm.dim / 8; i += 128) reinterpret_cast<uint4 *>(rowbuf)[i] = __ldcg(xr + i);
                 }
                 ok = named_bar_and(2 + half, 128, ok);
                 if (ok && has_row && gtid < 32) {
-                    const __nv_bfloat16 *rs = reinterpret_cast<const __nv_bfloat16 *>(rowbuf);
+                    // lane i adds x[i], x[i + 32], ... in that order (the reference's summation order); dim % 64 == 0
+                    const uint16_t *rs = reinterpret_cast<const uint16_t *>(rowbuf) + gtid;
                     float sum_sq = 0.0f;
-                    for (int i = gtid; i < nm.dim; i += 32) {
-                        const float v = __bfloat162float(rs[i]);
-                        sum_sq += v * v;
+                    for (int t = 0; t < nm.dim / 32; t += 8) {
+                        uint32_t h[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) h[u] = rs[(t + u) * 32];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const float v = __uint_as_float(h[u] << 16);
+                            sum_sq += v * v;
+                        }
                     }
                     for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
                     if (gtid == 0) rms_slot[half] = sqrtf(sum_sq / nm.dim + nm.eps);
@@ -508,6 +596,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                 ok = named_bar_and(2 + half, 128, ok);
                 if (ok && has_row) {
                     const float rms = rms_slot[half];
+                    const ExactRowDivider by_rms(rms);       // same quotients as x / rms, without sixteen IEEE divisions
                     const int sf_chunks = nm.dim / 64;
                     const int rem = row & 127;
                     for (int b = gtid; b < nm.dim / 16; b += 128) {
@@ -519,8 +608,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                             const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                const float a0 = __fdiv_rn(__uint_as_float(xs[j] << 16), rms) * __uint_as_float(ws[j] << 16);
-                                const float a1 = __fdiv_rn(__uint_as_float(xs[j] & 0xFFFF0000u), rms) * __uint_as_float(ws[j] & 0xFFFF0000u);
+                                const float a0 = by_rms(__uint_as_float(xs[j] << 16)) * __uint_as_float(ws[j] << 16);
+                                const float a1 = by_rms(__uint_as_float(xs[j] & 0xFFFF0000u)) * __uint_as_float(ws[j] & 0xFFFF0000u);
                                 v[8 * h + 2 * j] = bf16_round(a0);
                                 v[8 * h + 2 * j + 1] = bf16_round(a1);
                             }
@@ -534,13 +623,18 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                 if (!ok) alive = false;
             }
             // ---- end of the phase: everything this CTA wrote becomes visible, then the CTA arrives ----
-            fence_proxy_async_all();
+            if (ew == 0) TAIL_ACC(ph, 11);           // epilogue / norm: the work itself
             alive = named_bar_and(1, EPI_WARPS * 32, alive);
             if (!alive) break;          // the verdict is the same in all epilogue threads
+            if (ew == 0) TAIL_ACC(ph, 12);           // fence + CTA barrier
             if (ew == 0 && lane == 0) {
                 __threadfence();
                 atomicAdd(phase_counter(ph), 1u);
             }
+            if (ew == 0) TAIL_ACC(ph, 13);           // gpu-scope fence + arrival
+#ifdef GLMASR_EXPERIMENTS
+            if (ew == 0 && lane == 0 && P.dbg != nullptr) P.dbg[((size_t)blockIdx.x * kTailMaxPhases + ph) * 16 + 15] = (unsigned long long)clock64();
+#endif
         }
     }
 

@@ -37,6 +37,8 @@ struct alignas(64) TailGemm {
     int K;                               // multiple of 256
     int cpm;                             // CTAs per row tile that share this phase's columns (<= grid / num_m_tiles)
     int epi;
+    int res_local;                       // TAIL_EPI_RESIDUAL: out was last written by an earlier launch, or earlier in this one
+                                         // by the very threads that now read it (same columns, same cpm): no acquire needed
     int ldo;                             // row pitch of out, elements
     __nv_bfloat16 *out;
     uint8_t *q_packed;                   // TAIL_EPI_SILU_QUANT: bytes [M, q_ld]
@@ -69,6 +71,7 @@ struct alignas(64) TailParams {
     unsigned int base;                   // their value when this launch starts (every launch adds the grid size to each)
     int *status;
     int debug;                           // experiment builds only (timing experiments that leave work out)
+    unsigned long long *dbg;             // experiment builds only: cycle counters [grid][kTailMaxPhases][16]
 };
 
 // CTAs per row tile that share a phase of `units` 32-column units per row tile (one of the two tensors for

@@ -282,32 +282,6 @@ __global__ void rmsnorm_quant_kernel(uint8_t *__restrict__ q_packed, uint8_t *__
     }
 }
 
-// x / d for many x and one divisor d, each quotient rounded exactly as the IEEE division the reference's
-// rmsnorm performs (x[i] / rms).  The correctly rounded reciprocal is taken once per divisor, kept as
-// r_hi + r_lo, and every quotient then costs four multiply-adds: q0 = x * (r_hi + r_lo) lies within one
-// unit in the last place of x / d, the residual e = x - q0 * d is exact in a fused multiply-add, and
-// q0 + e * r_hi rounds to the correctly rounded quotient (Markstein's theorem; it needs r_hi = RN(1 / d)
-// and a divisor whose significand is not all ones).  Operands outside the range where every intermediate
-// is a normal number, zeros, infinities and NaNs take the ordinary division.
-struct ExactRowDivider {
-    float d, r_hi, r_lo, fast_min;
-    __device__ __forceinline__ explicit ExactRowDivider(float divisor) : d(divisor) {
-        r_hi = __frcp_rn(d);
-        r_lo = fmaf(-d, r_hi, 1.0f) * r_hi;
-        const bool ok = d > 9.094947e-13f && d < 1.0995116e12f &&                  // 2^-40 < d < 2^40
-                        (__float_as_uint(d) & 0x007FFFFFu) != 0x007FFFFFu;
-        fast_min = ok ? 8.6736174e-19f : __int_as_float(0x7FC00000);               // 2^-60, or NaN: never fast
-    }
-    __device__ __forceinline__ float operator()(float x) const {
-        if (fabsf(x) >= fast_min) {
-            const float q0 = fmaf(x, r_hi, x * r_lo);
-            const float e = fmaf(-q0, d, x);
-            return fmaf(e, r_hi, q0);
-        }
-        return __fdiv_rn(x, d);
-    }
-};
-
 // Same results, one WARP per row, for batches of thousands of rows (prefill), where the CTA-per-row
 // kernel above is a chain of load -> one-warp reduction -> quantise with little to overlap it.  A warp
 // reads its row once, coalesced, into a private strip of shared memory (128-byte lines 144 bytes apart,

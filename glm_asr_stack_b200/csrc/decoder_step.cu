@@ -377,6 +377,7 @@ static int project_mlp(const LayerRef &R, uint16_t *hid, const StepBuffers &B, i
 // Taken when every projection of the step runs in W4A4 (GLMASR_USE_CUTLASS_NVFP4=1 GLMASR_NVFP4_PAIRS=1), the batch
 // is at most 256 rows and every shape divides into the kernel's units; GLMASR_DECODE_TAIL=0 keeps the step on one
 // launch per operation.
+static constexpr int kTailDebugSlot = 51;   // workspace slot of the layer tail's cycle counters (experiment builds)
 static bool g_tail_refused = false;     // a launch was refused by the runtime: do not try again in this process
 static bool tail_enabled() {
     static int v = -1;
@@ -479,6 +480,10 @@ static bool launch_layer_tail(const LayerRef &R, const LayerRef *next, uint16_t 
     if (!tail_fill_gemm(P.g[1], B.nq, B.nsf, M, num_m_tiles, grid, gu_p, 2, TAIL_EPI_SILU_QUANT, nullptr, 0, gq, gsf, R.down.input_scale, 1))
         return false;
     if (!tail_fill_gemm(P.g[2], gq, gsf, M, num_m_tiles, grid, down_p, 1, TAIL_EPI_RESIDUAL, hid, H, nullptr, nullptr, 0.0f, 2)) return false;
+    // o and down write the same columns of the hidden state; with the same split every thread of the down phase
+    // adds to what it wrote itself in the o phase
+    P.g[0].res_local = 1;
+    P.g[2].res_local = (P.g[0].cpm == P.g[2].cpm && R.o.N == R.down.N) ? 1 : 0;
     fill_norm(P.n[0], R.norm2, R.gate.input_scale);
     add(TAIL_GEMM, 0);
     add(TAIL_NORM, 0);
@@ -507,6 +512,7 @@ static bool launch_layer_tail(const LayerRef &R, const LayerRef *next, uint16_t 
     {
         const char *e = getenv("GLMASR_TAIL_DEBUG");
         P.debug = e ? atoi(e) : 0;
+        P.dbg = (unsigned long long *)workspace_slot(kTailDebugSlot, (size_t)grid * kTailMaxPhases * 16 * 8);
     }
 #endif
     profile_bracket_begin(flops, wbytes);
@@ -536,6 +542,7 @@ enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
     // (both are temporaries of one call).
     WS_D_AQ = 24, WS_D_ASF = 25,
     WS_D_GQ = 48, WS_D_GSF = 49, WS_D_COUNTER = 50,   // layer tail: quantised SiLU-gate output, grid counter
+    // 51: the layer tail's cycle counters (experiment builds)
 };
 
 // ============================================================================================
@@ -712,6 +719,19 @@ extern "C" int glmasr_decode_layer_tail(uint16_t *hidden, int M, const uint8_t *
                ? 0
                : -1;
 }
+
+#ifdef GLMASR_EXPERIMENTS
+// experiment builds only: read (and clear) the layer-tail kernel's cycle counters [CTAs][phases][16]
+extern "C" int glmasr_tail_debug_read(unsigned long long *host_out, int clear) {
+    const int grid = tail_grid_size();
+    const size_t bytes = (size_t)grid * kTailMaxPhases * 16 * 8;
+    unsigned long long *d = (unsigned long long *)workspace_slot(kTailDebugSlot, bytes);
+    cudaStreamSynchronize(current_stream());
+    if (host_out != nullptr && cudaMemcpy(host_out, d, bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (clear) cudaMemset(d, 0, bytes);
+    return grid;
+}
+#endif
 
 // ============================================================================================
 // decoder_decode_step_batched
