@@ -45,22 +45,38 @@ enum : int { WS_E_NORM = 38, WS_E_QKV = 39, WS_E_FFN = 40, WS_E_POS = 41, WS_E_M
 // LayerNorm (reference: layernorm_kernel, Infer-engine/cuda/kernels.cu:299-345): one warp per row; lane i
 // adds x[i], x[i + 32], ... in that order, a shuffle-down tree, lane 0's total broadcast; the variance is a
 // second pass over (x - mean)^2; out = bf16(((x - mean) * inv_std) * w + b).  Eight rows per CTA.  out may
-// alias x (a lane reads all of its elements before it writes any).
+// alias x (a warp has its whole row in shared memory before it writes any of it).
 // --------------------------------------------------------------------------------------------
 template <int MAXE>
 __global__ void __launch_bounds__(256) layernorm_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfloat16 *weight,
                                                         const __nv_bfloat16 *bias, float eps, int rows, int dim) {
+    // Rows move between global and shared memory in 16-byte pieces (dim % 8 == 0, 16-byte aligned rows); the
+    // arithmetic reads the warp's row from shared memory in the reference's lane-strided order.  weight and bias
+    // are staged once per CTA.
+    extern __shared__ __align__(16) uint8_t ln_smem[];
+    __nv_bfloat16 *w_s = reinterpret_cast<__nv_bfloat16 *>(ln_smem);
+    __nv_bfloat16 *b_s = w_s + dim;
     pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, row = blockIdx.x * 8 + wib;
+    __nv_bfloat16 *row_s = b_s + dim + (size_t)wib * dim;
+    const int vecs = dim >> 3;
+    for (int i = threadIdx.x; i < vecs; i += 256) {
+        reinterpret_cast<uint4 *>(w_s)[i] = reinterpret_cast<const uint4 *>(weight)[i];
+        reinterpret_cast<uint4 *>(b_s)[i] = bias != nullptr ? reinterpret_cast<const uint4 *>(bias)[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
     pdl_wait();
-    const int lane = threadIdx.x & 31, row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row < rows) {
+        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * dim);
+        for (int i = lane; i < vecs; i += 32) reinterpret_cast<uint4 *>(row_s)[i] = xr[i];
+    }
+    __syncthreads();
     if (row >= rows) return;
-    const __nv_bfloat16 *xr = x + (size_t)row * dim;
     float v[MAXE];
     float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < MAXE; ++j) {
         const int i = lane + 32 * j;
-        v[j] = i < dim ? __bfloat162float(xr[i]) : 0.0f;
+        v[j] = i < dim ? __bfloat162float(row_s[i]) : 0.0f;
         if (i < dim) sum += v[j];
     }
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xFFFFFFFFu, sum, off);
@@ -75,16 +91,17 @@ __global__ void __launch_bounds__(256) layernorm_kernel(__nv_bfloat16 *out, cons
     for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
     sum_sq = __shfl_sync(0xFFFFFFFFu, sum_sq, 0);
     const float inv_std = 1.0f / sqrtf(sum_sq / dim + eps);
-    __nv_bfloat16 *orow = out + (size_t)row * dim;
 #pragma unroll
     for (int j = 0; j < MAXE; ++j) {
         const int i = lane + 32 * j;
         if (i < dim) {
             const float val = (v[j] - mean) * inv_std;
-            const float b = bias != nullptr ? __bfloat162float(bias[i]) : 0.0f;
-            orow[i] = __float2bfloat16(val * __bfloat162float(weight[i]) + b);
+            row_s[i] = __float2bfloat16(val * __bfloat162float(w_s[i]) + __bfloat162float(b_s[i]));
         }
     }
+    __syncwarp();
+    uint4 *orow = reinterpret_cast<uint4 *>(out + (size_t)row * dim);
+    for (int i = lane; i < vecs; i += 32) orow[i] = reinterpret_cast<const uint4 *>(row_s)[i];
 }
 
 // any width (three passes over global memory), same arithmetic; in place is fine here too: a lane reads and writes
@@ -122,8 +139,9 @@ void launch_layernorm(__nv_bfloat16 *out, const __nv_bfloat16 *x, const __nv_bfl
                       float eps, int rows, int dim, cudaStream_t st) {
     if (rows <= 0) return;
     const dim3 grid((rows + 7) / 8);
-    if (dim <= 32 * 40)       // the row fits the registers of a warp (the encoder's 1280)
-        launch_chained(layernorm_kernel<40>, grid, dim3(256), (size_t)0, st, out, x, weight, bias, eps, rows, dim);
+    const bool vec = (dim % 8) == 0 && (((uintptr_t)out | (uintptr_t)x | (uintptr_t)weight | (uintptr_t)bias) & 15) == 0;
+    if (dim <= 32 * 40 && vec)       // the row fits the registers of a warp (the encoder's 1280)
+        launch_chained(layernorm_kernel<40>, grid, dim3(256), (size_t)dim * 2 * 10, st, out, x, weight, bias, eps, rows, dim);
     else
         launch_chained(layernorm_generic_kernel, grid, dim3(256), (size_t)0, st, out, x, weight, bias, eps, rows, dim);
     note_launches(1);

@@ -40,20 +40,28 @@ namespace {
 
 constexpr int QT = 128;                       // queries per CTA
 constexpr int KT = 64;                        // keys per step
-constexpr int Q_BYTES = 2 * 128 * 128;        // two boxes of 128 rows x 128 bytes (dims 0-63, 64-127)
-constexpr int K_BYTES = 2 * KT * 128;         // two boxes of 64 rows x 128 bytes
-constexpr int V_BYTES = 128 * 128;            // V^T: 128 dims x 64 keys
 constexpr int P_BYTES = 128 * 128;            // P: 128 queries x 64 keys, bf16
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + Q_BYTES;
-constexpr int OFF_V = OFF_K + 2 * K_BYTES;
-constexpr int OFF_P = OFF_V + 2 * V_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;      // 112 KB of tiles, then barriers
-constexpr int OFF_OS_TABLE = OFF_BAR + 256;  // 128 floats: the quantiser's second division, one entry per scale byte
-constexpr int SMEM_BYTES = OFF_OS_TABLE + 512;
-constexpr int TMEM_COLS = 256;                // S0 [0,64), S1 [64,128), O [128,256)
+constexpr int TMEM_COLS = 256;                // S0 [0,64), S1 [64,128), O [128,128 + head_dim)
 constexpr int THREADS = 192;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units
+
+// Shared-memory layout for one head_dim (64: the audio encoder, 128: the decoder).  Rows of Q and K are cut
+// into 64-dim boxes of 128 bytes (the widest box the 128-byte swizzle takes).
+template <int HD>
+struct Geo {
+    static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+    static constexpr int NB = HD / 64;                 // 64-dim boxes per Q / K row
+    static constexpr int Q_BYTES = NB * 128 * 128;
+    static constexpr int K_BYTES = NB * KT * 128;
+    static constexpr int V_BYTES = HD * 128;           // V^T: head_dim dims x 64 keys
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = OFF_Q + Q_BYTES;
+    static constexpr int OFF_V = OFF_K + 2 * K_BYTES;
+    static constexpr int OFF_P = OFF_V + 2 * V_BYTES;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;    // tiles (112 KB / 64 KB), then barriers
+    static constexpr int OFF_OS_TABLE = OFF_BAR + 256; // 128 floats: the quantiser's second division, one entry per scale byte
+    static constexpr int SMEM_BYTES = OFF_OS_TABLE + 512;
+};
 
 enum : int { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_SFREE = 11, B_PFULL = 13,
              B_PVDONE = 14, B_QEMPTY = 15, B_OFREE = 16 };
@@ -97,14 +105,15 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&b);
 }
 
-// vt[(h * 128 + d) * vt_cols + col(seq) + t] = v[(off(seq) + t) * ldv + h * 128 + d], zero for t >= len
+// vt[(h * HD + d) * vt_cols + col(seq) + t] = v[(off(seq) + t) * ldv + h * HD + d], zero for t >= len
 // up to the next multiple of 64.  grid = (64-token tiles, kv heads, sequences).
+template <int HD>
 __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restrict__ vt, int vt_cols,
                                                          const __nv_bfloat16 *__restrict__ v, int ldv,
                                                          const int *__restrict__ seq_offsets,
                                                          const int *__restrict__ seq_lens, int *__restrict__ vt_col,
                                                          int *status) {
-    __shared__ uint32_t tile[64][65];          // [token][dim pair], odd pitch
+    __shared__ uint32_t tile[64][HD / 2 + 1];  // [token][dim pair], odd pitch
     __shared__ int s_col;
     pdl_launch_dependents();
     pdl_wait();
@@ -119,12 +128,13 @@ __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restr
             if (blockIdx.x == 0 && blockIdx.y == 0) vt_col[seq] = col;
         }
     }
+    constexpr int CH = HD / 8;                  // 16-byte chunks (8 dims) per token row
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 64 * CH / 256; ++i) {
         const int idx = threadIdx.x + i * 256;
-        const int r = idx >> 4, c = idx & 15;          // token row, 16-byte chunk (8 dims)
+        const int r = idx / CH, c = idx % CH;          // token row, 16-byte chunk (8 dims)
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (t0 + r < len) val = *reinterpret_cast<const uint4 *>(v + (size_t)(off + t0 + r) * ldv + (size_t)h * 128 + c * 8);
+        if (t0 + r < len) val = *reinterpret_cast<const uint4 *>(v + (size_t)(off + t0 + r) * ldv + (size_t)h * HD + c * 8);
         tile[r][c * 4 + 0] = val.x;
         tile[r][c * 4 + 1] = val.y;
         tile[r][c * 4 + 2] = val.z;
@@ -137,7 +147,7 @@ __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restr
         return;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < HD * 8 / 256; ++i) {
         const int idx = threadIdx.x + i * 256;
         const int d = idx >> 3, c = idx & 7;           // dim row, 16-byte chunk (8 tokens)
         uint32_t w[4];
@@ -148,7 +158,7 @@ __global__ void __launch_bounds__(256) transpose_v_kernel(__nv_bfloat16 *__restr
             const uint32_t hi = (d & 1) ? (b >> 16) : (b & 0xFFFFu);
             w[e] = lo | (hi << 16);
         }
-        *reinterpret_cast<uint4 *>(vt + (size_t)(h * 128 + d) * vt_cols + col + t0 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4 *>(vt + (size_t)(h * HD + d) * vt_cols + col + t0 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -173,7 +183,11 @@ __device__ __forceinline__ bool decode_item(const AttnParams &p, int item, ItemI
     return true;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(const __grid_constant__ AttnParams p) {
+    using G = Geo<HD>;
+    constexpr int OFF_Q = G::OFF_Q, OFF_K = G::OFF_K, OFF_V = G::OFF_V, OFF_P = G::OFF_P, OFF_BAR = G::OFF_BAR;
+    constexpr int OFF_OS_TABLE = G::OFF_OS_TABLE, Q_BYTES = G::Q_BYTES, K_BYTES = G::K_BYTES, V_BYTES = G::V_BYTES;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     pdl_launch_dependents();
@@ -231,8 +245,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
             if (!mbar_wait_warp(bar(B_QEMPTY), (qi & 1u) ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) break;
             if (leader) {
                 mbar_expect_tx(bar(B_QFULL), Q_BYTES);
-                tma_load_2d(sbase + OFF_Q, &p.tm_q, bar(B_QFULL), it.head * 128, it.off + it.q0);
-                tma_load_2d(sbase + OFF_Q + Q_BYTES / 2, &p.tm_q, bar(B_QFULL), it.head * 128 + 64, it.off + it.q0);
+#pragma unroll
+                for (int b = 0; b < G::NB; ++b)
+                    tma_load_2d(sbase + OFF_Q + b * (Q_BYTES / G::NB), &p.tm_q, bar(B_QFULL), it.head * HD + 64 * b, it.off + it.q0);
             }
             ++qi;
             for (int j = 0; j < it.n; ++j, ++kv) {
@@ -242,13 +257,14 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                 if (leader) {
                     const uint32_t dst = sbase + OFF_K + (uint32_t)s * K_BYTES;
                     mbar_expect_tx(bar(B_KFULL + s), K_BYTES);
-                    tma_load_2d(dst, &p.tm_k, bar(B_KFULL + s), kv_head * 128, it.off + j * KT);
-                    tma_load_2d(dst + K_BYTES / 2, &p.tm_k, bar(B_KFULL + s), kv_head * 128 + 64, it.off + j * KT);
+#pragma unroll
+                    for (int b = 0; b < G::NB; ++b)
+                        tma_load_2d(dst + b * (K_BYTES / G::NB), &p.tm_k, bar(B_KFULL + s), kv_head * HD + 64 * b, it.off + j * KT);
                 }
                 if (!mbar_wait_warp(bar(B_VEMPTY + s), ph ^ 1u, abort_word, ST_TIMEOUT_ATTENTION)) { ok = false; break; }
                 if (leader) {
                     mbar_expect_tx(bar(B_VFULL + s), V_BYTES);
-                    tma_load_2d(sbase + OFF_V + (uint32_t)s * V_BYTES, &p.tm_vt, bar(B_VFULL + s), col + j * KT, kv_head * 128);
+                    tma_load_2d(sbase + OFF_V + (uint32_t)s * V_BYTES, &p.tm_vt, bar(B_VFULL + s), col + j * KT, kv_head * HD);
                 }
             }
         }
@@ -256,7 +272,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
         // ================================ MMA issuer ==================================
         const bool leader = elect_one();
         constexpr uint32_t idesc_s = idesc_bf16(128, KT);
-        constexpr uint32_t idesc_o = idesc_bf16(128, 128);
+        constexpr uint32_t idesc_o = idesc_bf16(128, HD);
         const uint32_t t_o = tmem_base + 128;
         uint32_t ks = 0, kp = 0, qi = 0;        // S products issued, P V products issued, items started
         bool ok = true;
@@ -275,9 +291,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                     if (leader) {
                         const uint32_t kaddr = sbase + OFF_K + (uint32_t)s * K_BYTES;
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const uint64_t adesc = smem_desc_sw128(sbase + OFF_Q + (uint32_t)(k >> 2) * (Q_BYTES / 2)) + (uint64_t)(((k & 3) * 32) >> 4);
-                            const uint64_t bdesc = smem_desc_sw128(kaddr + (uint32_t)(k >> 2) * (K_BYTES / 2)) + (uint64_t)(((k & 3) * 32) >> 4);
+                        for (int k = 0; k < HD / 16; ++k) {
+                            const uint64_t adesc = smem_desc_sw128(sbase + OFF_Q + (uint32_t)(k >> 2) * (Q_BYTES / G::NB)) + (uint64_t)(((k & 3) * 32) >> 4);
+                            const uint64_t bdesc = smem_desc_sw128(kaddr + (uint32_t)(k >> 2) * (K_BYTES / G::NB)) + (uint64_t)(((k & 3) * 32) >> 4);
                             umma_bf16(tmem_base + (uint32_t)s * KT, adesc, bdesc, idesc_s, k > 0 ? 1u : 0u);
                         }
                         umma_commit(bar(B_KEMPTY + s));
@@ -389,7 +405,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                     tc_fence_after();
                     if (rescale) {
 #pragma unroll 1
-                        for (int ch = 0; ch < 4; ++ch) {
+                        for (int ch = 0; ch < HD / 32; ++ch) {
                             uint32_t o[32];
                             tmem_ld_x32(t_row + 128 + (uint32_t)ch * 32, o);
                             tmem_ld_wait();
@@ -425,15 +441,15 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
             // cover whole 128-byte (bf16) or 64-byte (quantised) row segments instead of 16 bytes per row.
             const int wrow0 = quad * 32;                               // first tile row of this warp
             const uint32_t stage = sbase + OFF_P + (uint32_t)wrow0 * 128u;
-            if (p.q_packed == nullptr) {
+            if (HD != 128 || p.q_packed == nullptr) {
 #pragma unroll 1
-                for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < HD / 64; ++half) {
 #pragma unroll
                     for (int c2 = 0; c2 < 2; ++c2) {
                         uint32_t o[32];
                         tmem_ld_x32(t_row + 128 + (uint32_t)(half * 64 + c2 * 32), o);
                         tmem_ld_wait();
-                        if (half == 1 && c2 == 1) {                    // the accumulator may be overwritten by the next item
+                        if (half == HD / 64 - 1 && c2 == 1) {           // the accumulator may be overwritten by the next item
                             tc_fence_before();
                             mbar_arrive(bar(B_OFREE));
                         }
@@ -457,12 +473,12 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(src));
                             const int rg = it.q0 + wrow0 + r;
                             if (rg < len)
-                                *reinterpret_cast<uint4 *>(p.out + (size_t)(off + rg) * p.ldo + (size_t)head * 128 + half * 64 + c * 8) = w;
+                                *reinterpret_cast<uint4 *>(p.out + (size_t)(off + rg) * p.ldo + (size_t)head * HD + half * 64 + c * 8) = w;
                         }
                     }
                     __syncwarp();
                 }
-            } else {
+            } else if constexpr (HD == 128) {
                 // a row of one head is eight 16-element blocks of the quantiser: 64 packed bytes, 8 scale bytes
                 uint32_t sf_lo = 0u, sf_hi = 0u;
 #pragma unroll 1
@@ -555,26 +571,32 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     if (q_packed != nullptr && (q_sf == nullptr || !(q_input_scale > 0.0f) || (((uintptr_t)q_packed) & 15) != 0 ||
                                 (((uintptr_t)q_sf) & 3) != 0 || (num_q_heads % 2) != 0))
         return false;
-    if (head_dim != 128 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0 || total_tokens <= 0) return false;
+    if ((head_dim != 128 && head_dim != 64) || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0 || total_tokens <= 0) return false;
+    if (head_dim != 128 && q_packed != nullptr) return false;          // the quantising epilogue exists for head_dim 128 only
+    const int HD = head_dim;
     if ((ldq % 8) != 0 || (ldo % 8) != 0 || (ldk % 8) != 0 || (ldv % 8) != 0) return false;
     if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) != 0) return false;
-    if (ldq < num_q_heads * 128 || ldk < num_kv_heads * 128) return false;
+    if (ldq < num_q_heads * HD || ldk < num_kv_heads * HD) return false;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(prefill_attention_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(prefill_attention_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<128>::SMEM_BYTES) !=
+                cudaSuccess ||
+            cudaFuncSetAttribute(prefill_attention_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<64>::SMEM_BYTES) !=
+                cudaSuccess)
             return false;
-        cudaFuncSetAttribute(prefill_attention_umma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+        cudaFuncSetAttribute(prefill_attention_umma_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             (int)cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(prefill_attention_umma_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              (int)cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     const int vt_cols = (total_tokens + 64 * num_seqs + 63) & ~63;
-    __nv_bfloat16 *vt = (__nv_bfloat16 *)workspace_slot(WS_ATTN_VT, (size_t)num_kv_heads * 128 * (size_t)vt_cols * 2);
+    __nv_bfloat16 *vt = (__nv_bfloat16 *)workspace_slot(WS_ATTN_VT, (size_t)num_kv_heads * HD * (size_t)vt_cols * 2);
     AttnParams p;
     memset(&p, 0, sizeof(p));
-    if (!make_bf16_tmap_sw128(&p.tm_q, q, (uint64_t)num_q_heads * 128, (uint64_t)total_tokens, (uint64_t)ldq * 2, 64, 128)) return false;
-    if (!make_bf16_tmap_sw128(&p.tm_k, k, (uint64_t)num_kv_heads * 128, (uint64_t)total_tokens, (uint64_t)ldk * 2, 64, KT)) return false;
-    if (!make_bf16_tmap_sw128(&p.tm_vt, vt, (uint64_t)vt_cols, (uint64_t)num_kv_heads * 128, (uint64_t)vt_cols * 2, 64, 128)) return false;
+    if (!make_bf16_tmap_sw128(&p.tm_q, q, (uint64_t)num_q_heads * HD, (uint64_t)total_tokens, (uint64_t)ldq * 2, 64, 128)) return false;
+    if (!make_bf16_tmap_sw128(&p.tm_k, k, (uint64_t)num_kv_heads * HD, (uint64_t)total_tokens, (uint64_t)ldk * 2, 64, KT)) return false;
+    if (!make_bf16_tmap_sw128(&p.tm_vt, vt, (uint64_t)vt_cols, (uint64_t)num_kv_heads * HD, (uint64_t)vt_cols * 2, 64, HD)) return false;
     p.out = out;
     p.seq_offsets = seq_offsets;
     p.seq_lens = seq_lens;
@@ -596,7 +618,10 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
     p.q_inv_in = q_packed != nullptr ? 1.0f / q_input_scale : 0.0f;
 
     const dim3 tgrid((max_seq_len + 63) / 64, num_kv_heads, num_seqs);
-    launch_chained(transpose_v_kernel, tgrid, dim3(256), (size_t)0, st, vt, vt_cols, v, ldv, seq_offsets, seq_lens, vt_col, p.status);
+    if (HD == 128)
+        launch_chained(transpose_v_kernel<128>, tgrid, dim3(256), (size_t)0, st, vt, vt_cols, v, ldv, seq_offsets, seq_lens, vt_col, p.status);
+    else
+        launch_chained(transpose_v_kernel<64>, tgrid, dim3(256), (size_t)0, st, vt, vt_cols, v, ldv, seq_offsets, seq_lens, vt_col, p.status);
     note_launches(1);
     static int num_sms = 0;
     if (num_sms == 0) {
@@ -617,7 +642,10 @@ bool launch_prefill_attention_umma(__nv_bfloat16 *out, int ldo, const __nv_bfloa
         cudaMemsetAsync(p.dbg, 0, (size_t)grid.x * 8 * sizeof(unsigned long long), st);
     }
 #endif
-    launch_chained(prefill_attention_umma_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, st, p);
+    if (HD == 128)
+        launch_chained(prefill_attention_umma_kernel<128>, grid, dim3(THREADS), (size_t)Geo<128>::SMEM_BYTES, st, p);
+    else
+        launch_chained(prefill_attention_umma_kernel<64>, grid, dim3(THREADS), (size_t)Geo<64>::SMEM_BYTES, st, p);
 #ifdef GLMASR_EXPERIMENTS
     if (debug) {
         // timing experiment: where the soft-max warps of every CTA spent their cycles (averages over the CTAs)
