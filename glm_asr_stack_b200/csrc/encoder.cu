@@ -71,31 +71,33 @@ __global__ void __launch_bounds__(256) layernorm_kernel(__nv_bfloat16 *out, cons
     }
     __syncthreads();
     if (row >= rows) return;
-    float v[MAXE];
+    // three passes over the row in shared memory (kept out of registers: eight CTAs per SM stay resident)
     float sum = 0.0f;
-#pragma unroll
+#pragma unroll 8
     for (int j = 0; j < MAXE; ++j) {
         const int i = lane + 32 * j;
-        v[j] = i < dim ? __bfloat162float(row_s[i]) : 0.0f;
-        if (i < dim) sum += v[j];
+        if (i < dim) sum += __bfloat162float(row_s[i]);
     }
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xFFFFFFFFu, sum, off);
     sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
     const float mean = sum / dim;
     float sum_sq = 0.0f;
-#pragma unroll
+#pragma unroll 8
     for (int j = 0; j < MAXE; ++j) {
-        const float d = v[j] - mean;
-        if (lane + 32 * j < dim) sum_sq += d * d;
+        const int i = lane + 32 * j;
+        if (i < dim) {
+            const float d = __bfloat162float(row_s[i]) - mean;
+            sum_sq += d * d;
+        }
     }
     for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xFFFFFFFFu, sum_sq, off);
     sum_sq = __shfl_sync(0xFFFFFFFFu, sum_sq, 0);
     const float inv_std = 1.0f / sqrtf(sum_sq / dim + eps);
-#pragma unroll
+#pragma unroll 8
     for (int j = 0; j < MAXE; ++j) {
         const int i = lane + 32 * j;
         if (i < dim) {
-            const float val = (v[j] - mean) * inv_std;
+            const float val = (__bfloat162float(row_s[i]) - mean) * inv_std;
             row_s[i] = __float2bfloat16(val * __bfloat162float(w_s[i]) + __bfloat162float(b_s[i]));
         }
     }
@@ -180,6 +182,47 @@ __global__ void encoder_rope_kernel(__nv_bfloat16 *q, __nv_bfloat16 *k, const fl
     }
 }
 
+// Same values, 16 bytes per access: a thread takes dims d0..d0+7 (d0 = 0 or 8) of one head of one row and their
+// partners d0+16..d0+23, for q and k.  Needs 16-byte aligned rows and heads (strides and head_dim multiples of 8).
+__global__ void __launch_bounds__(256) encoder_rope_vec_kernel(__nv_bfloat16 *q, __nv_bfloat16 *k, const float *__restrict__ cos_t,
+                                                               const float *__restrict__ sin_t, const int *__restrict__ row_pos,
+                                                               int total_rows, int num_heads, int head_dim, int q_stride, int k_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total_rows * num_heads * 2) return;
+    const int d0 = (idx & 1) * 8, rh = idx >> 1;
+    const int head = rh % num_heads, row = rh / num_heads;
+    const int pos = row_pos[row];
+    float c[8], s[8];
+    {
+        const float4 *cp = reinterpret_cast<const float4 *>(cos_t + pos * kRotHalf + d0);
+        const float4 *sp = reinterpret_cast<const float4 *>(sin_t + pos * kRotHalf + d0);
+        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+        c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
+        s[0] = s0.x, s[1] = s0.y, s[2] = s0.z, s[3] = s0.w, s[4] = s1.x, s[5] = s1.y, s[6] = s1.z, s[7] = s1.w;
+    }
+    auto rotate = [&](__nv_bfloat16 *base) {
+        uint4 *pa = reinterpret_cast<uint4 *>(base + d0), *pb = reinterpret_cast<uint4 *>(base + d0 + kRotHalf);
+        const uint4 va = *pa, vb = *pb;
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t oa[4], ob[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a0 = __uint_as_float(wa[i] << 16), a1 = __uint_as_float(wa[i] & 0xFFFF0000u);
+            const float b0 = __uint_as_float(wb[i] << 16), b1 = __uint_as_float(wb[i] & 0xFFFF0000u);
+            const __nv_bfloat162 ra = __floats2bfloat162_rn(a0 * c[2 * i] - b0 * s[2 * i], a1 * c[2 * i + 1] - b1 * s[2 * i + 1]);
+            const __nv_bfloat162 rb = __floats2bfloat162_rn(b0 * c[2 * i] + a0 * s[2 * i], b1 * c[2 * i + 1] + a1 * s[2 * i + 1]);
+            oa[i] = *reinterpret_cast<const uint32_t *>(&ra);
+            ob[i] = *reinterpret_cast<const uint32_t *>(&rb);
+        }
+        *pa = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+        *pb = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+    };
+    if (q != nullptr) rotate(q + (size_t)row * q_stride + head * head_dim);
+    if (k != nullptr) rotate(k + (size_t)row * k_stride + head * head_dim);
+}
+
 static float *g_rope_dev = nullptr;          // lives in a workspace slot: dropped by encoder_forget_all before the slots are freed
 static const float *rope_tables(cudaStream_t st) {
     float *&dev = g_rope_dev;
@@ -203,9 +246,16 @@ void launch_encoder_rope(__nv_bfloat16 *q, __nv_bfloat16 *k, const int *d_row_po
                          int q_stride, int k_stride, cudaStream_t st) {
     if (total_rows <= 0) return;
     const float *tab = rope_tables(st);
-    const int work = total_rows * num_heads * kRotHalf;
-    launch_chained(encoder_rope_kernel, dim3((work + 255) / 256), dim3(256), (size_t)0, st, q, k, tab,
-                   tab + (size_t)kRopeTablePos * kRotHalf, d_row_pos, total_rows, num_heads, head_dim, q_stride, k_stride);
+    const bool vec = (head_dim % 8) == 0 && (q_stride % 8) == 0 && (k_stride % 8) == 0 && (((uintptr_t)q | (uintptr_t)k) & 15) == 0;
+    if (vec) {
+        const int work = total_rows * num_heads * 2;
+        launch_chained(encoder_rope_vec_kernel, dim3((work + 255) / 256), dim3(256), (size_t)0, st, q, k, tab,
+                       tab + (size_t)kRopeTablePos * kRotHalf, d_row_pos, total_rows, num_heads, head_dim, q_stride, k_stride);
+    } else {
+        const int work = total_rows * num_heads * kRotHalf;
+        launch_chained(encoder_rope_kernel, dim3((work + 255) / 256), dim3(256), (size_t)0, st, q, k, tab,
+                       tab + (size_t)kRopeTablePos * kRotHalf, d_row_pos, total_rows, num_heads, head_dim, q_stride, k_stride);
+    }
     note_launches(1);
 }
 

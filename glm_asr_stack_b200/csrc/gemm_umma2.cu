@@ -73,6 +73,19 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             const int n_tile = tile / num_m_pairs;
             const int acc = acc_it & 1;
             const uint32_t aph = (acc_it >> 1) & 1u;
+            if (p.epi == EPI_RESIDUAL) {
+                // the residual of this tile is not in any cache yet (M x N bf16 streamed once): ask for this
+                // thread's four 64-byte pieces now, while the tile's MMAs run, so that the loads of the epilogue
+                // below find them in L2
+                const SubTile stp = resolve_subtile(p, n_tile, half, 2);
+                const int prow = m_tile * 128 + quad * 32 + lane;
+                if (prow < p.M) {
+                    const __nv_bfloat16 *rp = p.residual + (size_t)prow * p.ldo + stp.col0;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (c * 32 < stp.ncols) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + c * 32));
+                }
+            }
             DBG_T0();
             bool ok = mbar_wait(tfull_bar(acc), aph, abort_word, ST_TIMEOUT_EPILOGUE);
             ok = __all_sync(0xFFFFFFFFu, ok);
