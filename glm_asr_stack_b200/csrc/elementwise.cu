@@ -329,15 +329,25 @@ __global__ void argmax_rows_kernel(const __nv_bfloat16 *__restrict__ logits, int
     };
     const bool vec_ok = (((uintptr_t)p & 15) == 0);
     const int nvec = vec_ok ? vocab / 8 : 0;
-    for (int c = tid; c < nvec; c += 256) {
-        const uint4 q = reinterpret_cast<const uint4 *>(p)[c];
+    // four 16-byte loads in flight per thread: a row is read once from HBM and one load at a time leaves the
+    // memory system idle (the order of the comparisons does not matter: argmax_better is a total order)
+    auto consider8 = [&](const uint4 &q, int c) {
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             consider(__uint_as_float(w[j] << 16), c * 8 + 2 * j);
             consider(__uint_as_float(w[j] & 0xFFFF0000u), c * 8 + 2 * j + 1);
         }
+    };
+    int c = tid;
+    for (; c + 768 < nvec; c += 1024) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) q[u] = reinterpret_cast<const uint4 *>(p)[c + 256 * u];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) consider8(q[u], c + 256 * u);
     }
+    for (; c < nvec; c += 256) consider8(reinterpret_cast<const uint4 *>(p)[c], c);
     for (int v = nvec * 8 + tid; v < vocab; v += 256) consider(__bfloat162float(p[v]), v);
     sh_val[tid] = bv;
     sh_idx[tid] = bi;
