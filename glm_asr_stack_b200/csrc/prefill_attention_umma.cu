@@ -100,6 +100,31 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// sm_100 arithmetic the soft-max loop is written around (it is bound by instruction issue, ~4.5 per score):
+// a three-input maximum and packed two-lane fp32 multiply-add / add.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&b);
@@ -377,7 +402,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                 }
                 float mx = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < KT; ++c) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
+                for (int c = 0; c < KT; c += 2) mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1]));
                 const float m_new = fmaxf(m, mx * scale);
                 float alpha = 1.0f;
                 if (j == 0) {
@@ -388,16 +413,23 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_umma_kernel(cons
                 }
                 const bool rescale = __any_sync(0xFFFFFFFFu, alpha != 1.0f);
                 const float neg_m = -m;
-                float sum = 0.0f;
+                // two scores per multiply-add and per addition; the row sum is kept as two partial sums
+                const unsigned long long scale2 = pack_f32x2(scale, scale), neg_m2 = pack_f32x2(neg_m, neg_m);
+                unsigned long long sum2 = pack_f32x2(0.0f, 0.0f);
                 uint32_t pk[32];
 #pragma unroll
                 for (int c = 0; c < KT; c += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale, neg_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale, neg_m));
-                    sum += p0 + p1;
+                    float t0, t1;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])),
+                                           scale2, neg_m2),
+                                 t0, t1);
+                    const float p0 = ex2(t0), p1 = ex2(t1);
+                    sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
                     pk[c >> 1] = pack2(p0, p1);
                 }
-                l = l * alpha + sum;
+                float sum_lo, sum_hi;
+                unpack_f32x2(sum2, sum_lo, sum_hi);
+                l = l * alpha + (sum_lo + sum_hi);
                 ATT_DBG(2);
                 if (j >= 1) {
                     // P V of the previous step has to be complete before P is overwritten or O rescaled
