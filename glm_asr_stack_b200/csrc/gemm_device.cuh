@@ -212,12 +212,16 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 }
 
 __device__ __forceinline__ float silu_gate(float g, float u) {
-    // (g * sigmoid(g)) * u as in the reference SiLU-gate (Infer-engine/cuda/kernels.cu:1259-1263), with
-    // the hardware exponential and reciprocal: the fused epilogue is compared with the reference
-    // within the bf16 tolerance anyway (its inputs come from a differently ordered accumulation),
-    // and the exact expf + IEEE division made the epilogue slower than the tile's MMAs.
-    const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
-    return (g * sig) * u;
+    // (g * sigmoid(g)) * u as in the reference SiLU-gate (Infer-engine/cuda/kernels.cu:1259-1263), with the
+    // hardware exponential and reciprocal: the fused epilogue is compared with the reference within the bf16
+    // tolerance anyway (its inputs come from a differently ordered accumulation), and the exact expf + IEEE
+    // division made the epilogue slower than the tile's MMAs.  Six instructions: the flush-to-zero forms of
+    // ex2 / rcp need no range fix-up code around them, and a flushed exp(-g) (g > 87) or a flushed 1 / (1 + e)
+    // (e > 2^126, g < -87) gives the same product as the unflushed one to the last bit of a bf16.
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return (g * r) * u;
 }
 
 
