@@ -108,28 +108,31 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
             uint32_t q_first_lo = 0, q_first_hi = 0, sf_first = 0;       // quantised first half, stored with the second
 #pragma unroll 1
             for (int it = 0; it < 2; ++it) {     // 16 outputs per pass
+                // two values per multiply / conversion (scale_round_bf16_x2, silu_gate_x2: the same bits as the scalar
+                // forms): this epilogue shares its issue slots with the MMA and producer warps
                 float g[16], u[16];
+                const unsigned long long ag2 = pack_f32x2(ag, ag), au2 = pack_f32x2(au, au);
                 if (!owns_shared) {
                     uint32_t a[16], b[16];
                     tmem_ld_x16(g_col + it * 16, a);
                     tmem_ld_x16(u_col + it * 16, b);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        g[i] = bf16_round(__uint_as_float(a[i]) * ag);
-                        u[i] = bf16_round(__uint_as_float(b[i]) * au);
+                    for (int i = 0; i < 8; ++i) {
+                        scale_round_bf16_x2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]), ag2, g[2 * i], g[2 * i + 1]);
+                        scale_round_bf16_x2(__uint_as_float(b[2 * i]), __uint_as_float(b[2 * i + 1]), au2, u[2 * i], u[2 * i + 1]);
                     }
                 } else {
                     uint32_t a[16];
                     tmem_ld_x16((kept_is_gate ? u_col : g_col) + it * 16, a);
                     tmem_ld_wait();
-                    const float sa = kept_is_gate ? au : ag;
+                    const unsigned long long sa2 = kept_is_gate ? au2 : ag2;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const uint32_t kw = it == 0 ? kept[i] : kept[8 + i];
                         const float k_lo = __uint_as_float(kw << 16), k_hi = __uint_as_float(kw & 0xFFFF0000u);
-                        const float x_lo = bf16_round(__uint_as_float(a[2 * i]) * sa);
-                        const float x_hi = bf16_round(__uint_as_float(a[2 * i + 1]) * sa);
+                        float x_lo, x_hi;
+                        scale_round_bf16_x2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]), sa2, x_lo, x_hi);
                         g[2 * i] = kept_is_gate ? k_lo : x_lo;
                         g[2 * i + 1] = kept_is_gate ? k_hi : x_hi;
                         u[2 * i] = kept_is_gate ? x_lo : k_lo;
@@ -144,19 +147,19 @@ __global__ void __launch_bounds__(640, 1) umma_gemm_pair16_kernel(const __grid_c
                 }
                 float v[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = silu_gate(g[i], u[i]);
+                for (int i = 0; i < 8; ++i) silu_gate_x2(g[2 * i], g[2 * i + 1], u[2 * i], u[2 * i + 1], v[2 * i], v[2 * i + 1]);
                 const int c0 = slice * 32 + it * 16;
                 const int col = sg.col0 + c0;
                 const int nvalid = sg.ncols - c0;
                 if (p.q_packed != nullptr) {
                     // the next GEMM's operand: quantise the bf16-rounded products of this 16-column block
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = bf16_round(v[i]);
+                    for (int i = 0; i < 8; ++i) round_bf16_x2(v[2 * i], v[2 * i + 1], v[2 * i], v[2 * i + 1]);
                     uint32_t qlo, qhi, sf;
                     if (GLMASR_EXP(p, 8)) {           // timing experiment: no quantiser arithmetic (wrong results)
                         qlo = __float_as_uint(v[0]), qhi = __float_as_uint(v[9]), sf = __float_as_uint(v[3]) & 0x7Fu;
                     } else {
-                        sf = quantize_block16_lut(v, p.q_inv_in, os_table, qlo, qhi);
+                        sf = quantize_block16_fast(v, p.q_inv_in, os_table, qlo, qhi);
                     }
                     if (it == 0) {
                         q_first_lo = qlo, q_first_hi = qhi, sf_first = sf;
