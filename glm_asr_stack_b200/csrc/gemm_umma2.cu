@@ -73,19 +73,23 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             const int n_tile = tile / num_m_pairs;
             const int acc = acc_it & 1;
             const uint32_t aph = (acc_it >> 1) & 1u;
-            if (p.epi == EPI_RESIDUAL) {
-                // the residual of this tile is not in any cache yet (M x N bf16 streamed once): ask for this
-                // thread's four 64-byte pieces now, while the tile's MMAs run, so that the loads of the epilogue
-                // below find them in L2
-                const SubTile stp = resolve_subtile(p, n_tile, half, 2);
-                const int prow = m_tile * 128 + quad * 32 + lane;
-                if (prow < p.M) {
-                    const __nv_bfloat16 *rp = p.residual + (size_t)prow * p.ldo + stp.col0;
+            // The residual does not depend on the accumulator: this thread's 128 bytes of the first 64-column box are
+            // requested before the wait for the tile's MMAs, those of the second box once the first is computed.
+            const bool owns_pre = (half == 1 - acc);
+            const int first_box_pre = (owns_pre && acc == 0) ? 1 : 0;
+            const SubTile st_pre = resolve_subtile(p, n_tile, half, 2);
+            const int row_pre = m_tile * 128 + quad * 32 + lane;
+            Packed16 res_box[2];
+            auto load_res_box = [&](int bx) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (c * 32 < stp.ncols) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + c * 32));
+                for (int hc = 0; hc < 2; ++hc) {
+                    const int c0 = bx * 64 + hc * 32;
+                    const int nvalid = st_pre.ncols - c0;
+                    if (row_pre < p.M && nvalid > 0)
+                        res_box[hc] = load_packed(p.residual + (size_t)row_pre * p.ldo + st_pre.col0 + c0, nvalid);
                 }
-            }
+            };
+            if (p.epi == EPI_RESIDUAL) load_res_box(first_box_pre);
             DBG_T0();
             bool ok = mbar_wait(tfull_bar(acc), aph, abort_word, ST_TIMEOUT_EPILOGUE);
             ok = __all_sync(0xFFFFFFFFu, ok);
@@ -230,8 +234,11 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                         const int col = st.col0 + c0;
                         const bool live = row_ok && nvalid > 0;
                         float v[32];
+                        const unsigned long long alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[hc][i]) * alpha;
+                        for (int i = 0; i < 16; ++i)
+                            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(r[hc][2 * i]), __uint_as_float(r[hc][2 * i + 1])), alpha2),
+                                         v[2 * i], v[2 * i + 1]);
                         if (p.bias != nullptr && nvalid > 0) {
                             float b[32];
                             unpack_bf16(load_packed(p.bias + col, nvalid), b);
@@ -239,15 +246,24 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                             for (int i = 0; i < 32; ++i) v[i] += b[i];
                         }
                         if (p.epi == EPI_RESIDUAL && live) {
-                            float res[32];
-                            unpack_bf16(load_packed(p.residual + (size_t)row * p.ldo + col, nvalid), res);
+                            // bf16(acc) + residual, two values per conversion and per addition
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + res[i];
+                            for (int i = 0; i < 16; ++i) {
+                                float x0, x1;
+                                round_bf16_x2(v[2 * i], v[2 * i + 1], x0, x1);
+                                const uint32_t rw = res_box[hc].w[i];
+                                unpack_f32x2(add_f32x2(pack_f32x2(x0, x1),
+                                                       pack_f32x2(__uint_as_float(rw << 16), __uint_as_float(rw & 0xFFFF0000u))),
+                                             v[2 * i], v[2 * i + 1]);
+                            }
                         }
                         const Packed16 pk = pack_bf16(v);
                         if (box_tma) stage_packed(pk, hc);
                         else if (live && !GLMASR_EXP(p, 4)) store_packed(out_row + col, pk, nvalid);
                     }
+                    // the other box's residual: requested now, in flight during the store of this box and the
+                    // tensor-memory load of the next
+                    if (p.epi == EPI_RESIDUAL && k == 0) load_res_box(bx ^ 1);
                     if (box_tma && !GLMASR_EXP(p, 4)) stage_flush(st.col0 + bx * 64, m_tile * 128 + quad * 32);
                 }
             }
