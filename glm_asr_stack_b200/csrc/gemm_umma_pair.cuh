@@ -247,15 +247,17 @@ __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairC
             const uint64_t bdesc0 = smem_desc_sw128(b_addr);
             if (leader_lane) {
                 const uint64_t sfdesc0 = smem_desc_sf_chunk(a_addr + C::A_BYTES + C::B_BYTES);
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch)
-                    tmem_cp_32x128b_warpx4_pair(sfa_t + 4 * ch, sfdesc0 + (uint64_t)((ch * C::SF_CHUNK) >> 4));
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
+                if (!(GLMASR_EXP(p, 32) && it > 0)) {        // experiment: scale factors copied once (wrong results)
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch)
-                        tmem_cp_32x128b_warpx4_pair(sfb_t + ch * 8 + 4 * h,
-                                                    sfdesc0 + (uint64_t)(((1 + h) * C::SF_TILE + ch * C::SF_CHUNK) >> 4));
+                        tmem_cp_32x128b_warpx4_pair(sfa_t + 4 * ch, sfdesc0 + (uint64_t)((ch * C::SF_CHUNK) >> 4));
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch)
+                            tmem_cp_32x128b_warpx4_pair(sfb_t + ch * 8 + 4 * h,
+                                                        sfdesc0 + (uint64_t)(((1 + h) * C::SF_TILE + ch * C::SF_CHUNK) >> 4));
+                }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
