@@ -495,16 +495,19 @@ __global__ void __launch_bounds__(THREADS, 1) decode_tail_kernel(const __grid_co
                                 tmem_ld_x32(t_row + ACC_RUN1 + 32 * j, ru);
                                 tmem_ld_wait();
                                 uint32_t q[4], sf = 0;
+                                const unsigned long long ag2 = pack_f32x2(ag, ag), au2 = pack_f32x2(au, au);
 #pragma unroll
                                 for (int b = 0; b < 2; ++b) {
                                     float blk[16];
 #pragma unroll
-                                    for (int i = 0; i < 16; ++i) {
-                                        const float gg = bf16_round(__uint_as_float(rg[16 * b + i]) * ag);
-                                        const float uu = bf16_round(__uint_as_float(ru[16 * b + i]) * au);
-                                        blk[i] = bf16_round(silu_gate(gg, uu));
+                                    for (int i = 0; i < 8; ++i) {      // two values at a time: the same bits as the scalar forms
+                                        float g0, g1, u0, u1, v0, v1;
+                                        scale_round_bf16_x2(__uint_as_float(rg[16 * b + 2 * i]), __uint_as_float(rg[16 * b + 2 * i + 1]), ag2, g0, g1);
+                                        scale_round_bf16_x2(__uint_as_float(ru[16 * b + 2 * i]), __uint_as_float(ru[16 * b + 2 * i + 1]), au2, u0, u1);
+                                        silu_gate_x2(g0, g1, u0, u1, v0, v1);
+                                        round_bf16_x2(v0, v1, blk[2 * i], blk[2 * i + 1]);
                                     }
-                                    sf |= quantize_block16_lut(blk, g.q_inv_in, os_table, q[2 * b], q[2 * b + 1]) << (8 * b);
+                                    sf |= quantize_block16_fast(blk, g.q_inv_in, os_table, q[2 * b], q[2 * b + 1]) << (8 * b);
                                 }
                                 if (row_ok) {
                                     const int col = w.r[0].col0 + 32 * j;
