@@ -30,6 +30,21 @@ __device__ __forceinline__ float e4m3_to_float_ref(uint32_t b) {
     return (b & 0x80u) ? -mag : mag;
 }
 
+// x / 6 rounded as the IEEE division (the quantiser's first division) in four multiply-adds: the correctly rounded
+// reciprocal of 6 as r_hi + r_lo, q0 = x * (r_hi + r_lo) within one unit of the quotient, the exact residual
+// x - 6 q0 from a fused multiply-add, and q0 + e * r_hi (Markstein; 6's significand is not all ones).  x outside
+// [2^-60, 2^60] takes the ordinary division.
+__device__ __forceinline__ float div6_exact(float x) {
+    const float r_hi = 0.16666667163372040f;                        // RN(1 / 6)
+    const float r_lo = -4.967053879312289e-09f;                     // fma(-6, r_hi, 1) * r_hi
+    if (x >= 8.6736174e-19f && x <= 1.1529215e18f) {
+        const float q0 = fmaf(x, r_hi, x * r_lo);
+        const float e = fmaf(-q0, 6.0f, x);
+        return fmaf(e, r_hi, q0);
+    }
+    return __fdiv_rn(x, 6.0f);
+}
+
 // One 16-element block of the activation quantiser (reference: Infer-engine/cuda/nvfp4_cutlass.cu:35-87):
 //   amax = max |v| ; scale = (inv_in * amax) / 6 ; s8 = e4m3(scale) ; os = inv_in / float(s8)
 //   q_j = e2m1(v_j * os), even j in the low nibble.
@@ -37,17 +52,22 @@ __device__ __forceinline__ float e4m3_to_float_ref(uint32_t b) {
 // quantiser and by GEMM epilogues that emit the next GEMM's operand directly, so both produce
 // the same bytes.
 __device__ __forceinline__ uint32_t quantize_block16(const float (&v)[16], float inv_in, uint32_t &lo, uint32_t &hi) {
+    // (three-input maximum, exact division by 6 in four multiply-adds, two products per multiply: the same bits
+    // as the plain expressions above in about two thirds of the instructions)
     float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    const float scale = amax > 0.0f ? __fdiv_rn(inv_in * amax, 6.0f) : 0.0f;
+    for (int j = 0; j < 16; j += 2) amax = max3(amax, fabsf(v[j]), fabsf(v[j + 1]));
+    const float scale = amax > 0.0f ? div6_exact(inv_in * amax) : 0.0f;
     const __nv_fp8_e4m3 s8(scale);
     const float scale_rounded = scale > 0.0f ? (float)s8 : 0.0f;
     const float os = scale_rounded > 0.0f ? __fdiv_rn(inv_in, scale_rounded) : 0.0f;
+    const unsigned long long os2 = pack_f32x2(os, os);
     lo = 0, hi = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        const uint32_t q = __nv_cvt_float2_to_fp4x2(make_float2(v[2 * j] * os, v[2 * j + 1] * os), __NV_E2M1,
+        float x0, x1;
+        unpack_f32x2(mul_f32x2(pack_f32x2(v[2 * j], v[2 * j + 1]), os2), x0, x1);
+        const uint32_t q = __nv_cvt_float2_to_fp4x2(make_float2(x0, x1), __NV_E2M1,
                                                     cudaRoundNearest) & 0xFFu;
         if (j < 4) lo |= q << (8 * j);
         else hi |= q << (8 * (j - 4));
@@ -87,21 +107,6 @@ __device__ __forceinline__ uint32_t quantize_block16_lut(const float (&v)[16], f
     return (uint32_t)s8.__x;
 }
 
-
-// x / 6 rounded as the IEEE division (the quantiser's first division) in four multiply-adds: the correctly rounded
-// reciprocal of 6 as r_hi + r_lo, q0 = x * (r_hi + r_lo) within one unit of the quotient, the exact residual
-// x - 6 q0 from a fused multiply-add, and q0 + e * r_hi (Markstein; 6's significand is not all ones).  x outside
-// [2^-60, 2^60] takes the ordinary division.
-__device__ __forceinline__ float div6_exact(float x) {
-    const float r_hi = 0.16666667163372040f;                        // RN(1 / 6)
-    const float r_lo = -4.967053879312289e-09f;                     // fma(-6, r_hi, 1) * r_hi
-    if (x >= 8.6736174e-19f && x <= 1.1529215e18f) {
-        const float q0 = fmaf(x, r_hi, x * r_lo);
-        const float e = fmaf(-q0, 6.0f, x);
-        return fmaf(e, r_hi, q0);
-    }
-    return __fdiv_rn(x, 6.0f);
-}
 
 // quantize_block16_lut on values that are already bf16-rounded floats, with the packed multiply, the three-input
 // maximum and div6_exact: the same bytes in about half the instructions.  pack_f32x2 / mul_f32x2 / max3: ptx.cuh.
