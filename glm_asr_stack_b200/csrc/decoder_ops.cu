@@ -132,19 +132,38 @@ __global__ void rope_inv_freq_kernel(int head_dim) {
     if (d < head_dim / 2) g_inv_freq[d] = 1.0f / powf(10000.0f, (2.0f * d) / head_dim);
 }
 
+// cos / sin of every row's position, [rows][head_dim] floats (cos for d < head_dim / 2, then sin): the values the
+// kernel below computes per launch, for callers that run it once per layer on the same positions.
+__global__ void rope_angles_kernel(float *__restrict__ table, const int *__restrict__ positions, int rows, int head_dim) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int half_dim = head_dim / 2;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * half_dim) return;
+    const int row = idx / half_dim, d = idx - row * half_dim;
+    const float theta = positions[row] * g_inv_freq[d];
+    table[(size_t)row * head_dim + d] = cosf(theta);
+    table[(size_t)row * head_dim + half_dim + d] = sinf(theta);
+}
+
 __global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *__restrict__ positions,
                                      const int64_t *__restrict__ slot_mapping, __nv_bfloat16 *__restrict__ key_cache,
-                                     __nv_bfloat16 *__restrict__ value_cache, int q_heads, int kv_heads, int head_dim) {
+                                     __nv_bfloat16 *__restrict__ value_cache, int q_heads, int kv_heads, int head_dim,
+                                     const float *__restrict__ angles) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float cs[];            // [half_dim] cos, [half_dim] sin
     const int seq = blockIdx.x;
     const int half_dim = head_dim / 2;
-    const int pos = positions[seq];
-    for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
-        const float theta = pos * g_inv_freq[d];
-        cs[d] = cosf(theta);
-        cs[half_dim + d] = sinf(theta);
+    if (angles != nullptr) {                 // computed once for all layers (rope_angles_kernel: the same expressions)
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) cs[d] = angles[(size_t)seq * head_dim + d];
+    } else {
+        const int pos = positions[seq];
+        for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
+            const float theta = pos * g_inv_freq[d];
+            cs[d] = cosf(theta);
+            cs[half_dim + d] = sinf(theta);
+        }
     }
     __syncthreads();
     __nv_bfloat16 *row = qkv + (size_t)seq * ld;
@@ -197,23 +216,36 @@ __global__ void rope_qk_cache_kernel(__nv_bfloat16 *qkv, int ld, int k_col, int 
         reinterpret_cast<uint4 *>(vdst)[c] = reinterpret_cast<const uint4 *>(row + v_col)[c];
 }
 
-bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *positions,
-                          const int64_t *slot_mapping, __nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, int num_seqs,
-                          int q_heads, int kv_heads, int head_dim, cudaStream_t st) {
-    const int row_elems = kv_heads * head_dim;
-    if (num_seqs <= 0) return true;
-    if ((head_dim % 16) != 0 || head_dim > 1024 || (row_elems % 8) != 0 || (ld % 8) != 0 || (v_col % 8) != 0 || (k_col % 8) != 0 ||
-        (((uintptr_t)qkv | (uintptr_t)value_cache | (uintptr_t)key_cache) & 15) != 0)
-        return false;
+static void ensure_inv_freq(int head_dim, cudaStream_t st) {
     if (g_inv_freq_dim != head_dim) {
         // ordinary launch: it completes before the kernels behind it start
         rope_inv_freq_kernel<<<(head_dim / 2 + 127) / 128, 128, 0, st>>>(head_dim);
         g_inv_freq_dim = head_dim;
     }
+}
+
+bool launch_rope_angles(float *table, const int *positions, int rows, int head_dim, cudaStream_t st) {
+    if (rows <= 0) return true;
+    if (table == nullptr || positions == nullptr || (head_dim % 2) != 0 || head_dim > 1024) return false;
+    ensure_inv_freq(head_dim, st);
+    const int total = rows * (head_dim / 2);
+    launch_chained(rope_angles_kernel, dim3((total + 255) / 256), dim3(256), (size_t)0, st, table, positions, rows, head_dim);
+    return true;
+}
+
+bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *positions,
+                          const int64_t *slot_mapping, __nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, int num_seqs,
+                          int q_heads, int kv_heads, int head_dim, cudaStream_t st, const float *angles) {
+    const int row_elems = kv_heads * head_dim;
+    if (num_seqs <= 0) return true;
+    if ((head_dim % 16) != 0 || head_dim > 1024 || (row_elems % 8) != 0 || (ld % 8) != 0 || (v_col % 8) != 0 || (k_col % 8) != 0 ||
+        (((uintptr_t)qkv | (uintptr_t)value_cache | (uintptr_t)key_cache) & 15) != 0)
+        return false;
+    ensure_inv_freq(head_dim, st);
     GLMASR_PREFER_MAX_SMEM(rope_qk_cache_kernel);
     launch_chained(rope_qk_cache_kernel, dim3(num_seqs), dim3(256), (size_t)head_dim * sizeof(float), st, qkv, ld, k_col, v_col, positions, slot_mapping,
                                                                              key_cache, value_cache, q_heads, kv_heads,
-                                                                             head_dim);
+                                                                             head_dim, angles);
     return true;
 }
 

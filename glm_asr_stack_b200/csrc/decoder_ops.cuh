@@ -17,9 +17,12 @@ void launch_rope_single_token(__nv_bfloat16 *tensor, int ld, int col0, const int
 // RoPE on q (columns [0, q_heads*head_dim)) and k (at k_col) of the new token's q|k|v row, in place, and the
 // K / V rows into the paged cache: the three launches between the projection and attention as one.
 // Returns false when the layout is not supported (alignment).
+// angles (optional): the rows' cos / sin as launch_rope_angles wrote them, so that 28 layers share one evaluation.
 bool launch_rope_qk_cache(__nv_bfloat16 *qkv, int ld, int k_col, int v_col, const int *positions,
                           const int64_t *slot_mapping, __nv_bfloat16 *key_cache, __nv_bfloat16 *value_cache, int num_seqs,
-                          int q_heads, int kv_heads, int head_dim, cudaStream_t st);
+                          int q_heads, int kv_heads, int head_dim, cudaStream_t st, const float *angles = nullptr);
+// table[rows][head_dim] floats: cos(pos * inv_freq[d]) for d < head_dim / 2, then the sines (the kernel's own expressions).
+bool launch_rope_angles(float *table, const int *positions, int rows, int head_dim, cudaStream_t st);
 // RMSNorm + activation quantiser for the next W4A4 GEMM: e2m1 bytes [rows, dim/2] and 128x4-tiled scales.
 // normed_out (optional, dense [rows, dim], 16-byte aligned): the bf16 result of the norm as well, for consumers
 // that take bf16.

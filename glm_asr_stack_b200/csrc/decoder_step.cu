@@ -543,6 +543,7 @@ enum DecodeSlot : int {   // workspace slots 13.. (api.cu owns 0..12)
     WS_D_AQ = 24, WS_D_ASF = 25,
     WS_D_GQ = 48, WS_D_GSF = 49, WS_D_COUNTER = 50,   // layer tail: quantised SiLU-gate output, grid counter
     // 51: the layer tail's cycle counters (experiment builds)
+    WS_D_ANGLES = 52,                                 // cos / sin of every row's position
 };
 
 // ============================================================================================
@@ -810,6 +811,10 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
     }
     launch_gather_block_tables(d_bt, pool->d_block_tables, d_rows, M, pool->max_blocks_per_seq, st);
     // the vectors above are pageable host memory: the async copies have completed staging on return
+    // the rotary angles depend on the positions only: one evaluation for all layers
+    float *rope_angles = (float *)workspace_slot(WS_D_ANGLES, (size_t)M * HD * sizeof(float));
+    if (launch_rope_angles(rope_angles, d_seq_lens, M, HD, st)) note_launches(1);
+    else rope_angles = nullptr;
 
     // the layer tail (o .. next layer's q|k|v) as one co-resident launch where it applies
     const bool tail = tail_enabled() && M <= 256;
@@ -832,7 +837,7 @@ extern "C" void decoder_decode_step_batched(void *handle, const void *ws_v, uint
         int glue = have_qkv ? 0 : project_qkv(R, hid, B, M, H, KV, st);
         have_qkv = false;
         // RoPE on q and k in place (position = cached length), KV write, attention over cached + 1 tokens
-        if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_seq_lens, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
+        if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_seq_lens, d_slot, k_base, v_base, M, QH, KVH, HD, st, rope_angles)) {
             glue += 1;
         } else {
             launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, 0, d_seq_lens, M, QH, HD, st);
@@ -971,6 +976,9 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_slot, h_slot.data(), (size_t)M * sizeof(int64_t), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_pos, h_pos.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, st));
     GLMASR_CUDA_CHECK(cudaMemcpyAsync(d_meta, h_meta.data(), (size_t)2 * num_seqs * sizeof(int), cudaMemcpyHostToDevice, st));
+    float *rope_angles = (float *)workspace_slot(WS_D_ANGLES, (size_t)M * HD * sizeof(float));
+    if (launch_rope_angles(rope_angles, d_pos, M, HD, st)) note_launches(1);
+    else rope_angles = nullptr;
 
     uint16_t *hid = hidden;
     for (int l = 0; l < L; ++l) {
@@ -980,7 +988,7 @@ extern "C" void decoder_prefill_paged_batched(void *handle, const void *ws_v, ui
         int glue = 0;
 
         glue += project_qkv(R, hid, B, M, H, KV, st);
-        if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_pos, d_slot, k_base, v_base, M, QH, KVH, HD, st)) {
+        if (launch_rope_qk_cache((__nv_bfloat16 *)qkv, NQKV, H, H + KV, d_pos, d_slot, k_base, v_base, M, QH, KVH, HD, st, rope_angles)) {
             glue += 1;
         } else {
             launch_rope_single_token((__nv_bfloat16 *)qkv, NQKV, 0, d_pos, M, QH, HD, st);
