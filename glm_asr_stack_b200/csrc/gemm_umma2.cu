@@ -73,23 +73,43 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             const int n_tile = tile / num_m_pairs;
             const int acc = acc_it & 1;
             const uint32_t aph = (acc_it >> 1) & 1u;
-            // The residual does not depend on the accumulator: this thread's 128 bytes of the first 64-column box are
-            // requested before the wait for the tile's MMAs, those of the second box once the first is computed.
+            // The residual does not depend on the accumulator, and a load issued when its value is needed waits
+            // behind the operand ring's traffic (about 3000 cycles here), so both 64-column boxes are requested
+            // before the wait for the tile's MMAs: the first straight into the staging buffer (idle between tiles;
+            // the sum is formed in place there), the second into registers.  A warp reads a box (32 rows x 128
+            // bytes) by whole lines, copy j of lane l being chunk l & 7 of row 4 j + (l >> 3), and the chunks reach
+            // their row's lane through the staging buffer: with one row per lane every load would touch 32 lines.
             const bool owns_pre = (half == 1 - acc);
             const int first_box_pre = (owns_pre && acc == 0) ? 1 : 0;
             const SubTile st_pre = resolve_subtile(p, n_tile, half, 2);
-            const int row_pre = m_tile * 128 + quad * 32 + lane;
-            Packed16 res_box[2];
-            auto load_res_box = [&](int bx) {
+            const bool res_lines = p.epi == EPI_RESIDUAL && p.tma_store && st_pre.ncols >= 128 && (p.ldo & 7) == 0 &&
+                                   (((uintptr_t)p.residual) & 15) == 0;
+            uint4 res_c[8];
+            if (res_lines) {
+                const int r0 = m_tile * 128 + quad * 32 + (lane >> 3);
+                const __nv_bfloat16 *src = p.residual + (size_t)min(r0, p.M - 1) * p.ldo + st_pre.col0 + (lane & 7) * 8;
+                stage_begin();      // the previous tile's last store has read the buffer
 #pragma unroll
-                for (int hc = 0; hc < 2; ++hc) {
-                    const int c0 = bx * 64 + hc * 32;
-                    const int nvalid = st_pre.ncols - c0;
-                    if (row_pre < p.M && nvalid > 0)
-                        res_box[hc] = load_packed(p.residual + (size_t)row_pre * p.ldo + st_pre.col0 + c0, nvalid);
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t rb = (uint32_t)(4 * j) + ((uint32_t)lane >> 3);
+                    const bool in = r0 + 4 * j < p.M;
+                    cp_async16_zfill(out_stage + rb * 128 + ((((uint32_t)lane & 7u) ^ (rb & 7u)) << 4),
+                                     src + first_box_pre * 64 + (in ? (size_t)(4 * j) * p.ldo : 0), in);
                 }
+                cp_async_commit();
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    res_c[j] = (r0 + 4 * j < p.M) ? *reinterpret_cast<const uint4 *>(src + (first_box_pre ^ 1) * 64 + (size_t)(4 * j) * p.ldo)
+                                                  : make_uint4(0u, 0u, 0u, 0u);
+            }
+            auto stage_res_lines = [&]() {      // registers -> staging buffer, in the layout stage_packed uses
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t rb = (uint32_t)(4 * j) + ((uint32_t)lane >> 3);
+                    sts128(out_stage + rb * 128 + ((((uint32_t)lane & 7u) ^ (rb & 7u)) << 4), res_c[j]);
+                }
+                __syncwarp();
             };
-            if (p.epi == EPI_RESIDUAL) load_res_box(first_box_pre);
             DBG_T0();
             bool ok = mbar_wait(tfull_bar(acc), aph, abort_word, ST_TIMEOUT_EPILOGUE);
             ok = __all_sync(0xFFFFFFFFu, ok);
@@ -226,7 +246,13 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                     if (k == 1) release_acc();
                     else if (owns_shared) release_shared();
                     const bool box_tma = p.tma_store && (st.ncols - bx * 64) >= 64;
-                    if (box_tma) stage_begin();
+                    if (res_lines && k == 0) {          // the buffer already holds this box's residual
+                        cp_async_wait<0>();
+                        __syncwarp();
+                    } else if (box_tma) {
+                        stage_begin();
+                        if (res_lines) stage_res_lines();
+                    }
 #pragma unroll
                     for (int hc = 0; hc < 2; ++hc) {
                         const int c0 = bx * 64 + hc * 32;
@@ -247,11 +273,21 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                         }
                         if (p.epi == EPI_RESIDUAL && live) {
                             // bf16(acc) + residual, two values per conversion and per addition
+                            Packed16 rs;
+                            if (res_lines) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint4 q = lds128(out_stage + (uint32_t)lane * 128 + ((((uint32_t)(hc * 4 + j)) ^ ((uint32_t)lane & 7u)) << 4));
+                                    rs.w[4 * j] = q.x, rs.w[4 * j + 1] = q.y, rs.w[4 * j + 2] = q.z, rs.w[4 * j + 3] = q.w;
+                                }
+                            } else {
+                                rs = load_packed(p.residual + (size_t)row * p.ldo + col, nvalid);
+                            }
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 float x0, x1;
                                 round_bf16_x2(v[2 * i], v[2 * i + 1], x0, x1);
-                                const uint32_t rw = res_box[hc].w[i];
+                                const uint32_t rw = rs.w[i];
                                 unpack_f32x2(add_f32x2(pack_f32x2(x0, x1),
                                                        pack_f32x2(__uint_as_float(rw << 16), __uint_as_float(rw & 0xFFFF0000u))),
                                              v[2 * i], v[2 * i + 1]);
@@ -261,15 +297,13 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                         if (box_tma) stage_packed(pk, hc);
                         else if (live && !GLMASR_EXP(p, 4)) store_packed(out_row + col, pk, nvalid);
                     }
-                    // the other box's residual: requested now, in flight during the store of this box and the
-                    // tensor-memory load of the next
-                    if (p.epi == EPI_RESIDUAL && k == 0) load_res_box(bx ^ 1);
                     if (box_tma && !GLMASR_EXP(p, 4)) stage_flush(st.col0 + bx * 64, m_tile * 128 + quad * 32);
                 }
             }
             DBG_ACC(2);
             ++acc_it;
         }
+        cp_async_wait<0>();                     // (a copy requested before a wait that gave up)
         if (store_leader) bulk_wait_all();      // this warp's bulk stores are complete before the CTA exits
         __syncwarp();
         if (dbg && warp == 2 && lane == 0 && rank == 0)

@@ -33,13 +33,6 @@ static constexpr int kWarps = 4;
 static constexpr int kWarpSmem = kStages * 2 * kTileBytes;          // K and V rings of one warp: 16 KB
 static constexpr int kAttnSmem = kWarps * kWarpSmem;                // 64 KB
 
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool valid) {
-    const int n = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"

@@ -96,6 +96,17 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ---- TMA ------------------------------------------------------------------------------------
+// 16 bytes global -> shared without a register (zeros when !valid; src must still be an address of the
+// allocation), in groups that cp_async_wait<N> waits for down to the N youngest.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Ask L2 for the 128-byte line at p (no register, no wait).
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tm) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
 }
