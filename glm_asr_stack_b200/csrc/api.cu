@@ -219,6 +219,15 @@ static int split_k_override() {
 }
 
 // GLMASR_PAIR16=0: SiLU-gate epilogues stay on the eight-epilogue-warp pair kernel (comparison runs)
+// GLMASR_SPLIT_TAIL=0: the pair kernel's last, partly filled tile round is not cut into half tiles.
+static bool split_tail_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_SPLIT_TAIL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
 static bool use_pair16_kernel() {
     static int v = -1;
     if (v < 0) {
@@ -617,6 +626,11 @@ static int run_fused(const FusedArgs &a) {
                 g_pair_ready[dev] = true;
             }
             p.num_n_tiles = n_tiles;
+            p.split_tail = (a.epi != EPI_SILU_GATE && split_tail_enabled()) ? 1 : 0;
+            for (int i = 0; i < p.num_segs && p.split_tail; ++i)
+                if (!make_tmap(&p.tm_b_half[i], a.w[i].w_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 2,
+                               (uint64_t)a.w[i].N, (uint64_t)a.K / 2, 128, 64, true))
+                    p.split_tail = 0;
             // epilogue through shared memory + bulk tensor stores when the output can be described to TMA
             bool tma_ok = aligned16(a.out) && (a.ldo % 8) == 0 && !no_tma_store();
             for (int i = 0; i < p.num_segs && a.epi != EPI_SILU_GATE; ++i)

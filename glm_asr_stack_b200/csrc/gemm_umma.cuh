@@ -74,6 +74,10 @@ struct alignas(64) GemmParams {
     float *partial;                     // [tiles][split_k][128 x BN] fp32, column-quad major
     int *tile_counters;                 // [tiles], zero between launches (the last CTA resets its tile's)
     int num_m_tiles, num_n_tiles;
+    // Pair kernel, store / residual epilogues: when the last round of 256 x 256 tiles would occupy at most half of
+    // the CTA pairs, each of its tiles is computed as two 256 x 128 halves by two pairs (N = 128 MMAs).
+    int split_tail;
+    CUtensorMap tm_b_half[kMaxSegments];    // split_tail: the weights again, as 64-row x 128-byte boxes
     int num_k_blocks;                   // K steps of 128 operand bytes per row (W4A4: 256 elements, else 64)
     int sf_k_chunks;                    // W4A4: 512-byte scale chunks per 128-row tile along K (= ceil(K/64))
     int *status;

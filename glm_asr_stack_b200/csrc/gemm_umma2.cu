@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
     } else {
         // ================================ epilogue (both CTAs) ==========================
         const uint32_t rank = ctx.rank, tmem_base = ctx.tmem_base, tiles = ctx.tiles;
-        const int pair = ctx.pair, num_pairs = ctx.num_pairs, num_m_pairs = ctx.num_m_pairs, total_tiles = ctx.total_tiles;
+        const int pair = ctx.pair, num_pairs = ctx.num_pairs, num_m_pairs = ctx.num_m_pairs;
         volatile int *abort_word = ctx.abort_word;
         auto tfull_bar = [&](int a) { return ctx.tfull_bar(a); };
         auto tempty_bar = [&](int a) { return ctx.tempty_bar(a); };
@@ -68,10 +68,16 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             }
         };
         uint32_t acc_it = 0;
-        for (int tile = pair; tile < total_tiles; tile += num_pairs) {
+        for (int w = pair; w < ctx.total_items; w += num_pairs) {
+            int tile, part;
+            ctx.resolve(w, tile, part);
             const int m_tile = (tile % num_m_pairs) * 2 + (int)rank;
             const int n_tile = tile / num_m_pairs;
             const int acc = acc_it & 1;
+            // This warp's columns.  Whole tile: 128-column sub-tile `half`, two 64-column boxes.  Half tile (the
+            // accumulator's first 128 columns hold sub-tile `part`): columns [64 half, 64 half + 64) of it, one box.
+            const int boxes = part < 0 ? 2 : 1;
+            const int w_tcol = part < 0 ? half * 128 : half * 64;      // first tensor-memory column within the accumulator
             const uint32_t aph = (acc_it >> 1) & 1u;
             // The residual does not depend on the accumulator, and a load issued when its value is needed waits
             // behind the operand ring's traffic (about 3000 cycles here), so both 64-column boxes are requested
@@ -80,9 +86,13 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
             // bytes) by whole lines, copy j of lane l being chunk l & 7 of row 4 j + (l >> 3), and the chunks reach
             // their row's lane through the staging buffer: with one row per lane every load would touch 32 lines.
             const bool owns_pre = (half == 1 - acc);
-            const int first_box_pre = (owns_pre && acc == 0) ? 1 : 0;
-            const SubTile st_pre = resolve_subtile(p, n_tile, half, 2);
-            const bool res_lines = p.epi == EPI_RESIDUAL && p.tma_store && st_pre.ncols >= 128 && (p.ldo & 7) == 0 &&
+            const int first_box_pre = (owns_pre && acc == 0 && part < 0) ? 1 : 0;
+            SubTile st_pre = resolve_subtile(p, n_tile, part < 0 ? half : part, 2);
+            if (part >= 0) {
+                st_pre.col0 += half * 64;
+                st_pre.ncols = max(0, min(64, st_pre.ncols - half * 64));
+            }
+            const bool res_lines = p.epi == EPI_RESIDUAL && p.tma_store && st_pre.ncols >= 64 * boxes && (p.ldo & 7) == 0 &&
                                    (((uintptr_t)p.residual) & 15) == 0;
             uint4 res_c[8];
             if (res_lines) {
@@ -97,10 +107,12 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                                      src + first_box_pre * 64 + (in ? (size_t)(4 * j) * p.ldo : 0), in);
                 }
                 cp_async_commit();
+                if (boxes == 2) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    res_c[j] = (r0 + 4 * j < p.M) ? *reinterpret_cast<const uint4 *>(src + (first_box_pre ^ 1) * 64 + (size_t)(4 * j) * p.ldo)
-                                                  : make_uint4(0u, 0u, 0u, 0u);
+                    for (int j = 0; j < 8; ++j)
+                        res_c[j] = (r0 + 4 * j < p.M) ? *reinterpret_cast<const uint4 *>(src + (first_box_pre ^ 1) * 64 + (size_t)(4 * j) * p.ldo)
+                                                      : make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             auto stage_res_lines = [&]() {      // registers -> staging buffer, in the layout stage_packed uses
 #pragma unroll
@@ -231,20 +243,20 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                 }
                 if (box_tma && !GLMASR_EXP(p, 4)) stage_flush(sg.col0 + half * 64, m_tile * 128 + quad * 32);
             } else {
-                const SubTile st = resolve_subtile(p, n_tile, half, 2);
+                const SubTile st = st_pre;          // this warp's columns (128, or 64 of a half tile)
                 const float alpha = p.alpha[st.seg];
                 // the owner's shared columns are its chunks 2, 3 (accumulator 0) or 0, 1 (accumulator 1):
-                // that 64-column box goes first
-                const int first_box = (owns_shared && acc == 0) ? 1 : 0;
+                // that 64-column box goes first (a half tile has one box per warp; the owners signal all the same)
+                const int first_box = first_box_pre;
 #pragma unroll 1
-                for (int k = 0; k < 2; ++k) {
+                for (int k = 0; k < boxes; ++k) {
                     const int bx = k ^ first_box;
                     uint32_t r[2][32];
-                    tmem_ld_x32(t_row + half * 128 + bx * 64, r[0]);
-                    tmem_ld_x32(t_row + half * 128 + bx * 64 + 32, r[1]);
+                    tmem_ld_x32(t_row + w_tcol + bx * 64, r[0]);
+                    tmem_ld_x32(t_row + w_tcol + bx * 64 + 32, r[1]);
                     tmem_ld_wait();
-                    if (k == 1) release_acc();
-                    else if (owns_shared) release_shared();
+                    if (k == 0 && owns_shared) release_shared();
+                    if (k == boxes - 1) release_acc();
                     const bool box_tma = p.tma_store && (st.ncols - bx * 64) >= 64;
                     if (res_lines && k == 0) {          // the buffer already holds this box's residual
                         cp_async_wait<0>();

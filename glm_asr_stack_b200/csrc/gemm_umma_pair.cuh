@@ -63,6 +63,8 @@ struct PairCfgT {
     static constexpr int OUT_STAGE_BYTES = OUT_STAGE_BYTES_;   // per epilogue warp
     static constexpr int SMEM_BYTES = 1024 + BAR_BYTES + STAGES * STAGE_BYTES + EPI_WARPS * OUT_STAGE_BYTES;
     static constexpr uint32_t TX_BYTES_PAIR = 2 * STAGE_BYTES;
+    // a 256 x 128 half tile: 64 weight rows per CTA and one weight-scale tile
+    static constexpr uint32_t TX_BYTES_PAIR_HALF = 2 * (STAGE_BYTES - B_BYTES / 2 - SF_TILE);
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -77,6 +79,20 @@ struct PairCtx {
     uint32_t rank;                // 0 = leader CTA (issues the MMAs), 1 = peer
     int warp, lane;
     int num_pairs, pair, num_m_pairs, total_tiles, nkb;
+    // Work items of the grid, taken round-robin by the pairs: items [0, split_from) are whole tiles; from there on
+    // two consecutive items are the column halves of one tile (GemmParams::split_tail).
+    int split_from, total_items;
+    // item -> tile and part (-1: the whole 256 x 256 tile; 0 / 1: its columns [0, 128) / [128, 256))
+    __device__ __forceinline__ void resolve(int w, int &tile, int &part) const {
+        if (w < split_from) {
+            tile = w;
+            part = -1;
+        } else {
+            const int j = w - split_from;
+            tile = split_from + (j >> 1);
+            part = j & 1;
+        }
+    }
 
     __device__ __forceinline__ uint32_t full_bar(int s) const { return bar + 8u * (uint32_t)s; }
     __device__ __forceinline__ uint32_t empty_bar(int s) const { return bar + 8u * (uint32_t)(C::STAGES + s); }
@@ -120,6 +136,7 @@ __device__ __forceinline__ PairCtx<C> pair_setup_begin(const GemmParams &p, uint
         tma_prefetch_desc(&p.tm_a);
         tma_prefetch_desc(&p.tm_sfa);
         for (int s = 0; s < p.num_segs; ++s) {
+            if (p.split_tail) tma_prefetch_desc(&p.tm_b_half[s]);
             tma_prefetch_desc(&p.tm_b[s]);
             tma_prefetch_desc(&p.tm_sfb[s]);
         }
@@ -144,6 +161,10 @@ __device__ __forceinline__ void pair_setup_finish(const GemmParams &p, PairCtx<C
     c.num_m_pairs = (p.num_m_tiles + 1) >> 1;
     c.total_tiles = c.num_m_pairs * p.num_n_tiles;
     c.nkb = p.num_k_blocks;
+    const int last_round = c.total_tiles % c.num_pairs;
+    const bool split = p.split_tail != 0 && last_round > 0 && 2 * last_round <= c.num_pairs;
+    c.split_from = split ? c.total_tiles - last_round : c.total_tiles;
+    c.total_items = split ? c.total_tiles + last_round : c.total_tiles;
 }
 
 // Warps 0 and C::PRODUCER_B_WARP of both CTAs.
@@ -160,11 +181,16 @@ __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx
     const int rank = (int)c.rank;
     uint32_t it = 0;
     bool ok = !(solo && c.warp == C::PRODUCER_B_WARP);
-    for (int tile = c.pair; ok && tile < c.total_tiles; tile += c.num_pairs) {
+    for (int w = c.pair; ok && w < c.total_items; w += c.num_pairs) {
+        int tile, part;
+        c.resolve(w, tile, part);
         const int m_tile = (tile % c.num_m_pairs) * 2 + rank;     // this CTA's 128-row tile
         const int n_tile = tile / c.num_m_pairs;
-        const SubTile mine = resolve_subtile(p, n_tile, rank, 2);       // the weight half this CTA loads
-        const SubTile st0 = resolve_subtile(p, n_tile, 0, 2);
+        // whole tile: this CTA loads weight sub-tile `rank`; half tile: rows [64 rank, 64 rank + 64) of sub-tile
+        // `part`, through the 64-row view of the weights
+        const SubTile mine = resolve_subtile(p, n_tile, part < 0 ? rank : part, 2);
+        const int b_row = part < 0 ? mine.row0 : mine.row0 + 64 * rank;
+        const SubTile st0 = part < 0 ? resolve_subtile(p, n_tile, 0, 2) : mine;
         const SubTile st1 = resolve_subtile(p, n_tile, 1, 2);
         const int sfa_row = m_tile * p.sf_k_chunks;
         const int sfb_row0 = (st0.row0 >> 7) * p.sf_k_chunks;
@@ -187,15 +213,16 @@ __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx
             }
             if (leader_lane) {
                 if (do_a) {
-                    if (rank == 0) mbar_expect_tx(c.full_bar(s), no_sf ? 2u * (C::A_BYTES + C::B_BYTES) : C::TX_BYTES_PAIR);
+                    if (rank == 0)
+                        mbar_expect_tx(c.full_bar(s), no_sf ? 2u * (C::A_BYTES + C::B_BYTES) : (part < 0 ? C::TX_BYTES_PAIR : C::TX_BYTES_PAIR_HALF));
                     tma_load_2d_pair(sb, &p.tm_a, fb, kb * 128, m_tile * 128);
                     if (!no_sf) tma_load_2d_pair(sf, &p.tm_sfa, fb, 0, sfa_row + kb * 4);
                 }
                 if (do_b) {
-                    tma_load_2d_pair(sb + C::A_BYTES, &p.tm_b[mine.seg], fb, kb * 128, mine.row0);
+                    tma_load_2d_pair(sb + C::A_BYTES, part < 0 ? &p.tm_b[mine.seg] : &p.tm_b_half[mine.seg], fb, kb * 128, b_row);
                     if (!no_sf) {
                         tma_load_2d_pair(sf + C::SF_TILE, &p.tm_sfb[st0.seg], fb, 0, sfb_row0 + kb * 4);
-                        tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
+                        if (part < 0) tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
                     }
                 }
             }
@@ -217,12 +244,15 @@ __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairC
     unsigned long long dbg_acc[4] = {0, 0, 0, 0};
     (void)dbg_acc;
     const bool leader_lane = elect_one();
-    constexpr uint32_t idesc = idesc_nvfp4(256, C::BN);
+    constexpr uint32_t idesc_whole = idesc_nvfp4(256, C::BN), idesc_half = idesc_nvfp4(256, C::BN / 2);
     const uint32_t empty0_peer = mapa_shared(c.empty_bar(0), 1);
     const uint32_t tfull0_peer = mapa_shared(c.tfull_bar(0), 1);
     uint32_t it = 0, acc_it = 0;
     bool ok = true;
-    for (int tile = c.pair; ok && tile < c.total_tiles; tile += c.num_pairs) {
+    for (int w = c.pair; ok && w < c.total_items; w += c.num_pairs) {
+        int tile, part;
+        c.resolve(w, tile, part);
+        const uint32_t idesc = part < 0 ? idesc_whole : idesc_half;   // a half tile fills the first 128 columns of its accumulator
         const int acc = acc_it & 1;
         const uint32_t aph = (acc_it >> 1) & 1u;
         DBG_T0();
@@ -253,10 +283,12 @@ __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairC
                         tmem_cp_32x128b_warpx4_pair(sfa_t + 4 * ch, sfdesc0 + (uint64_t)((ch * C::SF_CHUNK) >> 4));
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
+                        if (h == 0 || part < 0) {
 #pragma unroll
-                        for (int ch = 0; ch < 4; ++ch)
-                            tmem_cp_32x128b_warpx4_pair(sfb_t + ch * 8 + 4 * h,
-                                                        sfdesc0 + (uint64_t)(((1 + h) * C::SF_TILE + ch * C::SF_CHUNK) >> 4));
+                            for (int ch = 0; ch < 4; ++ch)
+                                tmem_cp_32x128b_warpx4_pair(sfb_t + ch * 8 + 4 * h,
+                                                            sfdesc0 + (uint64_t)(((1 + h) * C::SF_TILE + ch * C::SF_CHUNK) >> 4));
+                        }
                 }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {

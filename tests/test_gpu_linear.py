@@ -260,7 +260,7 @@ def test_layer_proj_device_and_host_agree(ops):
 
 
 # ---- W4A4 on CTA pairs (cta_group::2): taken when M >= 512 and there is a 256x256 tile for every pair ----
-@pytest.mark.parametrize("M,N,K", [(2560, 2048, 512), (2500, 2304, 256), (640, 8192, 1024)])
+@pytest.mark.parametrize("M,N,K", [(2560, 2048, 512), (2500, 2304, 256), (640, 8192, 1024), (2500, 1992, 256)])
 def test_pair_kernel_plain(ops, M, N, K):
     pw, sw, g = o.seeded_weight(N, K, 500 + N)
     x = o.seeded_activation(M, K, 600 + M)
@@ -300,6 +300,48 @@ def test_pair_kernel_fused_epilogues(ops):
                                        residual=to_dev_bf16(res), input_scale=isc))
     assert o.rel_err(out, o.residual_add(o.nvfp4_linear(x, w[0], w[1], isc, w[2]), res)) <= REL_TOL_TIGHT
     assert ops.status() == 0
+
+
+def pair_tail_checksums(ops):
+    """Results of pair-kernel launches whose last tile round fills at most half of the CTA pairs (80, 80 and 90
+    tiles for 74 pairs), so that round is cut into 256 x 128 half tiles unless GLMASR_SPLIT_TAIL=0: plain store with
+    ragged rows and columns, residual in place, three fused segments.  Returns per-launch (sum, xor) of the bf16 bits."""
+    out = []
+    for M, N, K, epi, seed in [(2500, 1992, 256, "store", 1), (2560, 2048, 512, "residual", 2), (2500, 2304, 256, "qkv", 3)]:
+        x = o.seeded_activation(M, K, 1200 + seed)
+        isc = o.default_input_scale(x)
+        xd = to_dev_bf16(x)
+        if epi == "qkv":
+            ws = [dev_weight(ops, *o.seeded_weight(n, K, 1210 + i)) for i, n in enumerate((1280, 512, 512))]
+            got = ops.fp4_linear_fused(ops.MODE_W4A4, xd, ws, input_scale=isc)
+        else:
+            w = dev_weight(ops, *o.seeded_weight(N, K, 1220 + seed))
+            res = to_dev_bf16(o.seeded_activation(M, N, 1230 + seed)) if epi == "residual" else None
+            got = ops.fp4_linear_fused(ops.MODE_W4A4, xd, [w], epilogue=ops.EPI_RESIDUAL if res is not None else ops.EPI_STORE,
+                                       residual=res, input_scale=isc)
+        bits = got.view(torch.int16).to(torch.int64) & 0xFFFF
+        weights = torch.arange(bits.numel(), device=bits.device, dtype=torch.int64).view_as(bits) % 65521 + 1
+        out.append((int(bits.sum().item()), int((bits * weights).sum().item())))
+    assert ops.status() == 0
+    return out
+
+
+def test_pair_kernel_half_tiles_equal_whole_tiles():
+    """The last tile round computed as half tiles (default) gives the bytes of whole tiles (GLMASR_SPLIT_TAIL=0,
+    read once per process)."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]\n"
+            "import test_gpu_linear as t\nfrom glm_asr_stack_b200 import ops\n"
+            "print('SUMS', t.pair_tail_checksums(ops))"
+            % (root, os.path.join(root, "oracle"), os.path.join(root, "tests")))
+    seen = []
+    for flag in ("0", "1"):
+        r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, GLMASR_SPLIT_TAIL=flag), capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0 and "SUMS" in r.stdout, r.stdout + r.stderr
+        seen.append([l for l in r.stdout.splitlines() if l.startswith("SUMS")][0])
+    assert seen[0] == seen[1], seen
 
 
 def test_pair_kernel_repeat_launches_stay_identical(ops):
