@@ -371,8 +371,119 @@ __global__ void argmax_rows_kernel(const __nv_bfloat16 *__restrict__ logits, int
     if (tid == 0) out_tokens[row] = sh_idx[0] < 0 ? 0 : sh_idx[0];
 }
 
+// The same arg-max with a row cut into `parts` column ranges, one CTA each (a few hundred rows of a 59264-wide
+// vocabulary are otherwise one or two CTAs per SM, each waiting on a handful of loads at a time).  A CTA leaves its
+// range's winner in `partial`; the CTA that arrives last at the row's counter merges the parts and resets the counter.
+// argmax_better is a total order, so the result is the one-CTA kernel's.
+struct ArgmaxPart {
+    float val;
+    int idx;
+};
+
+__global__ void __launch_bounds__(256) argmax_rows_parts_kernel(const __nv_bfloat16 *__restrict__ logits, int *__restrict__ out_tokens,
+                                                               int rows, int vocab, int parts, ArgmaxPart *partial,
+                                                               unsigned int *counters) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float sh_val[256];
+    __shared__ int sh_idx[256];
+    __shared__ int sh_last;
+    const int row = blockIdx.x / parts, part = blockIdx.x - row * parts, tid = threadIdx.x;
+    if (row >= rows) return;
+    const __nv_bfloat16 *p = logits + (size_t)row * (size_t)vocab;
+    // ranges in whole 16-byte vectors; the last part also takes the columns past the last whole vector
+    const int nvec = vocab / 8;
+    const int per = (nvec + parts - 1) / parts;
+    const int v0 = min(nvec, part * per), v1 = min(nvec, v0 + per);
+    float bv = -1e20f;
+    int bi = -1;
+    auto consider = [&](float v, int i) {
+        if (bi < 0) {
+            if (v > bv) { bv = v; bi = i; }
+        } else if (argmax_better(v, i, bv, bi)) {
+            bv = v;
+            bi = i;
+        }
+    };
+    auto consider8 = [&](const uint4 &q, int c) {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            consider(__uint_as_float(w[j] << 16), c * 8 + 2 * j);
+            consider(__uint_as_float(w[j] & 0xFFFF0000u), c * 8 + 2 * j + 1);
+        }
+    };
+    int c = v0 + tid;
+    for (; c + 768 < v1; c += 1024) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) q[u] = reinterpret_cast<const uint4 *>(p)[c + 256 * u];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) consider8(q[u], c + 256 * u);
+    }
+    for (; c < v1; c += 256) consider8(reinterpret_cast<const uint4 *>(p)[c], c);
+    if (part == parts - 1)
+        for (int v = nvec * 8 + tid; v < vocab; v += 256) consider(__bfloat162float(p[v]), v);
+    auto merge = [&](float ov, int oi) {          // fold (ov, oi) into this thread's slot of the shared arrays
+        const int mi = sh_idx[tid];
+        bool take;
+        if (oi < 0) take = false;
+        else if (mi < 0) take = true;
+        else take = argmax_better(ov, oi, sh_val[tid], mi);
+        if (take) {
+            sh_val[tid] = ov;
+            sh_idx[tid] = oi;
+        }
+    };
+    auto reduce_block = [&]() {
+        __syncthreads();
+        for (int off = 128; off > 0; off >>= 1) {
+            if (tid < off) merge(sh_val[tid + off], sh_idx[tid + off]);
+            __syncthreads();
+        }
+    };
+    sh_val[tid] = bv;
+    sh_idx[tid] = bi;
+    reduce_block();
+    if (tid == 0) {
+        partial[(size_t)row * parts + part] = ArgmaxPart{sh_val[0], sh_idx[0]};
+        __threadfence();
+        const unsigned int old = atomicAdd(counters + row, 1u);
+        sh_last = (old == (unsigned int)parts - 1u) ? 1 : 0;
+        if (sh_last) counters[row] = 0u;          // ready for the next launch
+    }
+    __syncthreads();
+    if (!sh_last) return;
+    __threadfence();
+    sh_val[tid] = -1e20f;
+    sh_idx[tid] = -1;
+    for (int q = tid; q < parts; q += 256) {
+        const int2 raw = __ldcg(reinterpret_cast<const int2 *>(partial + (size_t)row * parts + q));
+        merge(__int_as_float(raw.x), raw.y);
+    }
+    reduce_block();
+    if (tid == 0) out_tokens[row] = sh_idx[0] < 0 ? 0 : sh_idx[0];
+}
+
 void launch_argmax_rows(const __nv_bfloat16 *logits, int *out_tokens, int rows, int vocab, cudaStream_t st) {
     if (rows <= 0) return;
+    // enough CTAs for every SM to hold several; narrow rows stay on the one-CTA kernel
+    const int parts = (vocab >= 16384 && (((uintptr_t)logits & 15) == 0) && (vocab % 8) == 0) ? 4 : 1;
+    if (parts > 1) {
+        constexpr int kArgmaxSlot = 53;
+        static void *zeroed = nullptr;
+        static int zeroed_rows = 0;
+        const size_t part_bytes = ((size_t)rows * parts * sizeof(ArgmaxPart) + 255) & ~(size_t)255;
+        uint8_t *ws = (uint8_t *)workspace_slot(kArgmaxSlot, part_bytes + (size_t)rows * sizeof(unsigned int));
+        if (ws != zeroed || rows != zeroed_rows) {  // a fresh allocation or another layout: every counter starts at zero
+            GLMASR_CUDA_CHECK(cudaMemsetAsync(ws, 0, part_bytes + (size_t)rows * sizeof(unsigned int), st));
+            zeroed = ws;
+            zeroed_rows = rows;
+        }
+        launch_chained(argmax_rows_parts_kernel, dim3(rows * parts), dim3(256), 0, st, logits, out_tokens, rows, vocab, parts,
+                       reinterpret_cast<ArgmaxPart *>(ws), reinterpret_cast<unsigned int *>(ws + part_bytes));
+        return;
+    }
     GLMASR_PREFER_MAX_SMEM(argmax_rows_kernel);
     launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, logits, out_tokens, rows, vocab);
 }

@@ -87,6 +87,14 @@ def test_argmax_with_ties_matches_reference_order(ops):
     bits = o.f32_to_bf16_bits(v)
     got = ops.argmax_rows(to_dev_bf16(bits)).cpu().numpy()
     assert got.tolist() == o.argmax_rows_ref(bits).tolist()
+    # the wide-row kernel cuts a row into column ranges and merges them by a per-row counter that must be back at
+    # zero after every launch, also when the row count (and with it the scratch layout) changes between launches
+    for rows in (256, 5, 300, 5):
+        w = rng.standard_normal((rows, vocab)).astype(np.float32)
+        w[rows // 2, [11, 20000, 45000, vocab - 3]] = 7.5
+        wb = o.f32_to_bf16_bits(w)
+        for _ in range(2):
+            assert ops.argmax_rows(to_dev_bf16(wb)).cpu().numpy().tolist() == o.argmax_rows_ref(wb).tolist()
     # unaligned row pitch (vocab not a multiple of 8)
     b2 = o.f32_to_bf16_bits(rng.standard_normal((3, 1001)).astype(np.float32))
     assert ops.argmax_rows(to_dev_bf16(b2)).cpu().numpy().tolist() == o.argmax_rows_ref(b2).tolist()
