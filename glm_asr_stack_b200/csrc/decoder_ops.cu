@@ -378,10 +378,15 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_warp_kernel(uint8_t *__rest
                 const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float a0 = by_rms(__uint_as_float(xs[j] << 16)) * __uint_as_float(ws[j] << 16);
-                    const float a1 = by_rms(__uint_as_float(xs[j] & 0xFFFF0000u)) * __uint_as_float(ws[j] & 0xFFFF0000u);
-                    v[8 * h + 2 * j] = __bfloat162float(__float2bfloat16(a0));
-                    v[8 * h + 2 * j + 1] = __bfloat162float(__float2bfloat16(a1));
+                    // x / rms * w rounded to bf16, two elements per operation
+                    float q0, q1, a0, a1;
+                    by_rms.pair(__uint_as_float(xs[j] << 16), __uint_as_float(xs[j] & 0xFFFF0000u), q0, q1);
+                    unpack_f32x2(mul_f32x2(pack_f32x2(q0, q1), pack_f32x2(__uint_as_float(ws[j] << 16), __uint_as_float(ws[j] & 0xFFFF0000u))),
+                                 a0, a1);
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(a0, a1);
+                    const uint32_t bw = *reinterpret_cast<const uint32_t *>(&b2);
+                    v[8 * h + 2 * j] = __uint_as_float(bw << 16);
+                    v[8 * h + 2 * j + 1] = __uint_as_float(bw & 0xFFFF0000u);
                 }
             }
             if (normed_out != nullptr) store_bf16x16(normed_out + (size_t)row * dim + (size_t)(b0 + k) * 16, v);

@@ -149,12 +149,26 @@ struct ExactRowDivider {
         fast_min = ok ? 8.6736174e-19f : __int_as_float(0x7FC00000);               // 2^-60, or NaN: never fast
     }
     __device__ __forceinline__ float operator()(float x) const {
-        if (fabsf(x) >= fast_min) {
+        const float ax = fabsf(x);
+        if (ax >= fast_min && ax <= 1.1529215e18f) {                               // 2^-60 .. 2^60
             const float q0 = fmaf(x, r_hi, x * r_lo);
             const float e = fmaf(-q0, d, x);
             return fmaf(e, r_hi, q0);
         }
         return __fdiv_rn(x, d);
+    }
+    // Two quotients with the packed forms of the same four operations (same bits as two calls of operator()).
+    __device__ __forceinline__ void pair(float x0, float x1, float &o0, float &o1) const {
+        const float a0 = fabsf(x0), a1 = fabsf(x1);
+        if (fminf(a0, a1) >= fast_min && fmaxf(a0, a1) <= 1.1529215e18f) {
+            const unsigned long long x2 = pack_f32x2(x0, x1), rh2 = pack_f32x2(r_hi, r_hi);
+            const unsigned long long q0 = fma_f32x2(x2, rh2, mul_f32x2(x2, pack_f32x2(r_lo, r_lo)));
+            const unsigned long long e = fma_f32x2(q0, pack_f32x2(-d, -d), x2);
+            unpack_f32x2(fma_f32x2(e, rh2, q0), o0, o1);
+        } else {
+            o0 = (*this)(x0);
+            o1 = (*this)(x1);
+        }
     }
 };
 
