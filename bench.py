@@ -840,6 +840,11 @@ def main():
     shape_names = {2.0 * M * (HIDDEN + 2 * KV) * HIDDEN: "qkv", 2.0 * M * HIDDEN * HIDDEN: "o",
                    2.0 * M * 2 * FFN * HIDDEN: "gate_up", 2.0 * M * HIDDEN * FFN: "down"}
     ours_ms = {shape_names.get(f, str(f)): statistics.mean(v) for f, v in by_flops.items()}
+    # achieved TFLOP/s and algorithmic GB/s of each of the four launches (same brackets)
+    bytes_of = {f: b for _, f, b in prof}
+    by_shape = {shape_names.get(f, str(f)): {"ms": statistics.mean(v), "tflops": f / (statistics.mean(v) * 1e-3) / 1e12,
+                                              "algorithmic_gbs": bytes_of[f] / (statistics.mean(v) * 1e-3) / 1e9}
+                for f, v in by_flops.items()}
     peaks = measured_peaks()
     if args.mode == "w4a4":
         peak, peak_src = NOMINAL_FP4_TFLOPS, "nominal dense FP4 9 PFLOP/s (MEASURED_PEAKS.json holds no FP4 figure)"
@@ -856,6 +861,7 @@ def main():
     roofline = {"bound": "tensor", "kernel": kname, "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
                 "traffic": traffic, "launch_ms": top_ms, "gemm_ms_per_step": all_ms, "launch_ms_by_shape": ours_ms,
+                "by_shape": by_shape,
                 "achieved_gbs": top[0][2] / (top_ms * 1e-3) / 1e9,
                 "frac_of_measured_bf16": (achieved / peaks["bf16_tflops"]) if peaks else None,
                 "how": "CUDA events around every GEMM launch of 8 steps run right after the timed region"}
