@@ -413,15 +413,16 @@ __global__ void __launch_bounds__(256) argmax_rows_parts_kernel(const __nv_bfloa
             consider(__uint_as_float(w[j] & 0xFFFF0000u), c * 8 + 2 * j + 1);
         }
     };
-    int c = v0 + tid;
-    for (; c + 768 < v1; c += 1024) {
-        uint4 q[4];
+    // eight loads in flight per thread (a range of a 59264-wide row is seven or eight vectors per thread: one batch)
+    for (int c = v0 + tid; c < v1; c += 2048) {
+        uint4 q[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) q[u] = reinterpret_cast<const uint4 *>(p)[c + 256 * u];
+        for (int u = 0; u < 8; ++u)
+            if (c + 256 * u < v1) q[u] = reinterpret_cast<const uint4 *>(p)[c + 256 * u];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) consider8(q[u], c + 256 * u);
+        for (int u = 0; u < 8; ++u)
+            if (c + 256 * u < v1) consider8(q[u], c + 256 * u);
     }
-    for (; c < v1; c += 256) consider8(reinterpret_cast<const uint4 *>(p)[c], c);
     if (part == parts - 1)
         for (int v = nvec * 8 + tid; v < vocab; v += 256) consider(__bfloat162float(p[v]), v);
     auto merge = [&](float ov, int oi) {          // fold (ov, oi) into this thread's slot of the shared arrays
