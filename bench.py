@@ -946,7 +946,10 @@ def main():
         secondary["note"] = ("decode / prefill: every projection block-scaled FP4 (W4A4), the arithmetic the path is built "
                              "for (GLMASR_USE_CUTLASS_NVFP4=1 GLMASR_NVFP4_PAIRS=1); *_reference_mix: what the reference "
                              "computes under GLMASR_USE_CUTLASS_NVFP4=1 and this library's drivers do by default -- q, o, down "
-                             "W4A4, the same-input pairs k|v and gate|up as fused W4A16 GEMMs")
+                             "W4A4, the same-input pairs k|v and gate|up as fused W4A16 GEMMs, which run on bf16 copies of "
+                             "those weights made on first use and kept on the device (1.53 GB for 28 layers, "
+                             "GLMASR_W4A16_RESIDENT_MB; the reference dequantises them on every call), so that step streams "
+                             "1.53 GB more than the algorithmic FP4 bytes its roofline is computed from")
 
     if rank == 0:
         line = {

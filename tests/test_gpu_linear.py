@@ -461,6 +461,24 @@ def run_small_m_case(ops, M, N, K, epi):
     assert ops.status() == 0
 
 
+def test_w4a16_in_kernel_dequant_in_subprocess():
+    """W4A16 calls run on resident bf16 copies of the weights by default; with GLMASR_W4A16_RESIDENT_MB=0 (read once
+    per process) they take the kernel that dequantises inside the GEMM, which must meet the same bars."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys; sys.path[:0]=[%r,%r,%r]\n"
+            "import test_gpu_linear as t\nfrom glm_asr_stack_b200 import ops\n"
+            "for c in [(1, 128, 256), (17, 64, 512), (256, 6144, 2048), (300, 640, 512)]:\n"
+            "    t.test_fp4_linear_w4a16_vs_o1(ops, *c)\n"
+            "t.test_fused_qkv_segments(ops, 'w4a16')\nt.test_fused_silu_gate_epilogue(ops, 'w4a16', 300, 640, 512)\n"
+            "t.test_fused_residual_epilogue(ops, 'w4a16')\nt.test_w4a16_two_subtile_tiles_store_every_column(ops)\n"
+            "print('IN-KERNEL OK')"
+            % (root, os.path.join(root, "oracle"), os.path.join(root, "tests")))
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, GLMASR_W4A16_RESIDENT_MB="0"), capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0 and "IN-KERNEL OK" in r.stdout, r.stdout + r.stderr
+
+
 def test_split_k_in_subprocess():
     """The split-K variant (GLMASR_SPLIT_K, read once per process): partials summed in split order by the CTA
     that finishes last -- same bar against O2, and bit-identical results across repeated launches."""
