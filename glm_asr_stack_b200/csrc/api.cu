@@ -701,7 +701,9 @@ static int run_fused(const FusedArgs &a) {
     }
 
     // W4A4 with enough 256 x 256 tiles for every CTA pair: the cta_group::2 kernel
-    if (a.mode == GEMM_W4A4 && use_pair_kernel()) {
+    // (a bias together with a residual stays on the single-CTA kernel, whose epilogue rounds bf16(acc) + bias before
+    // the residual is added, as residual_add_bias does: Infer-engine/cuda/kernels.cu:763-782)
+    if (a.mode == GEMM_W4A4 && use_pair_kernel() && !(a.bias != nullptr && a.epi == EPI_RESIDUAL)) {
         const int n_tiles = a.epi == EPI_SILU_GATE ? p.seg_subtiles[0] : (subtiles + 1) / 2;
         const int m_pairs = (p.num_m_tiles + 1) / 2;
         const int pairs = num_sms() / 2;
