@@ -320,6 +320,12 @@ def library_fp4_yardstick(shapes, big=8192):
     res["peak_shape"] = f"{big}^3"
     res["peak_ms"] = best.value
     res["peak_tflops"] = 2.0 * big ** 3 / (best.value * 1e-3) / 1e12
+    # the same GEMM back to back for about a second: the rate the power cap leaves the library, to read the sustained
+    # headline against (the burst figure above runs at the boost clock)
+    iters_1s = max(20, int(1.0 / (best.value * 1e-3)))
+    if fn(big, big, big, iters_1s, 3, 2, 1, ctypes.byref(best), ctypes.byref(first)) == 0:
+        res["sustained_tflops"] = 2.0 * big ** 3 / (best.value * 1e-3) / 1e12
+        res["sustained_calls"] = iters_1s
     res["shapes"] = {}
     for name, (M, N, K) in shapes.items():
         if fn(M, N, K, 20, 3, 4, 4, ctypes.byref(best), ctypes.byref(first)) == 0:
@@ -880,6 +886,11 @@ def main():
                                                    f"{yard['peak_shape']} on this GPU, best of the heuristic's algorithms, "
                                                    "20 back-to-back calls (burst)")
                 roofline["frac_of_fp4_measured"] = achieved / yard["peak_tflops"]
+                if "sustained_tflops" in yard:
+                    roofline["fp4_measured_sustained_tflops"] = yard["sustained_tflops"]
+                    roofline["fp4_measured_sustained_how"] = (f"the same {yard['peak_shape']} GEMM, {yard['sustained_calls']} calls back "
+                                                              "to back (about 1 s, under the power cap like the sustained headline)")
+                    roofline["layer_sustained_over_fp4_measured_sustained"] = value / yard["sustained_tflops"]
                 roofline["library_gemm"] = yard["shapes"]
                 # the same four launches of this library under the library's timing conditions
                 own = own_gemm_like_library(M, keep, (isc_h, isc_h * 0.5))
