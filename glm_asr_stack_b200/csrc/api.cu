@@ -257,6 +257,15 @@ static int split_k_override() {
 }
 
 // GLMASR_PAIR16=0: SiLU-gate epilogues stay on the eight-epilogue-warp pair kernel (comparison runs)
+// GLMASR_BF16_PAIR=0: bf16 GEMMs never take the CTA-pair kernel.
+static bool use_pair_bf16() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("GLMASR_BF16_PAIR");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
 // GLMASR_SPLIT_TAIL=0: the pair kernel's last, partly filled tile round is not cut into half tiles.
 static bool split_tail_enabled() {
     static int v = -1;
@@ -703,7 +712,9 @@ static int run_fused(const FusedArgs &a) {
     // W4A4 with enough 256 x 256 tiles for every CTA pair: the cta_group::2 kernel
     // (a bias together with a residual stays on the single-CTA kernel, whose epilogue rounds bf16(acc) + bias before
     // the residual is added, as residual_add_bias does: Infer-engine/cuda/kernels.cu:763-782)
-    if (a.mode == GEMM_W4A4 && use_pair_kernel() && !(a.bias != nullptr && a.epi == EPI_RESIDUAL)) {
+    // The bf16 GEMM takes the same kernel on bf16 operands (GLMASR_BF16_PAIR=0: always the single-CTA kernel).
+    const bool pair_bf16 = a.mode == GEMM_BF16 && use_pair_bf16();
+    if ((a.mode == GEMM_W4A4 || pair_bf16) && use_pair_kernel() && (pair_bf16 || !(a.bias != nullptr && a.epi == EPI_RESIDUAL))) {
         const int n_tiles = a.epi == EPI_SILU_GATE ? p.seg_subtiles[0] : (subtiles + 1) / 2;
         const int m_pairs = (p.num_m_tiles + 1) / 2;
         const int pairs = num_sms() / 2;
@@ -713,7 +724,7 @@ static int run_fused(const FusedArgs &a) {
                 g_pair_ready[dev] = true;
             }
             p.num_n_tiles = n_tiles;
-            p.split_tail = (a.epi != EPI_SILU_GATE && split_tail_enabled()) ? 1 : 0;
+            p.split_tail = (!pair_bf16 && a.epi != EPI_SILU_GATE && split_tail_enabled()) ? 1 : 0;
             for (int i = 0; i < p.num_segs && p.split_tail; ++i)
                 if (!make_tmap(&p.tm_b_half[i], a.w[i].w_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.K / 2,
                                (uint64_t)a.w[i].N, (uint64_t)a.K / 2, 128, 64, true))
@@ -723,7 +734,7 @@ static int run_fused(const FusedArgs &a) {
             for (int i = 0; i < p.num_segs && a.epi != EPI_SILU_GATE; ++i)
                 if (i + 1 < p.num_segs && (p.seg_rows[i] % 8) != 0) tma_ok = false;   // segment column offsets stay 16-byte aligned
             // SiLU-gate epilogues run on the sixteen-epilogue-warp variant (32 x 32 output boxes)
-            const bool wide = a.epi == EPI_SILU_GATE && use_pair16_kernel();
+            const bool wide = !pair_bf16 && a.epi == EPI_SILU_GATE && use_pair16_kernel();
             if (tma_ok && a.q_out == nullptr)
                 tma_ok = wide ? make_tmap(&p.tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)p.n_out, (uint64_t)a.M,
                                           (uint64_t)a.ldo * 2, 32, 32, false, true)
@@ -754,6 +765,7 @@ static int run_fused(const FusedArgs &a) {
                 tl.bytes = (double)n_rows * a.K * 0.5625 + (double)a.M * a.K * 0.5625 + 2.0 * a.M * p.n_out +
                            (a.epi == EPI_RESIDUAL ? 2.0 * a.M * p.n_out : 0.0);
                 if (a.q_out != nullptr) tl.bytes -= (2.0 - 0.5625) * a.M * p.n_out;   // e2m1 + scales instead of bf16
+                if (pair_bf16) tl.bytes += ((double)n_rows * a.K + (double)a.M * a.K) * (2.0 - 0.5625);   // bf16 operands
                 cudaEventRecord(tl.start, g_stream);
             }
             if (wide) {
@@ -762,7 +774,7 @@ static int run_fused(const FusedArgs &a) {
                     g_pair16_ready[dev] = true;
                 }
                 if (launch_umma_gemm_pair16(p, pairs, g_stream) != cudaSuccess) return -1;
-            } else if (launch_umma_gemm_pair(p, pairs, g_stream) != cudaSuccess) {
+            } else if ((pair_bf16 ? launch_umma_gemm_pair_bf16(p, pairs, g_stream) : launch_umma_gemm_pair(p, pairs, g_stream)) != cudaSuccess) {
                 return -1;
             }
             ++g_launches;

@@ -88,6 +88,8 @@ struct alignas(64) GemmParams {
 // W4A4 on CTA pairs (cta_group::2): 256 x 256 tiles, one cluster of two CTAs per tile.
 cudaError_t launch_umma_gemm_pair(const GemmParams &p, int num_pairs, cudaStream_t st);
 cudaError_t umma_gemm_pair_init();
+// The same kernel on bf16 operands (kind::f16, no scale factors): tm_a / tm_b are the bf16 views, num_k_blocks = K / 64.
+cudaError_t launch_umma_gemm_pair_bf16(const GemmParams &p, int num_pairs, cudaStream_t st);
 // Same pipeline with sixteen epilogue warps, for the SiLU-gate epilogues (gemm_umma3.cu); tm_out must be
 // a 32-row x 32-column, 64B-swizzled view of the output when tma_store is set.
 cudaError_t launch_umma_gemm_pair16(const GemmParams &p, int num_pairs, cudaStream_t st);

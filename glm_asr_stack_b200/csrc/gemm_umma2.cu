@@ -19,6 +19,7 @@ namespace glmasr {
 // 32 rows x 64 bf16 (128B-swizzled) of output staging per epilogue warp; 1 KB of barriers and flags
 using PairCfg = PairCfgT<8, 32 * 128, 1024>;
 
+template <bool BF16>
 __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
     using C = PairCfg;
     extern __shared__ uint8_t smem_dyn[];
@@ -27,9 +28,9 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
 
     const int warp = ctx.warp, lane = ctx.lane;
     if (warp == 0 || warp == C::PRODUCER_B_WARP) {
-        pair_producer<C>(p, ctx);
+        pair_producer<C, BF16>(p, ctx);
     } else if (warp == 1) {
-        pair_mma_issuer<C>(p, ctx);
+        pair_mma_issuer<C, BF16>(p, ctx);
     } else {
         // ================================ epilogue (both CTAs) ==========================
         const uint32_t rank = ctx.rank, tmem_base = ctx.tmem_base, tiles = ctx.tiles;
@@ -280,8 +281,22 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
                         if (p.bias != nullptr && nvalid > 0) {
                             float b[32];
                             unpack_bf16(load_packed(p.bias + col, nvalid), b);
+                            // With a residual the reference adds the bias to the linear's bf16 OUTPUT and rounds again
+                            // before the residual (residual_add_bias, Infer-engine/cuda/kernels.cu:763-782).  Only the
+                            // bf16 instance takes that combination (the host keeps it off the FP4 instance).
+                            if (BF16 && p.epi == EPI_RESIDUAL) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] += b[i];
+                                for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]) + b[i];
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] += b[i];
+                            }
+                        }
+                        if constexpr (BF16) {
+                            if (p.epi == EPI_GELU) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+                            }
                         }
                         if (p.epi == EPI_RESIDUAL && live) {
                             // bf16(acc) + residual, two values per conversion and per addition
@@ -326,11 +341,17 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
 }
 
 cudaError_t umma_gemm_pair_init() {
-    return cudaFuncSetAttribute(umma_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES);
+    const cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(umma_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES);
 }
 
 cudaError_t launch_umma_gemm_pair(const GemmParams &p, int num_pairs, cudaStream_t st) {
-    return pair_launch<PairCfg>(umma_gemm_pair_kernel, p, num_pairs, st);
+    return pair_launch<PairCfg>(umma_gemm_pair_kernel<false>, p, num_pairs, st);
+}
+
+cudaError_t launch_umma_gemm_pair_bf16(const GemmParams &p, int num_pairs, cudaStream_t st) {
+    return pair_launch<PairCfg>(umma_gemm_pair_kernel<true>, p, num_pairs, st);
 }
 
 }  // namespace glmasr

@@ -167,8 +167,9 @@ __device__ __forceinline__ void pair_setup_finish(const GemmParams &p, PairCtx<C
     c.total_items = split ? c.total_tiles + last_round : c.total_tiles;
 }
 
-// Warps 0 and C::PRODUCER_B_WARP of both CTAs.
-template <class C>
+// Warps 0 and C::PRODUCER_B_WARP of both CTAs.  BF16: the operands are bf16 (64 elements per 128-byte row, kind::f16
+// MMAs) and there are no scale factors; a stage keeps its layout and leaves the scale-factor part unused.
+template <class C, bool BF16 = false>
 __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx<C> &c) {
     const bool dbg = GLMASR_EXP(p, 64) && p.dbg_cycles != nullptr;
     unsigned long long dbg_acc[4] = {0, 0, 0, 0};
@@ -177,6 +178,7 @@ __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx
     const bool solo = GLMASR_EXP(p, 256);
     const bool do_a = c.warp == 0, do_b = solo ? c.warp == 0 : c.warp == C::PRODUCER_B_WARP;
     const bool leader_lane = elect_one();
+    constexpr int KX = BF16 ? 64 : 128;                        // elements of the operand maps per 128-byte row (bf16 / packed e2m1 bytes)
     const uint32_t full0 = mapa_shared(c.full_bar(0), 0);      // CTA 0's full[0]; full[s] = full0 + 8 s
     const int rank = (int)c.rank;
     uint32_t it = 0;
@@ -204,7 +206,7 @@ __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx
             const uint32_t sb = c.stage_base(s);
             const uint32_t fb = full0 + 8u * (uint32_t)s;
             const uint32_t sf = sb + C::A_BYTES + C::B_BYTES;
-            const bool no_sf = GLMASR_EXP(p, 2);      // experiment: no scale-factor traffic (wrong results)
+            const bool no_sf = BF16 || GLMASR_EXP(p, 2);      // (experiment 2: no scale-factor traffic, wrong results)
             if (GLMASR_EXP(p, 8) && it >= (uint32_t)C::STAGES) {
                 // experiment: operands stay resident in shared memory after the first round of the ring
                 if (leader_lane && do_a && rank == 0) mbar_arrive(c.full_bar(s));
@@ -214,12 +216,13 @@ __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx
             if (leader_lane) {
                 if (do_a) {
                     if (rank == 0)
-                        mbar_expect_tx(c.full_bar(s), no_sf ? 2u * (C::A_BYTES + C::B_BYTES) : (part < 0 ? C::TX_BYTES_PAIR : C::TX_BYTES_PAIR_HALF));
-                    tma_load_2d_pair(sb, &p.tm_a, fb, kb * 128, m_tile * 128);
+                        mbar_expect_tx(c.full_bar(s), no_sf ? 2u * (C::A_BYTES + (part < 0 ? C::B_BYTES : C::B_BYTES / 2))
+                                                            : (part < 0 ? C::TX_BYTES_PAIR : C::TX_BYTES_PAIR_HALF));
+                    tma_load_2d_pair(sb, &p.tm_a, fb, kb * KX, m_tile * 128);
                     if (!no_sf) tma_load_2d_pair(sf, &p.tm_sfa, fb, 0, sfa_row + kb * 4);
                 }
                 if (do_b) {
-                    tma_load_2d_pair(sb + C::A_BYTES, part < 0 ? &p.tm_b[mine.seg] : &p.tm_b_half[mine.seg], fb, kb * 128, b_row);
+                    tma_load_2d_pair(sb + C::A_BYTES, part < 0 ? &p.tm_b[mine.seg] : &p.tm_b_half[mine.seg], fb, kb * KX, b_row);
                     if (!no_sf) {
                         tma_load_2d_pair(sf + C::SF_TILE, &p.tm_sfb[st0.seg], fb, 0, sfb_row0 + kb * 4);
                         if (part < 0) tma_load_2d_pair(sf + 2 * C::SF_TILE, &p.tm_sfb[st1.seg], fb, 0, sfb_row1 + kb * 4);
@@ -237,14 +240,15 @@ __device__ __forceinline__ void pair_producer(const GemmParams &p, const PairCtx
 }
 
 // Warp 1.  Only the leader CTA issues; the peer's warp 1 falls through to the teardown.
-template <class C>
+template <class C, bool BF16 = false>
 __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairCtx<C> &c) {
     if (c.rank != 0) return;
     const bool dbg = GLMASR_EXP(p, 64) && p.dbg_cycles != nullptr;
     unsigned long long dbg_acc[4] = {0, 0, 0, 0};
     (void)dbg_acc;
     const bool leader_lane = elect_one();
-    constexpr uint32_t idesc_whole = idesc_nvfp4(256, C::BN), idesc_half = idesc_nvfp4(256, C::BN / 2);
+    constexpr uint32_t idesc_whole = BF16 ? idesc_bf16(256, C::BN) : idesc_nvfp4(256, C::BN);
+    constexpr uint32_t idesc_half = BF16 ? idesc_bf16(256, C::BN / 2) : idesc_nvfp4(256, C::BN / 2);
     const uint32_t empty0_peer = mapa_shared(c.empty_bar(0), 1);
     const uint32_t tfull0_peer = mapa_shared(c.tfull_bar(0), 1);
     uint32_t it = 0, acc_it = 0;
@@ -277,7 +281,7 @@ __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairC
             const uint64_t bdesc0 = smem_desc_sw128(b_addr);
             if (leader_lane) {
                 const uint64_t sfdesc0 = smem_desc_sf_chunk(a_addr + C::A_BYTES + C::B_BYTES);
-                if (!(GLMASR_EXP(p, 32) && it > 0)) {        // experiment: scale factors copied once (wrong results)
+                if (!BF16 && !(GLMASR_EXP(p, 32) && it > 0)) {        // (experiment 32: scale factors copied once, wrong results)
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch)
                         tmem_cp_32x128b_warpx4_pair(sfa_t + 4 * ch, sfdesc0 + (uint64_t)((ch * C::SF_CHUNK) >> 4));
@@ -293,8 +297,11 @@ __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairC
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                    umma_nvfp4_pair(d_tmem, adesc0 + (uint64_t)((k * 32) >> 4), bdesc0 + (uint64_t)((k * 32) >> 4), idesc,
-                                    accumulate, sfa_t + 4 * k, sfb_t + 8 * k);
+                    if constexpr (BF16)
+                        umma_bf16_pair(d_tmem, adesc0 + (uint64_t)((k * 32) >> 4), bdesc0 + (uint64_t)((k * 32) >> 4), idesc, accumulate);
+                    else
+                        umma_nvfp4_pair(d_tmem, adesc0 + (uint64_t)((k * 32) >> 4), bdesc0 + (uint64_t)((k * 32) >> 4), idesc,
+                                        accumulate, sfa_t + 4 * k, sfb_t + 8 * k);
                 }
                 umma_commit_pair(c.empty_bar(s));                       // frees the stage in this CTA ...
                 umma_commit_pair(empty0_peer + 8u * (uint32_t)s);       // ... and in the peer
