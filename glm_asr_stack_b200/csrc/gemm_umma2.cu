@@ -10,6 +10,8 @@
 #include "fp4_format.cuh"
 #include "gemm_device.cuh"
 #include "gemm_umma.cuh"
+#include <type_traits>
+
 #include "gemm_umma_pair.cuh"
 #include "ptx.cuh"
 #include "runtime.cuh"
@@ -18,10 +20,11 @@ namespace glmasr {
 
 // 32 rows x 64 bf16 (128B-swizzled) of output staging per epilogue warp; 1 KB of barriers and flags
 using PairCfg = PairCfgT<8, 32 * 128, 1024>;
+using PairCfgBf16 = PairCfgT<8, 32 * 128, 1024, false>;
 
 template <bool BF16>
 __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
-    using C = PairCfg;
+    using C = typename std::conditional<BF16, PairCfgBf16, PairCfg>::type;
     extern __shared__ uint8_t smem_dyn[];
     PairCtx<C> ctx = pair_setup_begin<C>(p, smem_dyn);
     pair_setup_finish<C>(p, ctx);
@@ -343,7 +346,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1) umma_gemm_pair_kernel(con
 cudaError_t umma_gemm_pair_init() {
     const cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(umma_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES);
+    return cudaFuncSetAttribute(umma_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfgBf16::SMEM_BYTES);
 }
 
 cudaError_t launch_umma_gemm_pair(const GemmParams &p, int num_pairs, cudaStream_t st) {
@@ -351,7 +354,7 @@ cudaError_t launch_umma_gemm_pair(const GemmParams &p, int num_pairs, cudaStream
 }
 
 cudaError_t launch_umma_gemm_pair_bf16(const GemmParams &p, int num_pairs, cudaStream_t st) {
-    return pair_launch<PairCfg>(umma_gemm_pair_kernel<true>, p, num_pairs, st);
+    return pair_launch<PairCfgBf16>(umma_gemm_pair_kernel<true>, p, num_pairs, st);
 }
 
 }  // namespace glmasr

@@ -33,17 +33,20 @@
 
 namespace glmasr {
 
-template <int EPI_WARPS_, int OUT_STAGE_BYTES_, int BAR_BYTES_>
+// SCALES_ = false: bf16 operands.  A stage then has no scale-factor part (32 KB, six stages) and the two accumulators
+// take 256 tensor-memory columns each without sharing any (nothing else needs columns), so a tile's MMAs wait only
+// for the epilogue of the tile before the previous one.
+template <int EPI_WARPS_, int OUT_STAGE_BYTES_, int BAR_BYTES_, bool SCALES_ = true>
 struct PairCfgT {
     static constexpr int BN = 256;
     static constexpr int A_BYTES = 128 * 128;             // this CTA's 128 rows x 256 k of packed e2m1
     static constexpr int B_BYTES = 128 * 128;             // this CTA's half of the weight tile
     static constexpr int SF_CHUNK = 512;
     static constexpr int SF_TILE = 4 * SF_CHUNK;          // 128 rows x 256 k of scales
-    static constexpr int SFA_BYTES = SF_TILE;
-    static constexpr int SFB_BYTES = 2 * SF_TILE;         // all 256 weight rows
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 38912
-    static constexpr int STAGES = 5;
+    static constexpr int SFA_BYTES = SCALES_ ? SF_TILE : 0;
+    static constexpr int SFB_BYTES = SCALES_ ? 2 * SF_TILE : 0;         // all 256 weight rows
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 38912 (32768 without scales)
+    static constexpr int STAGES = SCALES_ ? 5 : 6;
     static constexpr int EPI_WARPS = EPI_WARPS_;
     // warp 0: producer of the activation tile and its scales; warp 1: MMA issuer; warps 2 .. 1 + EPI_WARPS:
     // epilogue; the last warp: producer of the weight half-tile and the weight scales.  Two producer warps
@@ -54,7 +57,7 @@ struct PairCfgT {
     // Two accumulators that share 64 columns: acc0 = columns [0, 256), acc1 = [192, 448).  A tile's
     // MMAs may start as soon as the previous tile's epilogue has drained the 64 shared columns
     // (which it does first), instead of the whole accumulator.
-    static constexpr int ACC_STRIDE = 192;
+    static constexpr int ACC_STRIDE = SCALES_ ? 192 : 256;
     static constexpr int OVL_LO = 192, OVL_HI = 256;      // shared physical columns
     static constexpr int SFA_COL = 448;
     static constexpr int SFB_COL = SFA_COL + 16;          // 464 .. 495
@@ -263,7 +266,11 @@ __device__ __forceinline__ void pair_mma_issuer(const GemmParams &p, const PairC
         // this accumulator's previous tile (two tiles ago) fully drained ...
         if (!mbar_wait_warp(c.tempty_bar(acc), aph ^ 1u, c.abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
         // ... and the shared columns drained by the previous tile's epilogue
-        if (acc_it > 0 && !mbar_wait_warp(c.tovl_bar(), (acc_it - 1) & 1u, c.abort_word, ST_TIMEOUT_MMA)) { ok = false; break; }
+        if (C::ACC_STRIDE < C::BN && acc_it > 0 &&
+            !mbar_wait_warp(c.tovl_bar(), (acc_it - 1) & 1u, c.abort_word, ST_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+        }
         DBG_ACC(0);
         tc_fence_after();
         const uint32_t d_tmem = c.tmem_base + (uint32_t)(acc * C::ACC_STRIDE);
