@@ -612,6 +612,12 @@ def measure_e2e(model, total_windows, new_tokens, dist, rank, local_rank, world,
     pipe.new_tokens = 4                                        # warm-up: a few windows, a few tokens, same buffers
     pipe.transcribe(pcm[:min(warm_windows, max(n, 1))])
     pipe.new_tokens = new_tokens
+    if dist is not None:
+        # the gather of the token ids once untimed, with the shapes of the timed one: the first point-to-point exchange
+        # of a process group sets up its connections (0.15 s at 2 ranks, 1.7 s at 8), which is start-up, not transcription
+        base0 = total_windows // world
+        warm = torch.zeros((base0 + 1, new_tokens), dtype=torch.int32, device="cuda")
+        dist.gather(warm, [torch.empty_like(warm) for _ in range(world)] if rank == 0 else None, dst=0)
     torch.cuda.synchronize()
     from glm_asr_stack_b200 import ops
     _st = ops.status()
