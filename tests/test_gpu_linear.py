@@ -104,7 +104,9 @@ def test_bias_in_fp4_linear(ops):
     assert o.rel_err(out, o.fp4_linear(x, pw, sw, g, None, bias)) <= REL_TOL_TIGHT
 
 
-@pytest.mark.parametrize("M,N,K", [(3, 128, 64), (256, 1024, 512), (70, 59264 // 8, 256)])
+# (the last two: enough 256 x 256 tiles for every CTA pair, so the bf16 instance of the pair kernel, with ragged rows
+#  and a column count that is not a multiple of 64)
+@pytest.mark.parametrize("M,N,K", [(3, 128, 64), (256, 1024, 512), (70, 59264 // 8, 256), (2500, 1992, 256), (5000, 1280, 1280)])
 def test_bf16_linear(ops, M, N, K):
     rng = np.random.default_rng(21)
     x = o.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
@@ -458,6 +460,29 @@ def run_small_m_case(ops, M, N, K, epi):
     assert o.rel_err(bits_of(first), want) <= tol
     for _ in range(20):
         assert torch.equal(f(), first)
+    assert ops.status() == 0
+
+
+def test_w4a16_pair_kernel_epilogues(ops):
+    """W4A16 at prefill size runs the bf16 instance of the CTA-pair kernel on resident bf16 copies of the weights: three
+    fused segments, SiLU-gate and residual epilogues against the oracle's fallback arithmetic (O1')."""
+    M, K = 3300, 512
+    x = o.seeded_activation(M, K, 1700)
+    xd = to_dev_bf16(x)
+    ws = [o.seeded_weight(n, K, 1710 + i) for i, n in enumerate((1024, 256, 256))]
+    out = bits_of(ops.fp4_linear_fused(ops.MODE_W4A16, xd, [dev_weight(ops, *w) for w in ws]))
+    col = 0
+    for (pw, sw, g), n in zip(ws, (1024, 256, 256)):
+        assert o.rel_err(out[:, col:col + n], o.fp4_linear(x, pw, sw, g)) <= REL_TOL_TIGHT, col
+        col += n
+    wg, wu = o.seeded_weight(1024, K, 1720), o.seeded_weight(1024, K, 1721)
+    act = bits_of(ops.fp4_linear_fused(ops.MODE_W4A16, xd, [dev_weight(ops, *wg), dev_weight(ops, *wu)], epilogue=ops.EPI_SILU_GATE))
+    want = o.silu_mul_split_packed(np.concatenate([o.fp4_linear(x, *wg), o.fp4_linear(x, *wu)], axis=1))
+    assert o.rel_err(act, want) <= REL_TOL_VS_ORACLE and o.cosine(act, want) >= 0.9999
+    w = o.seeded_weight(2048, K, 1730)
+    res = o.seeded_activation(M, 2048, 1731)
+    out = bits_of(ops.fp4_linear_fused(ops.MODE_W4A16, xd, [dev_weight(ops, *w)], epilogue=ops.EPI_RESIDUAL, residual=to_dev_bf16(res)))
+    assert o.rel_err(out, o.residual_add(o.fp4_linear(x, *w), res)) <= REL_TOL_TIGHT
     assert ops.status() == 0
 
 
